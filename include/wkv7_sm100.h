@@ -1,0 +1,94 @@
+/*
+ * C ABI of libwkv7_sm100.so — the B200 (sm_100a) implementation of the RWKV-7 WKV7 hot path.
+ *
+ * Plain pointers and sizes only; every buffer (inputs, outputs, checkpoints) is owned and
+ * allocated by the caller, the library never allocates device memory.  All pointers are device
+ * pointers unless said otherwise.  Every entry point validates its arguments on the host and
+ * returns a status code (0 = success, negative = WKV7_ERR_*) without launching anything when
+ * validation fails.  Kernels are launched on `stream` (a cudaStream_t passed as void*; 0 = the
+ * default stream) and the call returns without synchronising.
+ *
+ * Tensor layout (the reference's internal op layout, wind_rwkv/rwkv7/rwkv7_attn.py:53-59):
+ *   r, w, k, v, a, b, g, y and their gradients: [B, T, H, N] with element strides
+ *   (stride_b, stride_t, stride_h, 1); N == 64.  A contiguous [B, T, H*N] tensor has
+ *   stride_b = T*H*N, stride_t = H*N, stride_h = N.  Head- or batch-sharded views are
+ *   expressed through the strides.  Base pointers and strides must keep every row 16-byte
+ *   aligned.  States s0, sT, dsT, ds0: fp32 [B, H, N, N] contiguous, S[value][key].
+ *   Checkpoints: fp32 [B, H, T/16, N, N] contiguous (state at the start of every 16-step chunk).
+ *   io_dtype: WKV7_BF16 (bf16 tensors, single-TF32 tensor-core products, fp32 state) or
+ *   WKV7_F32 (fp32 tensors, 3xTF32 split products).
+ *
+ * Recurrence (w is the RAW decay input; the op applies exp(-exp(w)) itself):
+ *   S_t = S_{t-1} diag(exp(-exp(w_t))) + (S_{t-1} a_t) b_t^T + v_t k_t^T ,   y_t = S_t r_t
+ */
+#ifndef WKV7_SM100_H
+#define WKV7_SM100_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WKV7_BF16 0
+#define WKV7_F32 1
+
+#define WKV7_OK 0
+#define WKV7_ERR_SHAPE (-1)          /* negative or inconsistent dimensions */
+#define WKV7_ERR_HEAD_SIZE (-2)      /* only N == 64 is built */
+#define WKV7_ERR_CHUNK (-3)          /* T is not a multiple of 16 */
+#define WKV7_ERR_ALIGN (-4)          /* a pointer or stride breaks 16-byte row alignment */
+#define WKV7_ERR_DTYPE (-5)
+#define WKV7_ERR_NULL (-6)           /* a required pointer is null */
+#define WKV7_ERR_LAUNCH (-7)         /* the CUDA launch failed */
+#define WKV7_ERR_TOO_LARGE (-8)
+#define WKV7_ERR_DEVICE_TIMEOUT (-9) /* reported by wkv7_device_status() */
+
+/* Human-readable text for a status code (host pointer, static storage). */
+const char* wkv7_status_string(int status);
+
+/* Bytes of checkpoint buffer the forward writes for the backward: B*H*(T/16)*N*N*4. */
+int64_t wkv7_checkpoint_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
+
+/* Reads and clears the device-side status word of the current device (synchronises the
+ * device).  Kernels bound every wait; one that gave up leaves WKV7_ERR_DEVICE_TIMEOUT here. */
+int wkv7_device_status(void);
+
+/*
+ * WKV7 forward.  Replaces cuda_forward / forward_kernel of the reference
+ * (wind_rwkv/rwkv7/attn.cpp:8-13, attn.cu:11-128) behind th.ops.wind.forward
+ * (rwkv7_attn.py:5-11).  s0 may be null (zero initial state), sT may be null (final state not
+ * wanted), ckpt may be null (no backward will follow).
+ */
+int wkv7_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+             const float* s0, void* y, float* sT, float* ckpt,
+             int64_t B, int64_t T, int64_t H, int64_t N,
+             int64_t stride_b, int64_t stride_t, int64_t stride_h, int io_dtype, void* stream);
+
+/*
+ * WKV7 backward.  Replaces cuda_backward / backward_kernel of the reference
+ * (attn.cpp:15-22, attn.cu:131-348) behind th.ops.wind.backward (rwkv7_attn.py:13-16).
+ * ckpt is what wkv7_fwd wrote.  dsT may be null (zero); when dsT is given, sT (the forward's
+ * final state) is required.  ds0 may be null.  Gradients use the same strides as the inputs.
+ */
+int wkv7_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+             const void* dy, const float* ckpt, const float* dsT, const float* sT,
+             void* dr, void* dw, void* dk, void* dv, void* da, void* db, float* ds0,
+             int64_t B, int64_t T, int64_t H, int64_t N,
+             int64_t stride_b, int64_t stride_t, int64_t stride_h, int io_dtype, void* stream);
+
+/*
+ * Fused WKV7 + per-head GroupNorm (eps) + bonus term + output gate, forward.  Replaces the
+ * attn_ln variant (wind_rwkv/rwkv7/attn_ln.cpp:10-13, attn_ln.cu:106-234; Python side
+ * rwkv7_attn_ln.py:5-11).  params: fp32 [3, H*N] = (GroupNorm weight, GroupNorm bias, bonus).
+ *   y = (GroupNorm_head(S_t r_t) + (sum_j r_j k_j bonus_j) v) * g
+ */
+int wkv7_attn_ln_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+                     const void* g, const float* params, const float* s0, void* y, float* sT, float* ckpt,
+                     float eps, int64_t B, int64_t T, int64_t H, int64_t N,
+                     int64_t stride_b, int64_t stride_t, int64_t stride_h, int io_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WKV7_SM100_H */

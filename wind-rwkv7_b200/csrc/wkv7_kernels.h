@@ -1,0 +1,36 @@
+// Internal launcher interface between the C ABI (capi.cu) and the kernel translation units.
+#pragma once
+#include "wkv7_common.cuh"
+
+namespace wkv7 {
+
+struct FwdParams {
+    const void *r, *w, *k, *v, *a, *b;  // [B,T,H,N], io dtype
+    const void* g;                      // attn_ln only
+    const float* params;                // attn_ln only: [3, H*N] = ln_weight, ln_bias, bonus
+    const float* s0;                    // [B,H,N,N] or null (zeros)
+    void* y;                            // [B,T,H,N]
+    float* sT;                          // [B,H,N,N] or null
+    float* ckpt;                        // [B,H,T/16,N,N] chunk-start states, or null
+    long long B, T, H;
+    Strides st;
+    float eps;
+    int* status;                        // device status word
+};
+
+struct BwdParams {
+    const void *r, *w, *k, *v, *a, *b, *dy;
+    const float* ckpt;   // written by the forward
+    const float* dsT;    // [B,H,N,N] or null (zeros)
+    const float* sT;     // final state of the forward; needed only when dsT is given
+    void *dr, *dw, *dk, *dv, *da, *db;
+    float* ds0;          // or null
+    long long B, T, H;
+    Strides st;
+    int* status;
+};
+
+int launch_fwd(const FwdParams& p, int io_dtype, bool ln, cudaStream_t stream);
+int launch_bwd(const BwdParams& p, int io_dtype, cudaStream_t stream);
+
+}  // namespace wkv7

@@ -1,0 +1,88 @@
+"""ctypes binding of libwkv7_sm100.so (C ABI declared in include/wkv7_sm100.h).
+
+There is no fallback: if the library cannot be loaded, or a call returns a non-zero
+status, a RuntimeError is raised.
+"""
+import ctypes
+import os
+
+import torch as th
+
+_PKG_ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+LIB_PATH = os.path.join(_PKG_ROOT, 'lib', 'libwkv7_sm100.so')
+
+WKV7_BF16, WKV7_F32 = 0, 1
+HEAD_SIZE = 64
+CHUNK = 16
+
+_lib = None
+
+_vp, _i64, _int, _f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
+
+_SIGNATURES = {
+    'wkv7_status_string': (ctypes.c_char_p, [_int]),
+    'wkv7_checkpoint_bytes': (_i64, [_i64] * 4),
+    'wkv7_device_status': (_int, []),
+    'wkv7_fwd': (_int, [_vp] * 10 + [_i64] * 7 + [_int, _vp]),
+    'wkv7_bwd': (_int, [_vp] * 17 + [_i64] * 7 + [_int, _vp]),
+    'wkv7_attn_ln_fwd': (_int, [_vp] * 12 + [_f32] + [_i64] * 7 + [_int, _vp]),
+}
+
+
+def exported_symbols():
+    """Names the header declares; used by the symbol-presence test."""
+    return list(_SIGNATURES)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f'{LIB_PATH} is missing: build it with `python wind-rwkv7_b200/build.py` '
+                '(needs nvcc; there is no CPU or PyTorch fallback for these ops)')
+        L = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            f = getattr(L, name)
+            f.restype, f.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+def check(status, what):
+    if status != 0:
+        msg = lib().wkv7_status_string(status).decode()
+        raise RuntimeError(f'{what} failed: {msg} (status {status})')
+
+
+def io_dtype(t):
+    if t.dtype == th.bfloat16:
+        return WKV7_BF16
+    if t.dtype == th.float32:
+        return WKV7_F32
+    raise TypeError(f'wkv7 ops take bfloat16 or float32 tensors, got {t.dtype}')
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def stream_of(t):
+    return th.cuda.current_stream(t.device).cuda_stream
+
+
+def require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError('wkv7 ops run on CUDA tensors only (sm_100a); there is no CPU path')
+
+
+def strides4(x):
+    """Element strides (b, t, h) of a [B,T,H,N] view with unit inner stride."""
+    assert x.dim() == 4 and x.stride(3) == 1, 'inner dimension must be contiguous'
+    return x.stride(0), x.stride(1), x.stride(2)
+
+
+def device_status():
+    """Reads and clears the device status word (synchronises)."""
+    return lib().wkv7_device_status()

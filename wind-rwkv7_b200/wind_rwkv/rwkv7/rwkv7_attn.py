@@ -1,0 +1,114 @@
+"""WKV7 attention: drop-in for wind_rwkv/rwkv7/rwkv7_attn.py of johanwind/wind-rwkv7.
+
+Same entry points and argument order (`load_attn(HEAD_SIZE)`, `attn(r,w,k,v,a,b,HEAD_SIZE)`,
+`WindRWKV7.apply(w,q,k,v,a,b,s0) -> (y, sT, s)`); the work is done by the sm_100a kernels of
+libwkv7_sm100.so.  Differences, all additive: states and chunk checkpoints are fp32 (upstream:
+bf16), float32 tensors are accepted as well as bfloat16, `attn` takes keyword-only `s0` and
+`return_state`, and launches go to the current stream.
+"""
+import torch as th
+
+from . import _lib
+
+
+def _same_layout(ts):
+    s = ts[0].stride()
+    return all(t.stride() == s and t.stride(3) == 1 for t in ts)
+
+
+def fw_attn(w, q, k, v, a, b, s0):
+    """Forward launcher (upstream: rwkv7_attn.py:5-11). Returns y, sT (fp32), s (fp32 checkpoints)."""
+    B, T, H, C = w.shape
+    _lib.require_cuda(w, q, k, v, a, b, s0)
+    if not _same_layout([w, q, k, v, a, b]):
+        w, q, k, v, a, b = [i.contiguous() for i in (w, q, k, v, a, b)]
+    y = th.empty_like(v)
+    if y.stride() != v.stride():
+        y = th.empty_strided(v.shape, v.stride(), dtype=v.dtype, device=v.device)
+    sT = th.empty(B, H, C, C, dtype=th.float32, device=w.device)
+    s = th.empty(B, H, T // _lib.CHUNK, C, C, dtype=th.float32, device=w.device)
+    sb, st, sh = _lib.strides4(w)
+    rc = _lib.lib().wkv7_fwd(q.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
+                             _lib.ptr(s0), y.data_ptr(), sT.data_ptr(), s.data_ptr(),
+                             B, T, H, C, sb, st, sh, _lib.io_dtype(w), _lib.stream_of(w))
+    _lib.check(rc, 'wkv7_fwd')
+    return y, sT, s
+
+
+def bw_attn(w, q, k, v, a, b, s, dy, dsT, sT):
+    """Backward launcher (upstream: rwkv7_attn.py:13-16)."""
+    B, T, H, C = w.shape
+    if not _same_layout([w, q, k, v, a, b, dy]):
+        w, q, k, v, a, b, dy = [i.contiguous() for i in (w, q, k, v, a, b, dy)]
+    dw, dq, dk, dv, da, db = [th.empty_strided(w.shape, w.stride(), dtype=w.dtype, device=w.device) for _ in range(6)]
+    ds0 = th.empty(B, H, C, C, dtype=th.float32, device=w.device)
+    sb, st, sh = _lib.strides4(w)
+    rc = _lib.lib().wkv7_bwd(q.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
+                             dy.data_ptr(), s.data_ptr(), _lib.ptr(dsT), _lib.ptr(sT if dsT is not None else None),
+                             dq.data_ptr(), dw.data_ptr(), dk.data_ptr(), dv.data_ptr(), da.data_ptr(), db.data_ptr(),
+                             ds0.data_ptr(), B, T, H, C, sb, st, sh, _lib.io_dtype(w), _lib.stream_of(w))
+    _lib.check(rc, 'wkv7_bwd')
+    return dw, dq, dk, dv, da, db, ds0
+
+
+def _check_inputs(w, q, k, v, a, b, s0):
+    B, T, H, C = w.shape
+    assert T % _lib.CHUNK == 0, 'T must be a multiple of 16'
+    assert C == _lib.HEAD_SIZE, 'only head size 64 is built'
+    assert all(i.dtype == w.dtype for i in [q, k, v, a, b]), 'r,w,k,v,a,b must share one dtype'
+    assert all(i.shape == w.shape for i in [q, k, v, a, b])
+    if s0 is not None:
+        assert list(s0.shape) == [B, H, C, C]
+
+
+class WindRWKV7(th.autograd.Function):
+    """(w,q,k,v,a,b,s0) -> (y, sT, s), as upstream's autograd function (rwkv7_attn.py:18-44).
+
+    s0 may be None (zeros), fp32, or bf16 (converted); sT and ds0 are fp32 unless s0 was bf16.
+    """
+
+    @staticmethod
+    def forward(ctx, w, q, k, v, a, b, s0):
+        _check_inputs(w, q, k, v, a, b, s0)
+        s0f = None if s0 is None else s0.float().contiguous()
+        y, sT, s = fw_attn(w, q, k, v, a, b, s0f)
+        ctx.save_for_backward(w, q, k, v, a, b, s, sT)
+        ctx.s0_dtype = None if s0 is None else s0.dtype
+        ctx.mark_non_differentiable(s)
+        ctx.set_materialize_grads(False)
+        if s0 is not None and s0.dtype != th.float32:
+            return y, sT.to(s0.dtype), s
+        return y, sT, s
+
+    @staticmethod
+    def backward(ctx, dy, dsT, ds):
+        w, q, k, v, a, b, s, sT = ctx.saved_tensors
+        assert ds is None
+        if dy is None:
+            dy = th.zeros_like(v)
+        if dsT is not None:
+            dsT = dsT.float().contiguous()
+        dw, dq, dk, dv, da, db, ds0 = bw_attn(w, q, k, v, a, b, s, dy, dsT, sT)
+        if ctx.s0_dtype is None:
+            ds0 = None
+        elif ctx.s0_dtype != th.float32:
+            ds0 = ds0.to(ctx.s0_dtype)
+        return dw, dq, dk, dv, da, db, ds0
+
+
+def load_attn(HEAD_SIZE):
+    """Upstream JIT-compiles its extension here (rwkv7_attn.py:46-51); this loads the prebuilt library."""
+    if HEAD_SIZE != _lib.HEAD_SIZE:
+        raise ValueError(f'only HEAD_SIZE == {_lib.HEAD_SIZE} is built, got {HEAD_SIZE}')
+    _lib.lib()
+
+
+def attn(r, w, k, v, a, b, HEAD_SIZE, *, s0=None, return_state=False):
+    """y = WKV7(r,w,k,v,a,b) for [B,T,H*HEAD_SIZE] tensors (upstream: rwkv7_attn.py:53-59)."""
+    B, T, HC = w.shape
+    C = HEAD_SIZE
+    H = HC // C
+    r, w, k, v, a, b = [i.view(B, T, H, C) for i in [r, w, k, v, a, b]]
+    y, sT, _ = WindRWKV7.apply(w, r, k, v, a, b, s0)
+    y = y.view(B, T, HC)
+    return (y, sT) if return_state else y
