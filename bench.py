@@ -1,0 +1,291 @@
+"""Benchmark of the WKV7 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload: WKV7 forward+backward at the 124M shape (B=64 per GPU, T=1024, H=12, N=64, bf16 inputs,
+fp32 state), seeded synthetic inputs with the value distributions of the workload definition.  A
+step is one forward and one backward over the device-resident batch.  With N > 1 (launched under
+torchrun, one rank per GPU) every rank processes its own batch shard; chains are independent, so
+there is no collective on the data path ("weak" scaling) and NCCL is used only to take the maximum
+time over ranks.  One JSON line is printed by rank 0.
+
+`--impl reference` times the reference's own CPU implementation of the path — the naive per-step
+recurrence, restated in oracle/wkv7_ref.py, forward + autograd backward — on the host cores, on a
+bounded batch slice of the same workload.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path[:0] = [os.path.join(ROOT, 'wind-rwkv7_b200')]
+
+import torch as th  # noqa: E402
+
+METRIC = 'WKV7 fwd+bwd Mtokens/s per GPU at H12 N64 T1024 bf16; % of HBM/TC roofline'
+B_PER_GPU, T, H, N = 64, 1024, 12, 64
+FWD_BYTES_PER_TOKEN_HEAD = 7 * N * 2    # r,w,k,v,a,b in + y out, bf16
+BWD_BYTES_PER_TOKEN_HEAD = 13 * N * 2   # r,w,k,v,a,b,dy in + six gradients out, bf16
+# Fallback copy of the pool's measured STREAM-style bandwidth, used when MEASURED_PEAKS.json is absent.
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one backward launch at this workload, from the
+# ncu capture summarised under profiles/ (null until captured).
+BWD_DRAM_TRAFFIC_BYTES = None
+
+
+def hbm_peak():
+    p = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(p):
+        return float(json.load(open(p))['hbm_gbs']), 'measured'
+    return FALLBACK_HBM_GBS, 'fallback'
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons (NVML) while the timed region runs."""
+
+    def __init__(self, device):
+        self.device, self.samples, self.stop, self.thread = device, [], False, None
+
+    def _run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            try:
+                uuid = 'GPU-' + str(th.cuda.get_device_properties(self.device).uuid)
+                h = nv.nvmlDeviceGetHandleByUUID(uuid)
+            except Exception:
+                h = nv.nvmlDeviceGetHandleByIndex(self.device)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            while not self.stop:
+                mhz = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                try:
+                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:
+                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.samples.append((mhz, reasons))
+                time.sleep(0.002)
+        except Exception as e:  # no NVML: report it rather than guess
+            self.error = repr(e)
+
+    def __enter__(self):
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+        time.sleep(0.05)
+        self.samples.clear()
+        return self
+
+    def __exit__(self, *a):
+        self.stop = True
+        self.thread.join(timeout=10)
+
+    def summary(self):
+        if not self.samples:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['unsampled: ' + getattr(self, 'error', 'no samples')]}
+        mhz = sorted(s[0] for s in self.samples)
+        bits = {'hw_slowdown': 0x8, 'sw_power_cap': 0x4, 'sw_thermal_slowdown': 0x20, 'hw_thermal_slowdown': 0x40}
+        reasons = [n for n, b in bits.items() if any(s[1] & b for s in self.samples)]
+        return {'sm_mhz': mhz[len(mhz) // 2], 'sm_max_mhz': self.max_mhz, 'reasons': reasons, 'samples': len(mhz)}
+
+
+def shard_of(rank, world, total):
+    """Contiguous batch shard [lo, hi) of `total` items for `rank` (used by the sharded tests)."""
+    per, rem = divmod(total, world)
+    lo = rank * per + min(rank, rem)
+    return lo, lo + per + (1 if rank < rem else 0)
+
+
+def max_over_ranks(ms, dist, device):
+    t = th.tensor([ms], dtype=th.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def cpu_reference_run(sample_B, steps, warmup):
+    """The reference's CPU recurrence (restated in oracle/wkv7_ref.py) on a batch slice, fwd+bwd."""
+    sys.path.insert(0, os.path.join(ROOT, 'oracle'))
+    import wkv7_ref
+    from wind_rwkv.rwkv7 import synthetic
+    d = synthetic.wkv7_inputs(sample_B, T, H, N, seed=1, dtype=th.bfloat16)
+    ins = [d[n].requires_grad_() for n in 'rwkvab']
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        y = wkv7_ref.ref_attn(*ins, N)
+        y.backward(d['dy'])
+        for x in ins:
+            x.grad = None
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    return sample_B * T / sec / 1e6, sec
+
+
+def run_reference(args):
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    sample_B = 4
+    val, sec = cpu_reference_run(sample_B, max(1, min(args.steps, 3)), 1 if args.warmup else 0)
+    cores = th.get_num_threads()
+    line = {
+        'impl': 'reference', 'metric': METRIC, 'value': val, 'unit': 'Mtokens/s', 'n_gpus': args.gpus,
+        'steps': max(1, min(args.steps, 3)), 'warmup': 1 if args.warmup else 0, 'ms_per_step': sec * 1e3,
+        'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': {'workload': f'WKV7 fwd+bwd B{B_PER_GPU} T{T} H{H} N{N} (bounded sample: B={sample_B} of {B_PER_GPU})'},
+        'cpu_baseline': {'value': val, 'unit': 'Mtokens/s', 'cores': cores, 'kind': 'port',
+                         'sample': f'B={sample_B} of {B_PER_GPU}, T={T}, H={H}: torch fp32 per-step recurrence, '
+                                   f'forward + autograd backward, {cores} threads'},
+        'e2e': {'value': val, 'unit': 'Mtokens/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+    }
+    print(json.dumps(line))
+
+
+def run_ours(args):
+    from wind_rwkv.rwkv7 import _lib, attn, synthetic
+    from wind_rwkv.rwkv7.rwkv7_attn import bw_attn, fw_attn
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    assert th.cuda.is_available(), 'bench.py measures the CUDA path; there is no CPU fallback'
+    th.cuda.set_device(local)
+    dev = th.device('cuda', local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group('nccl', device_id=dev)
+
+    B = args.batch
+    d = synthetic.wkv7_inputs(B, T, H, N, seed=1 + rank, dtype=th.bfloat16, device=dev)
+    w, r, k, v, a, b = [d[n].view(B, T, H, N) for n in 'wrkvab']
+    dy = d['dy'].view(B, T, H, N)
+    ev = lambda: th.cuda.Event(enable_timing=True)
+
+    def step(evs=None):
+        if evs:
+            evs[0].record()
+        y, sT, s = fw_attn(w, r, k, v, a, b, None)
+        if evs:
+            evs[1].record()
+        g = bw_attn(w, r, k, v, a, b, s, dy, None, sT)
+        if evs:
+            evs[2].record()
+        return y, g
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    th.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    th.cuda.synchronize()
+    evs = [[ev(), ev(), ev()] for _ in range(args.steps)]
+    t_start, t_end = ev(), ev()
+    with ClockSampler(local) as clocks:
+        t_start.record()
+        for i in range(args.steps):
+            step(evs[i])
+        t_end.record()
+        th.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    th.cuda.synchronize()
+    total_ms = t_start.elapsed_time(t_end)
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
+    if dist:
+        total_ms = max_over_ranks(total_ms, dist, dev)
+    ms_per_step = total_ms / args.steps
+    value = world * B * T / (ms_per_step * 1e-3) / 1e6
+
+    # end to end through the public API with host buffers: H2D of r,w,k,v,a,b,dy from pinned memory,
+    # attn() forward + autograd backward, D2H of y and the six gradients.
+    host_in = {n: d[n].cpu().pin_memory() for n in list('rwkvab') + ['dy']}
+    host_out = [th.empty(B, T, H * N, dtype=th.bfloat16).pin_memory() for _ in range(7)]
+
+    def e2e_step():
+        ins = [host_in[n].to(dev, non_blocking=True).requires_grad_() for n in 'rwkvab']
+        gy = host_in['dy'].to(dev, non_blocking=True)
+        y = attn(*ins, N)
+        y.backward(gy)
+        for dst, src in zip(host_out, [y.detach()] + [x.grad for x in ins]):
+            dst.copy_(src, non_blocking=True)
+
+    e2e_steps = 0 if args.no_e2e else max(2, min(args.steps, 5))
+    for _ in range(2 if e2e_steps else 0):
+        e2e_step()
+    th.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    e0, e1 = ev(), ev()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    th.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) if e2e_steps else float('inf')
+    if dist:
+        e2e_ms = max_over_ranks(e2e_ms, dist, dev)
+    e2e_value = world * B * T / (e2e_ms / max(e2e_steps, 1) * 1e-3) / 1e6
+    nbytes = B * T * H * N * 2
+    status = _lib.device_status()
+
+    if rank == 0:
+        peak, which = hbm_peak()
+        bwd_bytes = B * T * H * BWD_BYTES_PER_TOKEN_HEAD
+        fwd_bytes = B * T * H * FWD_BYTES_PER_TOKEN_HEAD
+        achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
+        line = {
+            'metric': METRIC, 'value': value, 'unit': 'Mtokens/s', 'n_gpus': world, 'steps': args.steps,
+            'warmup': max(args.warmup, 3), 'ms_per_step': ms_per_step, 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
+            'config': {'workload': f'WKV7 fwd+bwd B{B} per GPU T{T} H{H} N{N}, bf16 in/out, fp32 state (config 1)',
+                       'global_batch': world * B, 'parallelism': f'batch-sharded x{world}, no collective',
+                       'l2': 'inputs (7 x 100 MB) and outputs exceed the 126 MB L2; no explicit flush',
+                       'precision': 'single-TF32 tensor-core products, fp32 accumulate'},
+            'roofline': {'bound': 'hbm', 'kernel': 'wkv7_bwd_kernel', 'achieved': achieved, 'peak': peak,
+                         'unit': 'GB/s', 'frac': achieved / peak, 'peak_source': which,
+                         'traffic': BWD_DRAM_TRAFFIC_BYTES, 'algorithmic_bytes': bwd_bytes,
+                         'kernel_ms': bwd_ms,
+                         'fwd': {'kernel': 'wkv7_fwd_kernel', 'kernel_ms': fwd_ms, 'algorithmic_bytes': fwd_bytes,
+                                 'achieved': fwd_bytes / (fwd_ms * 1e-3) / 1e9,
+                                 'frac': fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak},
+                         'step_frac': (fwd_bytes + bwd_bytes) / (ms_per_step * 1e-3) / 1e9 / peak},
+            'e2e': {'value': e2e_value, 'unit': 'Mtokens/s', 'h2d_bytes_per_step': 7 * nbytes,
+                    'd2h_bytes_per_step': 7 * nbytes, 'steps': e2e_steps},
+            'gpu_launches': 2 * args.steps,
+            'clocks': clocks.summary(),
+            'device_status': status,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            sample_B = 4
+            val, sec = cpu_reference_run(sample_B, 2, 1)
+            line['cpu_baseline'] = {
+                'value': val, 'unit': 'Mtokens/s', 'cores': th.get_num_threads(), 'kind': 'port',
+                'sample': f'B={sample_B} of {B}, T={T}, H={H}: torch fp32 per-step recurrence (the reference\'s '
+                          f'ref_attn restated), forward + autograd backward, {sec:.1f} s per pass (1 warm-up + 2 timed)'}
+        print(json.dumps(line))
+    if dist:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=50)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer leg (profiling runs)')
+    ap.add_argument('--batch', type=int, default=B_PER_GPU, help='batch per GPU (default: the benchmark shape)')
+    args = ap.parse_args()
+    if args.impl == 'reference':
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == '__main__':
+    main()

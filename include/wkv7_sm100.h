@@ -16,7 +16,8 @@
  *   aligned.  States s0, sT, dsT, ds0: fp32 [B, H, N, N] contiguous, S[value][key].
  *   Checkpoints: fp32 [B, H, T/16, N, N] contiguous (state at the start of every 16-step chunk).
  *   io_dtype: WKV7_BF16 (bf16 tensors, single-TF32 tensor-core products, fp32 state) or
- *   WKV7_F32 (fp32 tensors, 3xTF32 split products).
+ *   WKV7_F32 (fp32 tensors, 3xTF32 split products), or WKV7_F32_TF32 (fp32 tensors, single-TF32
+ *   products: what the bf16 path computes, observable without bf16 output rounding).
  *
  * Recurrence (w is the RAW decay input; the op applies exp(-exp(w)) itself):
  *   S_t = S_{t-1} diag(exp(-exp(w_t))) + (S_{t-1} a_t) b_t^T + v_t k_t^T ,   y_t = S_t r_t
@@ -32,6 +33,7 @@ extern "C" {
 
 #define WKV7_BF16 0
 #define WKV7_F32 1
+#define WKV7_F32_TF32 2 /* fp32 tensors, single-TF32 products: the bf16 path's arithmetic without output rounding */
 
 #define WKV7_OK 0
 #define WKV7_ERR_SHAPE (-1)          /* negative or inconsistent dimensions */

@@ -61,7 +61,7 @@ def test_state_carry_matches_one_long_call(golden):
 def test_c_oracle_state_gradients_match_autograd():
     th.manual_seed(3)
     B, T, H, N = 1, 48, 2, 64
-    import synthetic
+    from wind_rwkv.rwkv7 import synthetic
     d = synthetic.wkv7_inputs(B, T, H, N, seed=11, dtype=th.float64, s0_std=0.1)
     ins = [d[n].double().requires_grad_() for n in NAMES]
     s0 = d['s0'].double().requires_grad_()

@@ -19,7 +19,7 @@ int check_common(int64_t B, int64_t T, int64_t H, int64_t N, int64_t sb, int64_t
     if (B < 0 || T < 0 || H < 0 || N <= 0) return wkv7::kBadShape;
     if (N != wkv7::N) return wkv7::kBadHeadSize;
     if (T % wkv7::L != 0) return wkv7::kBadChunk;
-    if (io_dtype != WKV7_BF16 && io_dtype != WKV7_F32) return wkv7::kBadDtype;
+    if (io_dtype != WKV7_BF16 && io_dtype != WKV7_F32 && io_dtype != WKV7_F32_TF32) return wkv7::kBadDtype;
     const int64_t per16 = io_dtype == WKV7_BF16 ? 8 : 4;  // elements per 16 bytes
     if (sb % per16 || st % per16 || sh % per16) return wkv7::kBadAlign;
     if (sb < 0 || st < 0 || sh < 0) return wkv7::kBadShape;

@@ -522,6 +522,7 @@ template <typename IoT, int PREC> static int launch_bwd_t(const BwdParams& p, cu
 
 int launch_bwd(const BwdParams& p, int io_dtype, cudaStream_t stream) {
     if (io_dtype == 0) return launch_bwd_t<__nv_bfloat16, 1>(p, stream);
+    if (io_dtype == 2) return launch_bwd_t<float, 1>(p, stream);
     return launch_bwd_t<float, 3>(p, stream);
 }
 

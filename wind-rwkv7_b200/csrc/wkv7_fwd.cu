@@ -370,6 +370,7 @@ template <typename IoT, int PREC, bool LN> static int launch_fwd_t(const FwdPara
 
 int launch_fwd(const FwdParams& p, int io_dtype, bool ln, cudaStream_t stream) {
     if (io_dtype == 0) return ln ? launch_fwd_t<__nv_bfloat16, 1, true>(p, stream) : launch_fwd_t<__nv_bfloat16, 1, false>(p, stream);
+    if (io_dtype == 2) return ln ? launch_fwd_t<float, 1, true>(p, stream) : launch_fwd_t<float, 1, false>(p, stream);
     return ln ? launch_fwd_t<float, 3, true>(p, stream) : launch_fwd_t<float, 3, false>(p, stream);
 }
 
