@@ -90,6 +90,23 @@ int wkv7_attn_ln_fwd(const void* r, const void* w, const void* k, const void* v,
                      float eps, int64_t B, int64_t T, int64_t H, int64_t N,
                      int64_t stride_b, int64_t stride_t, int64_t stride_h, int io_dtype, void* stream);
 
+/* Bytes of workspace wkv7_attn_ln_bwd needs: B*3*H*N*4 (per-batch partial parameter gradients). */
+int64_t wkv7_attn_ln_bwd_workspace_bytes(int64_t B, int64_t H, int64_t N);
+
+/*
+ * Backward of the fused attn_ln op.  Replaces the attn_ln cuda_backward / backward_kernel
+ * (wind_rwkv/rwkv7/attn_ln.cpp:15-22, attn_ln.cu:237-486; Python side rwkv7_attn_ln.py:13-17).
+ * dy is the gradient of the fused output.  dparams: fp32 [3, H*N], overwritten (the reference
+ * accumulates into a zero-filled buffer with atomics; here per-batch partials go to `workspace`
+ * and are summed in a fixed order, so the result is deterministic).  Other arguments as wkv7_bwd.
+ */
+int wkv7_attn_ln_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+                     const void* g, const float* params, const void* dy, const float* ckpt, const float* dsT,
+                     const float* sT, void* dr, void* dw, void* dk, void* dv, void* da, void* db, void* dg,
+                     float* dparams, float* workspace, float* ds0, float eps,
+                     int64_t B, int64_t T, int64_t H, int64_t N,
+                     int64_t stride_b, int64_t stride_t, int64_t stride_h, int io_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -105,14 +105,19 @@ int wkv7_attn_ln_fwd(const void* r, const void* w, const void* k, const void* v,
                       stride_h, io_dtype, stream);
 }
 
-int wkv7_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
-             const void* dy, const float* ckpt, const float* dsT, const float* sT, void* dr, void* dw, void* dk,
-             void* dv, void* da, void* db, float* ds0, int64_t B, int64_t T, int64_t H, int64_t N, int64_t stride_b,
-             int64_t stride_t, int64_t stride_h, int io_dtype, void* stream) {
+static int bwd_common(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+                      const void* g, const float* params, bool ln, float eps, const void* dy, const float* ckpt,
+                      const float* dsT, const float* sT, void* dr, void* dw, void* dk, void* dv, void* da, void* db,
+                      void* dg, float* dparams, float* dparams_ws, float* ds0, int64_t B, int64_t T, int64_t H, int64_t N,
+                      int64_t stride_b, int64_t stride_t, int64_t stride_h, int io_dtype, void* stream) {
     int rc = check_common(B, T, H, N, stride_b, stride_t, stride_h, io_dtype);
     if (rc) return rc;
     if (B == 0 || H == 0) return WKV7_OK;
     if (T == 0) {
+        if (ln && dparams) {
+            if (cudaMemsetAsync(dparams, 0, (size_t)3 * H * N * sizeof(float), (cudaStream_t)stream) != cudaSuccess)
+                return WKV7_ERR_LAUNCH;
+        }
         if (ds0) {
             size_t bytes = (size_t)B * H * N * N * sizeof(float);
             cudaError_t e = dsT ? cudaMemcpyAsync(ds0, dsT, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream)
@@ -123,18 +128,42 @@ int wkv7_bwd(const void* r, const void* w, const void* k, const void* v, const v
     }
     if (!r || !w || !k || !v || !a || !b || !dy || !ckpt || !dr || !dw || !dk || !dv || !da || !db) return WKV7_ERR_NULL;
     if (dsT && !sT) return WKV7_ERR_NULL;
-    const void* ptrs[] = {r, w, k, v, a, b, dy, ckpt, dsT, sT, dr, dw, dk, dv, da, db, ds0};
+    if (ln && (!g || !params || !dg || !dparams || !dparams_ws)) return WKV7_ERR_NULL;
+    const void* ptrs[] = {r, w, k, v, a, b, dy, ckpt, dsT, sT, dr, dw, dk, dv, da, db, ds0, g, params, dg, dparams, dparams_ws};
     for (const void* p : ptrs)
         if (p && !aligned16(p)) return WKV7_ERR_ALIGN;
     wkv7::BwdParams p{};
     p.r = r; p.w = w; p.k = k; p.v = v; p.a = a; p.b = b; p.dy = dy;
     p.ckpt = ckpt; p.dsT = dsT; p.sT = sT;
+    p.g = g; p.params = params; p.dg = dg; p.dparams = dparams; p.dparams_ws = dparams_ws; p.eps = eps;
     p.dr = dr; p.dw = dw; p.dk = dk; p.dv = dv; p.da = da; p.db = db; p.ds0 = ds0;
     p.B = B; p.T = T; p.H = H;
     p.st = wkv7::Strides{stride_b, stride_t, stride_h};
     p.status = status_ptr();
     if (!p.status) return WKV7_ERR_LAUNCH;
-    return wkv7::launch_bwd(p, io_dtype, (cudaStream_t)stream);
+    return wkv7::launch_bwd(p, io_dtype, ln, (cudaStream_t)stream);
+}
+
+int wkv7_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+             const void* dy, const float* ckpt, const float* dsT, const float* sT, void* dr, void* dw, void* dk,
+             void* dv, void* da, void* db, float* ds0, int64_t B, int64_t T, int64_t H, int64_t N, int64_t stride_b,
+             int64_t stride_t, int64_t stride_h, int io_dtype, void* stream) {
+    return bwd_common(r, w, k, v, a, b, nullptr, nullptr, false, 0.f, dy, ckpt, dsT, sT, dr, dw, dk, dv, da, db, nullptr,
+                      nullptr, nullptr, ds0, B, T, H, N, stride_b, stride_t, stride_h, io_dtype, stream);
+}
+
+int64_t wkv7_attn_ln_bwd_workspace_bytes(int64_t B, int64_t H, int64_t N) {
+    if (B < 0 || H < 0 || N < 0) return 0;
+    return B * 3 * H * N * (int64_t)sizeof(float);
+}
+
+int wkv7_attn_ln_bwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+                     const void* g, const float* params, const void* dy, const float* ckpt, const float* dsT,
+                     const float* sT, void* dr, void* dw, void* dk, void* dv, void* da, void* db, void* dg,
+                     float* dparams, float* workspace, float* ds0, float eps, int64_t B, int64_t T, int64_t H,
+                     int64_t N, int64_t stride_b, int64_t stride_t, int64_t stride_h, int io_dtype, void* stream) {
+    return bwd_common(r, w, k, v, a, b, g, params, true, eps, dy, ckpt, dsT, sT, dr, dw, dk, dv, da, db, dg, dparams,
+                      workspace, ds0, B, T, H, N, stride_b, stride_t, stride_h, io_dtype, stream);
 }
 
 }  // extern "C"

@@ -18,6 +18,13 @@
 // and dlogdecay_k = sum_{t>=k} d/dc_t; dw = dlogdecay * (-exp(w)).  The last term for chunk c-1
 // equals sum_i dS0_c[i,:] S0_c[i,:], which is formed while chunk c is processed and carried.
 //
+// With LN = true the kernel is the backward of the fused attn_ln op (reference:
+// wind_rwkv/rwkv7/attn_ln.cu:40-104, 237-464): `dy` is then the gradient of the fused output; the
+// chunk's recurrence output Y is rebuilt, the GroupNorm / bonus / gate backward runs on it in the
+// transposed register layout (three cross-warp reductions per time step through shared memory),
+// and its result replaces dY for everything below.  Parameter gradients are accumulated in
+// registers over the whole chain and written as per-(batch, head) partials (no atomics).
+//
 // Stage B (rows = value index, per warp, no cross-warp traffic): U^T, du^T, dabu^T, dV^T, dS0.
 // Stage C (contractions over the value index, warp owns 16 key columns): the four score
 // gradients and DA, DQ, DB, DK with S0 and dSf read from shared memory.
@@ -33,22 +40,32 @@ template <typename IoT> struct BwdLayout {
     static constexpr int YS = (sizeof(IoT) == 2) ? 24 : 20;
 };
 
-template <typename IoT> struct BwdSmem {
+template <typename IoT, int PREC, bool LN> struct BwdSmem {
     using Lay = BwdLayout<IoT>;
     alignas(16) unsigned char st_in[5][Lay::TILEB];  // q, w, k, a, b (dead after the scan)
     alignas(16) unsigned char st_v[2][Lay::TILEB];
     alignas(16) unsigned char st_dy[2][Lay::TILEB];
+    alignas(16) unsigned char st_g[LN ? 2 : 1][LN ? Lay::TILEB : 16];
     alignas(16) float wq[L * OPS], wa[L * OPS], kwi[L * OPS], bwi[L * OPS];
-    alignas(16) float cum[L * OPS], lw[L * OPS];
+    alignas(16) float cum[L * OPS];
+    alignas(16) float lw[PREC == 3 ? L * OPS : 4];   // single-TF32 path derives it from cum
     alignas(16) float QK[L * SCS], QB[L * SCS], AK[L * SCS], AB[L * SCS], AI[L * SCS];
-    alignas(16) float dQK[L * SCS], dQB[L * SCS], dAK[L * SCS], dAB[L * SCS];
+    // Score gradients (stage C).  While stage B runs they are dead, and the same bytes serve as
+    // the per-warp transposition scratch for dv / dg and as the GroupNorm reduction buffers.
+    static constexpr int SCRATCH_FLOATS = WARPS * L * Lay::YS * (int)sizeof(IoT) / 4 + WARPS * L * 5;
+    static constexpr int SGRAD_FLOATS = 4 * L * SCS > SCRATCH_FLOATS ? 4 * L * SCS : SCRATCH_FLOATS;
+    alignas(16) float sgrad[SGRAD_FLOATS];  // score gradient i at sgrad + i * L * SCS
     alignas(16) float Ut[L * OPS], Dt[L * OPS];  // U and dabu as [time][value]
+    alignas(16) float Yt[LN ? L * OPS : 4];      // recurrence-output gradient as [time][value]
     alignas(16) float S0s[N * SS], dSs[N * SS];  // chunk-start state and dSf as [value][key]
     alignas(16) float fw[N];
     alignas(16) float Gp[2][WARPS][N];
-    alignas(16) IoT dvsc[WARPS][L * Lay::YS];
+    alignas(16) float lnp[LN ? 3 * N : 4];
+    float bdot[L], sbon[L];
     alignas(8) uint64_t bar_in, bar_vdy[2], bar_s0;
 };
+static_assert(sizeof(BwdSmem<__nv_bfloat16, 1, false>) <= 115712, "bf16 backward must fit two CTAs per SM");
+static_assert(sizeof(BwdSmem<__nv_bfloat16, 1, true>) <= 115712, "bf16 attn_ln backward must fit two CTAs per SM");
 
 template <typename IoT> __device__ __forceinline__ float bst_elem(const unsigned char* tile, int row, int col) {
     return to_f32<IoT>(*reinterpret_cast<const IoT*>(tile + row * BwdLayout<IoT>::ROWB + col * (int)sizeof(IoT)));
@@ -97,10 +114,10 @@ template <> __device__ __forceinline__ void store_pair<__nv_bfloat16>(__nv_bfloa
     *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(x, y);
 }
 
-template <typename IoT, int PREC>
+template <typename IoT, int PREC, bool LN>
 __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
     using Lay = BwdLayout<IoT>;
-    using Smem = BwdSmem<IoT>;
+    using Smem = BwdSmem<IoT, PREC, LN>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
 
@@ -115,6 +132,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
     const IoT* gdy = (const IoT*)p.dy + base;
     IoT* gout[5] = {(IoT*)p.dr + base, (IoT*)p.dw + base, (IoT*)p.dk + base, (IoT*)p.da + base, (IoT*)p.db + base};
     IoT* gdv = (IoT*)p.dv + base;
+    const IoT* gg = LN ? (const IoT*)p.g + base : nullptr;
+    IoT* gdg = LN ? (IoT*)p.dg + base : nullptr;
     const float* ckpt = p.ckpt + bh * nchunks * (long long)(N * N);
     constexpr uint32_t ROW_BYTES = N * sizeof(IoT);
 
@@ -125,6 +144,14 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
         mbar_init(&sm.bar_s0, 1);
         mbar_fence_init();
     }
+    if (LN) {
+        for (int i = tid; i < 3 * N; i += THREADS) sm.lnp[i] = p.params[(long long)(i / N) * p.H * N + hi * N + (i % N)];
+    }
+    // stage-B scratch aliased onto the score-gradient buffers
+    IoT* const dvsc = reinterpret_cast<IoT*>(sm.sgrad) + warp * (L * Lay::YS);
+    float* const red = sm.sgrad + (WARPS * L * Lay::YS * (int)sizeof(IoT)) / 4;  // [WARPS][L][2]
+    float* const red2 = red + WARPS * L * 2;                                             // [WARPS][L][3]
+    float dlnw_acc[2] = {0.f, 0.f}, dlnb_acc[2] = {0.f, 0.f}, dbon_acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
     // Carried decay term for the last chunk: sum_i dsT[i,:] * sT[i,:] (zero without dsT).
     for (int i = tid; i < WARPS * N; i += THREADS) sm.Gp[1][i / N][i % N] = 0.f;
     __syncthreads();
@@ -146,13 +173,15 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
         }
     };
     auto issue_vdy = [&](int c, int s) {
-        if (lane == 0) mbar_arrive_expect_tx(&sm.bar_vdy[s], 2 * L * ROW_BYTES);
+        if (lane == 0) mbar_arrive_expect_tx(&sm.bar_vdy[s], (LN ? 3 : 2) * L * ROW_BYTES);
         __syncwarp();
         {
             int ten = lane / L, row = lane % L;
             const IoT* src = (ten == 0 ? gv : gdy) + ((long long)c * L + row) * p.st.t;
             unsigned char* dst = (ten == 0 ? sm.st_v[s] : sm.st_dy[s]) + row * Lay::ROWB;
             bulk_g2s(dst, src, ROW_BYTES, &sm.bar_vdy[s]);
+            if (LN && lane < L)
+                bulk_g2s(sm.st_g[LN ? s : 0] + lane * Lay::ROWB, gg + ((long long)c * L + lane) * p.st.t, ROW_BYTES, &sm.bar_vdy[s]);
         }
     };
     auto issue_s0 = [&](int c) {
@@ -206,10 +235,23 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
                 sm.kwi[r * OPS + j] = bst_elem<IoT>(sm.st_in[2], r, j) * inv;
                 sm.bwi[r * OPS + j] = bst_elem<IoT>(sm.st_in[4], r, j) * inv;
                 sm.cum[r * OPS + j] = cum;
-                sm.lw[r * OPS + j] = lw;
+                if (PREC == 3) sm.lw[r * OPS + j] = lw;
                 prev = incl;
             }
             if (half) sm.fw[j] = prev;
+            if (LN) {  // bonus dot  sum_j r_j k_j bonus_j  per time step: 8 threads per row
+                const int row = tid >> 3, part = tid & 7;
+                float acc = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int ch = part * 8 + i;
+                    acc += bst_elem<IoT>(sm.st_in[0], row, ch) * bst_elem<IoT>(sm.st_in[2], row, ch) * sm.lnp[2 * N + ch];
+                }
+                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+                if (part == 0) sm.bdot[row] = acc;
+            }
         }
         if (__syncthreads_or(!ok)) { failed = true; break; }  // (A)
 
@@ -267,26 +309,154 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk) {
             vf[kk] = fragA_km_st<IoT, PREC>(vt, 16 * warp, 8 * kk, g, t4);
-            dyf[kk] = fragA_km_st<IoT, PREC>(dyt, 16 * warp, 8 * kk, g, t4);
+            if (!LN) dyf[kk] = fragA_km_st<IoT, PREC>(dyt, 16 * warp, 8 * kk, g, t4);
         }
         float U[2][4] = {};
+        float dvx[2][4] = {};  // LN: bonus-term contribution to dv
         {
-            float X[2][4] = {};
+            float X[2][4] = {}, Y[2][4] = {};
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
                 FragA<PREC> a = fragA_mk<PREC>(sm.S0s, SS, 16 * warp, 8 * kk, g, t4);
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) mma<PREC>(X[nt], a, fragB_nk<PREC>(sm.wa, OPS, 8 * nt, 8 * kk, g, t4));
+                for (int nt = 0; nt < 2; ++nt) {
+                    mma<PREC>(X[nt], a, fragB_nk<PREC>(sm.wa, OPS, 8 * nt, 8 * kk, g, t4));
+                    if (LN) mma<PREC>(Y[nt], a, fragB_nk<PREC>(sm.wq, OPS, 8 * nt, 8 * kk, g, t4));
+                }
             }
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                for (int kk = 0; kk <= nt; ++kk) mma<PREC>(X[nt], vf[kk], fragB_nk<PREC>(sm.AK, SCS, 8 * nt, 8 * kk, g, t4));
+                for (int kk = 0; kk <= nt; ++kk) {
+                    mma<PREC>(X[nt], vf[kk], fragB_nk<PREC>(sm.AK, SCS, 8 * nt, 8 * kk, g, t4));
+                    if (LN) mma<PREC>(Y[nt], vf[kk], fragB_nk<PREC>(sm.QK, SCS, 8 * nt, 8 * kk, g, t4));
+                }
             FragA<PREC> xa[2] = {fragA_from_acc<PREC>(X[0]), fragA_from_acc<PREC>(X[1])};
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                 for (int kk = 0; kk <= nt; ++kk) mma<PREC>(U[nt], xa[kk], fragB_nk<PREC>(sm.AI, SCS, 8 * nt, 8 * kk, g, t4));
+            if (LN) {
+                // ---- rebuild Y, then GroupNorm / bonus / gate backward in the [value][time] layout ----
+                FragA<PREC> ua0[2] = {fragA_from_acc<PREC>(U[0]), fragA_from_acc<PREC>(U[1])};
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int kk = 0; kk <= nt; ++kk) mma<PREC>(Y[nt], ua0[kk], fragB_nk<PREC>(sm.QB, SCS, 8 * nt, 8 * kk, g, t4));
+                // statistics: per-warp mean and centred sum of squares over 16 rows, merged below
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        float sy = Y[nt][e] + Y[nt][e + 2];
+                        sy += __shfl_xor_sync(0xffffffffu, sy, 4);
+                        sy += __shfl_xor_sync(0xffffffffu, sy, 8);
+                        sy += __shfl_xor_sync(0xffffffffu, sy, 16);
+                        const float mu = sy * (1.f / 16.f);
+                        const float d0 = Y[nt][e] - mu, d1 = Y[nt][e + 2] - mu;
+                        float q2 = d0 * d0 + d1 * d1;
+                        q2 += __shfl_xor_sync(0xffffffffu, q2, 4);
+                        q2 += __shfl_xor_sync(0xffffffffu, q2, 8);
+                        q2 += __shfl_xor_sync(0xffffffffu, q2, 16);
+                        if (g == 0) {
+                            const int tq = 8 * nt + 2 * t4 + e;
+                            red[(warp * L + tq) * 2 + 0] = mu;
+                            red[(warp * L + tq) * 2 + 1] = q2;
+                        }
+                    }
+                __syncthreads();  // (D1)
+                const unsigned char* gt = sm.st_g[LN ? vs : 0];
+                float xh[2][4], dxh[2][4], rstd_t[4];
+#pragma unroll
+                for (int i4 = 0; i4 < 4; ++i4) {
+                    const int nt = i4 >> 1, e = i4 & 1, tq = 8 * nt + 2 * t4 + e;
+                    float mu = 0.f, m2 = 0.f;
+#pragma unroll
+                    for (int w2 = 0; w2 < WARPS; ++w2) mu += red[(w2 * L + tq) * 2];
+                    mu *= 0.25f;
+#pragma unroll
+                    for (int w2 = 0; w2 < WARPS; ++w2) {
+                        const float dm = red[(w2 * L + tq) * 2] - mu;
+                        m2 += red[(w2 * L + tq) * 2 + 1] + 16.f * dm * dm;
+                    }
+                    const float rstd = 1.f / sqrtf(m2 * (1.f / N) + p.eps);
+                    rstd_t[i4] = rstd;
+                    const float bd = sm.bdot[tq];
+                    float a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+                    for (int hrow = 0; hrow < 2; ++hrow) {
+                        const int vc = 16 * warp + g + 8 * hrow, i = e + 2 * hrow;
+                        const float x = (Y[nt][i] - mu) * rstd;
+                        const float ve = bst_elem<IoT>(vt, tq, vc), ge = bst_elem<IoT>(gt, tq, vc), de = bst_elem<IoT>(dyt, tq, vc);
+                        const float z = x * sm.lnp[vc] + sm.lnp[N + vc] + bd * ve;
+                        const float dz = de * ge;
+                        Y[nt][i] = de * z;  // dg, stored below
+                        dlnw_acc[hrow] += dz * x;
+                        dlnb_acc[hrow] += dz;
+                        dvx[nt][i] = dz * bd;
+                        const float dx = dz * sm.lnp[vc];
+                        xh[nt][i] = x;
+                        dxh[nt][i] = dx;
+                        a1 += dx; a2 += dx * x; a3 += dz * ve;
+                    }
+#pragma unroll
+                    for (int m = 4; m <= 16; m <<= 1) {
+                        a1 += __shfl_xor_sync(0xffffffffu, a1, m);
+                        a2 += __shfl_xor_sync(0xffffffffu, a2, m);
+                        a3 += __shfl_xor_sync(0xffffffffu, a3, m);
+                    }
+                    if (g == 0) {
+                        red2[(warp * L + tq) * 3 + 0] = a1;
+                        red2[(warp * L + tq) * 3 + 1] = a2;
+                        red2[(warp * L + tq) * 3 + 2] = a3;
+                    }
+                }
+                // dg out through the per-warp scratch tile
+                {
+                    IoT* sc = dvsc;
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt) {
+                        const int tq = 8 * nt + 2 * t4;
+                        sc[tq * Lay::YS + g] = from_f32<IoT>(Y[nt][0]);
+                        sc[(tq + 1) * Lay::YS + g] = from_f32<IoT>(Y[nt][1]);
+                        sc[tq * Lay::YS + g + 8] = from_f32<IoT>(Y[nt][2]);
+                        sc[(tq + 1) * Lay::YS + g + 8] = from_f32<IoT>(Y[nt][3]);
+                    }
+                    __syncwarp();
+                    const int row = lane >> 1, hf = lane & 1;
+                    const uint4* src = reinterpret_cast<const uint4*>(sc + row * Lay::YS + 8 * hf);
+                    uint4* dst = reinterpret_cast<uint4*>(gdg + ((long long)c * L + row) * p.st.t + 16 * warp + 8 * hf);
+                    dst[0] = src[0];
+                    if (sizeof(IoT) == 4) dst[1] = src[1];
+                    __syncwarp();
+                }
+                __syncthreads();  // (D2)
+#pragma unroll
+                for (int i4 = 0; i4 < 4; ++i4) {
+                    const int nt = i4 >> 1, e = i4 & 1, tq = 8 * nt + 2 * t4 + e;
+                    float m1 = 0.f, m2 = 0.f, sb = 0.f;
+#pragma unroll
+                    for (int w2 = 0; w2 < WARPS; ++w2) {
+                        m1 += red2[(w2 * L + tq) * 3];
+                        m2 += red2[(w2 * L + tq) * 3 + 1];
+                        sb += red2[(w2 * L + tq) * 3 + 2];
+                    }
+                    m1 *= (1.f / N); m2 *= (1.f / N);
+                    if (warp == 0 && g == 0) sm.sbon[tq] = sb;
+#pragma unroll
+                    for (int hrow = 0; hrow < 2; ++hrow) {
+                        const int i = e + 2 * hrow;
+                        Y[nt][i] = rstd_t[i4] * (dxh[nt][i] - m1 - xh[nt][i] * m2);  // gradient of the recurrence output
+                    }
+                }
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    dyf[nt] = fragA_from_acc<PREC>(Y[nt]);
+                    const int tq = 8 * nt + 2 * t4, vc = 16 * warp + g;
+                    sm.Yt[tq * OPS + vc] = Y[nt][0]; sm.Yt[(tq + 1) * OPS + vc] = Y[nt][1];
+                    sm.Yt[tq * OPS + vc + 8] = Y[nt][2]; sm.Yt[(tq + 1) * OPS + vc + 8] = Y[nt][3];
+                }
+            }
         }
         // dS <- dSf = dS * fw
 #pragma unroll
@@ -327,14 +497,14 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
 
         // dv out (transposed through a per-warp scratch tile for 16-byte stores)
         {
-            IoT* sc = sm.dvsc[warp];
+            IoT* sc = dvsc;
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 const int tq = 8 * nt + 2 * t4;
-                sc[tq * Lay::YS + g] = from_f32<IoT>(dV[nt][0]);
-                sc[(tq + 1) * Lay::YS + g] = from_f32<IoT>(dV[nt][1]);
-                sc[tq * Lay::YS + g + 8] = from_f32<IoT>(dV[nt][2]);
-                sc[(tq + 1) * Lay::YS + g + 8] = from_f32<IoT>(dV[nt][3]);
+                sc[tq * Lay::YS + g] = from_f32<IoT>(dV[nt][0] + dvx[nt][0]);
+                sc[(tq + 1) * Lay::YS + g] = from_f32<IoT>(dV[nt][1] + dvx[nt][1]);
+                sc[tq * Lay::YS + g + 8] = from_f32<IoT>(dV[nt][2] + dvx[nt][2]);
+                sc[(tq + 1) * Lay::YS + g + 8] = from_f32<IoT>(dV[nt][3] + dvx[nt][3]);
             }
             __syncwarp();
             const int row = lane >> 1, hf = lane & 1;
@@ -384,11 +554,11 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             // 2 dQB = tril(dY U^T), 3 dAB = stril(dabu U^T)
             float d[2][4] = {};
             const bool strict = warp & 1;
-            float* dst = warp == 0 ? sm.dQK : warp == 1 ? sm.dAK : warp == 2 ? sm.dQB : sm.dAB;
+            float* dst = sm.sgrad + warp * (L * SCS);  // 0 dQK, 1 dAK, 2 dQB, 3 dAB
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
                 FragA<PREC> aD = fragA_mk<PREC>(sm.Dt, OPS, 0, 8 * kk, g, t4);
-                FragA<PREC> aY = fragA_mk_st<IoT, PREC>(dyt, 8 * kk, g, t4);
+                FragA<PREC> aY = LN ? fragA_mk<PREC>(sm.Yt, OPS, 0, 8 * kk, g, t4) : fragA_mk_st<IoT, PREC>(dyt, 8 * kk, g, t4);
                 FragA<PREC> aU = fragA_mk<PREC>(sm.Ut, OPS, 0, 8 * kk, g, t4);
                 FragA<PREC> aV = fragA_mk_st<IoT, PREC>(vt, 8 * kk, g, t4);
 #pragma unroll
@@ -419,10 +589,11 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
 
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk) {
-            FragA<PREC> aAB = fragA_mk<PREC>(sm.dAB, SCS, 0, 8 * kk, g, t4), aAK = fragA_mk<PREC>(sm.dAK, SCS, 0, 8 * kk, g, t4);
-            FragA<PREC> aQB = fragA_mk<PREC>(sm.dQB, SCS, 0, 8 * kk, g, t4), aQK = fragA_mk<PREC>(sm.dQK, SCS, 0, 8 * kk, g, t4);
-            FragA<PREC> tAB = fragA_km<PREC>(sm.dAB, SCS, 0, 8 * kk, g, t4), tAK = fragA_km<PREC>(sm.dAK, SCS, 0, 8 * kk, g, t4);
-            FragA<PREC> tQB = fragA_km<PREC>(sm.dQB, SCS, 0, 8 * kk, g, t4), tQK = fragA_km<PREC>(sm.dQK, SCS, 0, 8 * kk, g, t4);
+            const float *dQK = sm.sgrad, *dAK = sm.sgrad + L * SCS, *dQB = sm.sgrad + 2 * L * SCS, *dAB = sm.sgrad + 3 * L * SCS;
+            FragA<PREC> aAB = fragA_mk<PREC>(dAB, SCS, 0, 8 * kk, g, t4), aAK = fragA_mk<PREC>(dAK, SCS, 0, 8 * kk, g, t4);
+            FragA<PREC> aQB = fragA_mk<PREC>(dQB, SCS, 0, 8 * kk, g, t4), aQK = fragA_mk<PREC>(dQK, SCS, 0, 8 * kk, g, t4);
+            FragA<PREC> tAB = fragA_km<PREC>(dAB, SCS, 0, 8 * kk, g, t4), tAK = fragA_km<PREC>(dAK, SCS, 0, 8 * kk, g, t4);
+            FragA<PREC> tQB = fragA_km<PREC>(dQB, SCS, 0, 8 * kk, g, t4), tQK = fragA_km<PREC>(dQK, SCS, 0, 8 * kk, g, t4);
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 const int n0 = 16 * warp + 8 * nt;
@@ -444,7 +615,13 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             for (int hrow = 0; hrow < 2; ++hrow) {
                 const int tq = g + 8 * hrow;
                 const float2 cu = *reinterpret_cast<const float2*>(sm.cum + tq * OPS + key);
-                const float2 lwp = *reinterpret_cast<const float2*>(sm.lw + tq * OPS + key);
+                float2 lwp;
+                if (PREC == 3) {
+                    lwp = *reinterpret_cast<const float2*>(sm.lw + tq * OPS + key);
+                } else {  // running log-decay difference; row -1 is zero
+                    const float2 cp = tq > 0 ? *reinterpret_cast<const float2*>(sm.cum + (tq - 1) * OPS + key) : make_float2(0.f, 0.f);
+                    lwp = make_float2(cu.x - cp.x, cu.y - cp.y);
+                }
                 const float2 oq = *reinterpret_cast<const float2*>(sm.wq + tq * OPS + key);
                 const float2 oa = *reinterpret_cast<const float2*>(sm.wa + tq * OPS + key);
                 const float2 okw = *reinterpret_cast<const float2*>(sm.kwi + tq * OPS + key);
@@ -460,6 +637,13 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
                     o_q[e] = incl * DQ[nt][i];
                     o_b[e] = inv * DB[nt][i];
                     o_k[e] = inv * DK[nt][i];
+                    if (LN) {  // bonus term: y += (sum_j q_j k_j bonus_j) v
+                        const float sbv = sm.sbon[tq], bo = sm.lnp[2 * N + key + e];
+                        const float q_raw = wqv[e] * inv, k_raw = kwv[e] * incl;
+                        o_q[e] += sbv * k_raw * bo;
+                        o_k[e] += sbv * q_raw * bo;
+                        dbon_acc[nt][e] += sbv * q_raw * k_raw;
+                    }
                     e2[hrow][e] = wav[e] * DA[nt][i];
                     x[hrow][e] = wqv[e] * DQ[nt][i] - kwv[e] * DK[nt][i] - bwv[e] * DB[nt][i] + e2[hrow][e];
                     lwv[hrow][e] = lwa[e];
@@ -500,6 +684,28 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
         if (tid == 0) atomicExch(p.status, (int)kDeviceTimeout);
         return;
     }
+    if (LN) {
+        // per-(batch, head) partial parameter gradients: ws[b][0..2][h*N + channel]
+        float* ws = p.dparams_ws + bi * 3 * p.H * N + hi * N;
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            float a = dlnw_acc[hrow], b2 = dlnb_acc[hrow];
+            a += __shfl_xor_sync(0xffffffffu, a, 1); a += __shfl_xor_sync(0xffffffffu, a, 2);
+            b2 += __shfl_xor_sync(0xffffffffu, b2, 1); b2 += __shfl_xor_sync(0xffffffffu, b2, 2);
+            if (t4 == 0) {
+                ws[16 * warp + g + 8 * hrow] = a;
+                ws[p.H * N + 16 * warp + g + 8 * hrow] = b2;
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float a = dbon_acc[nt][e];
+                a += __shfl_xor_sync(0xffffffffu, a, 4); a += __shfl_xor_sync(0xffffffffu, a, 8); a += __shfl_xor_sync(0xffffffffu, a, 16);
+                if (g == 0) ws[2 * p.H * N + 16 * warp + 8 * nt + 2 * t4 + e] = a;
+            }
+    }
     if (p.ds0) {
         float* o = p.ds0 + bh * N * N;
 #pragma unroll
@@ -510,20 +716,35 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
     }
 }
 
-template <typename IoT, int PREC> static int launch_bwd_t(const BwdParams& p, cudaStream_t stream) {
-    using Smem = BwdSmem<IoT>;
-    auto kern = wkv7_bwd_kernel<IoT, PREC>;
+// dparams[i][c] = sum over batch of the per-(batch, head) partials, in a fixed order.
+__global__ void reduce_dparams_kernel(const float* __restrict__ ws, float* __restrict__ out, long long B, long long n3) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i >= n3) return;
+    float acc = 0.f;
+    for (long long b = 0; b < B; ++b) acc += ws[b * n3 + i];
+    out[i] = acc;
+}
+
+template <typename IoT, int PREC, bool LN> static int launch_bwd_t(const BwdParams& p, cudaStream_t stream) {
+    using Smem = BwdSmem<IoT, PREC, LN>;
+    auto kern = wkv7_bwd_kernel<IoT, PREC, LN>;
     const int smem = (int)sizeof(Smem);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return kLaunchFailed;
     kern<<<(unsigned)(p.B * p.H), THREADS, smem, stream>>>(p);
-    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+    if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
+    if (LN) {
+        const long long n3 = 3 * p.H * N;
+        reduce_dparams_kernel<<<(unsigned)((n3 + 255) / 256), 256, 0, stream>>>(p.dparams_ws, p.dparams, p.B, n3);
+        if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
+    }
+    return kOk;
 }
 
-int launch_bwd(const BwdParams& p, int io_dtype, cudaStream_t stream) {
-    if (io_dtype == 0) return launch_bwd_t<__nv_bfloat16, 1>(p, stream);
-    if (io_dtype == 2) return launch_bwd_t<float, 1>(p, stream);
-    return launch_bwd_t<float, 3>(p, stream);
+int launch_bwd(const BwdParams& p, int io_dtype, bool ln, cudaStream_t stream) {
+    if (io_dtype == 0) return ln ? launch_bwd_t<__nv_bfloat16, 1, true>(p, stream) : launch_bwd_t<__nv_bfloat16, 1, false>(p, stream);
+    if (io_dtype == 2) return ln ? launch_bwd_t<float, 1, true>(p, stream) : launch_bwd_t<float, 1, false>(p, stream);
+    return ln ? launch_bwd_t<float, 3, true>(p, stream) : launch_bwd_t<float, 3, false>(p, stream);
 }
 
 }  // namespace wkv7

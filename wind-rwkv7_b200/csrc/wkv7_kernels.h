@@ -19,7 +19,13 @@ struct FwdParams {
 };
 
 struct BwdParams {
-    const void *r, *w, *k, *v, *a, *b, *dy;
+    const void *r, *w, *k, *v, *a, *b, *dy;  // dy: gradient of y (attn) or of the fused output (attn_ln)
+    const void* g;           // attn_ln only
+    const float* params;     // attn_ln only
+    void* dg;                // attn_ln only
+    float* dparams;          // attn_ln only: [3, H*N]
+    float* dparams_ws;       // attn_ln only: [B, 3, H*N] per-(batch, head) partials
+    float eps;
     const float* ckpt;   // written by the forward
     const float* dsT;    // [B,H,N,N] or null (zeros)
     const float* sT;     // final state of the forward; needed only when dsT is given
@@ -31,6 +37,6 @@ struct BwdParams {
 };
 
 int launch_fwd(const FwdParams& p, int io_dtype, bool ln, cudaStream_t stream);
-int launch_bwd(const BwdParams& p, int io_dtype, cudaStream_t stream);
+int launch_bwd(const BwdParams& p, int io_dtype, bool ln, cudaStream_t stream);
 
 }  // namespace wkv7

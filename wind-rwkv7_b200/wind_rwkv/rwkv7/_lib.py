@@ -26,6 +26,8 @@ _SIGNATURES = {
     'wkv7_fwd': (_int, [_vp] * 10 + [_i64] * 7 + [_int, _vp]),
     'wkv7_bwd': (_int, [_vp] * 17 + [_i64] * 7 + [_int, _vp]),
     'wkv7_attn_ln_fwd': (_int, [_vp] * 12 + [_f32] + [_i64] * 7 + [_int, _vp]),
+    'wkv7_attn_ln_bwd_workspace_bytes': (_i64, [_i64] * 3),
+    'wkv7_attn_ln_bwd': (_int, [_vp] * 22 + [_f32] + [_i64] * 7 + [_int, _vp]),
 }
 
 
