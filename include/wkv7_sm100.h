@@ -45,6 +45,10 @@ extern "C" {
 #define WKV7_ERR_LAUNCH (-7)         /* the CUDA launch failed */
 #define WKV7_ERR_TOO_LARGE (-8)
 #define WKV7_ERR_DEVICE_TIMEOUT (-9) /* reported by wkv7_device_status() */
+#define WKV7_ERR_STATIC_SCRATCH (-10) /* problem too large for wkv7_attn_ln_bwd_static's built-in scratch */
+
+/* Size of the scratch array compiled into the library for wkv7_attn_ln_bwd_static. */
+#define WKV7_STATIC_SCRATCH_BYTES (4u << 20)
 
 /* Human-readable text for a status code (host pointer, static storage). */
 const char* wkv7_status_string(int status);
@@ -106,6 +110,36 @@ int wkv7_attn_ln_bwd(const void* r, const void* w, const void* k, const void* v,
                      float* dparams, float* workspace, float* ds0, float eps,
                      int64_t B, int64_t T, int64_t H, int64_t N,
                      int64_t stride_b, int64_t stride_t, int64_t stride_h, int io_dtype, void* stream);
+
+/*
+ * wkv7_attn_ln_bwd for callers that cannot hand over a workspace.  No counterpart in the
+ * reference, where PyTorch allocates everything.
+ *
+ * Who needs it: code that drives the library without an allocator of its own and may not call
+ * cudaMalloc at this point -- a runtime that has already handed all device memory to its own
+ * pool, a plugin loaded into a host application that owns the memory, or a thread for which
+ * cudaMalloc's implicit device-wide synchronisation is not acceptable in the middle of a step.
+ * wkv7_attn_ln_bwd needs B*3*H*N floats of scratch for the per-batch partial parameter
+ * gradients; this variant keeps that scratch in an array of WKV7_STATIC_SCRATCH_BYTES (4 MiB)
+ * that is part of the library's device image.  Every GPU that loads the library holds those
+ * 4 MiB until the process exits, whether or not this entry point is ever called.
+ *
+ * Arguments and results are exactly those of wkv7_attn_ln_bwd without `workspace`; inputs and
+ * outputs are still the caller's.  The call itself allocates nothing: no cudaMalloc, cudaFree
+ * or allocating library routine.
+ *  - Limit: B*3*H*N*4 <= WKV7_STATIC_SCRATCH_BYTES, else WKV7_ERR_STATIC_SCRATCH and nothing runs.
+ *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
+ *    that device current) and caches it; make that first call before starting a stream capture.
+ *  - All calls on a device share the one array.  Each call overwrites the part it uses before
+ *    reading it, so nothing has to be cleared between calls, but two calls that can overlap on
+ *    the GPU (different streams, no dependency) race on it: serialise them.
+ */
+int wkv7_attn_ln_bwd_static(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+                            const void* g, const float* params, const void* dy, const float* ckpt, const float* dsT,
+                            const float* sT, void* dr, void* dw, void* dk, void* dv, void* da, void* db, void* dg,
+                            float* dparams, float* ds0, float eps,
+                            int64_t B, int64_t T, int64_t H, int64_t N,
+                            int64_t stride_b, int64_t stride_t, int64_t stride_h, int io_dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -3,6 +3,14 @@
 #include "../../include/wkv7_sm100.h"
 #include "wkv7_kernels.h"
 
+#include <mutex>
+
+// Scratch for wkv7_attn_ln_bwd_static: lives in the library's device image, one copy on every GPU
+// that loads the library, until the process exits.  Only its ADDRESS ON THE DEVICE may be given
+// to a kernel; in host code the name is a host-side stand-in, so the address is fetched once
+// per device with cudaGetSymbolAddress (see static_scratch()).
+static __device__ __align__(256) float g_attn_ln_static_scratch[WKV7_STATIC_SCRATCH_BYTES / sizeof(float)];
+
 namespace {
 
 __device__ int g_status_word = 0;
@@ -11,6 +19,23 @@ int* status_ptr() {
     int* p = nullptr;
     if (cudaGetSymbolAddress((void**)&p, g_status_word) != cudaSuccess) return nullptr;
     return p;
+}
+
+// Device address of g_attn_ln_static_scratch on the current device, looked up on the first call
+// for that device and cached.  Returns nullptr if the lookup fails.
+float* static_scratch() {
+    constexpr int kMaxDevices = 64;
+    static float* cache[kMaxDevices] = {};
+    static std::mutex mu;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cache[dev]) {
+        float* ptr = nullptr;
+        if (cudaGetSymbolAddress((void**)&ptr, g_attn_ln_static_scratch) != cudaSuccess) return nullptr;
+        cache[dev] = ptr;
+    }
+    return cache[dev];
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -43,6 +68,7 @@ const char* wkv7_status_string(int status) {
         case WKV7_ERR_LAUNCH: return "CUDA launch failed";
         case WKV7_ERR_TOO_LARGE: return "B*H exceeds the grid limit";
         case WKV7_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
+        case WKV7_ERR_STATIC_SCRATCH: return "problem needs more than WKV7_STATIC_SCRATCH_BYTES of built-in scratch (B*3*H*N*4 bytes); use wkv7_attn_ln_bwd with a caller-provided workspace";
         default: return "unknown status";
     }
 }
@@ -164,6 +190,19 @@ int wkv7_attn_ln_bwd(const void* r, const void* w, const void* k, const void* v,
                      int64_t N, int64_t stride_b, int64_t stride_t, int64_t stride_h, int io_dtype, void* stream) {
     return bwd_common(r, w, k, v, a, b, g, params, true, eps, dy, ckpt, dsT, sT, dr, dw, dk, dv, da, db, dg, dparams,
                       workspace, ds0, B, T, H, N, stride_b, stride_t, stride_h, io_dtype, stream);
+}
+
+int wkv7_attn_ln_bwd_static(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+                            const void* g, const float* params, const void* dy, const float* ckpt, const float* dsT,
+                            const float* sT, void* dr, void* dw, void* dk, void* dv, void* da, void* db, void* dg,
+                            float* dparams, float* ds0, float eps, int64_t B, int64_t T, int64_t H, int64_t N,
+                            int64_t stride_b, int64_t stride_t, int64_t stride_h, int io_dtype, void* stream) {
+    if (B < 0 || H < 0 || N < 0) return WKV7_ERR_SHAPE;
+    if (wkv7_attn_ln_bwd_workspace_bytes(B, H, N) > (int64_t)WKV7_STATIC_SCRATCH_BYTES) return WKV7_ERR_STATIC_SCRATCH;
+    float* scratch = static_scratch();
+    if (!scratch) return WKV7_ERR_LAUNCH;
+    return bwd_common(r, w, k, v, a, b, g, params, true, eps, dy, ckpt, dsT, sT, dr, dw, dk, dv, da, db, dg, dparams,
+                      scratch, ds0, B, T, H, N, stride_b, stride_t, stride_h, io_dtype, stream);
 }
 
 }  // extern "C"

@@ -28,6 +28,7 @@ _SIGNATURES = {
     'wkv7_attn_ln_fwd': (_int, [_vp] * 12 + [_f32] + [_i64] * 7 + [_int, _vp]),
     'wkv7_attn_ln_bwd_workspace_bytes': (_i64, [_i64] * 3),
     'wkv7_attn_ln_bwd': (_int, [_vp] * 22 + [_f32] + [_i64] * 7 + [_int, _vp]),
+    'wkv7_attn_ln_bwd_static': (_int, [_vp] * 21 + [_f32] + [_i64] * 7 + [_int, _vp]),
 }
 
 
