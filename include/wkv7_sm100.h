@@ -112,6 +112,59 @@ int wkv7_attn_ln_bwd(const void* r, const void* w, const void* k, const void* v,
                      int64_t stride_b, int64_t stride_t, int64_t stride_h, int io_dtype, void* stream);
 
 /*
+ * ddlerp: data-dependent token-shift interpolation.  Replaces fw1_triton_ / fw2_triton_
+ * (wind_rwkv/rwkv7/rwkv7_ddlerp.py:19-84) behind DDLerp.forward (:307-322).  All tensors bf16,
+ * contiguous: x [B,T,C], alpha [C], L [4D,C], R [4,C,D], beta [4,C] (the reference casts its fp32
+ * parameters to bf16 first, :309).  Outputs: m [B,T,4D] (tanh activations, input of the backward)
+ * and y [4,B,T,C].  Requires T % 64 == 0, C % 64 == 0 (as the reference, :44-45), D in {16,32,64}.
+ *   xx = x_{t-1} - x_t ;  m = tanh((x + xx*alpha) @ L^T) ;  y_k = x + xx*(m_k @ R_k^T + beta_k)
+ */
+int wkv7_ddlerp_fwd(const void* x, const void* alpha, const void* L, const void* R, const void* beta,
+                    void* m, void* y, int64_t B, int64_t T, int64_t C, int64_t D, void* stream);
+
+/*
+ * ddlerp backward.  Replaces bw1..bw4_triton_ (rwkv7_ddlerp.py:92-303) behind DDLerp.backward
+ * (:323-334).  dy0..dy3: bf16 [B,T,C].  dpre_workspace: bf16 [B,T,4D] scratch.  dx: bf16 [B,T,C].
+ * Parameter gradients are fp32 and overwritten: dalpha [C], dL [4D,C], dR [4,C,D], dbeta [4,C].
+ */
+int wkv7_ddlerp_bwd(const void* x, const void* alpha, const void* L, const void* R, const void* beta, const void* m,
+                    const void* dy0, const void* dy1, const void* dy2, const void* dy3,
+                    void* dpre_workspace, void* dx, float* dalpha, float* dL, float* dR, float* dbeta,
+                    int64_t B, int64_t T, int64_t C, int64_t D, void* stream);
+
+/*
+ * expand_loras: second-stage LoRA expansion producing (w, k, kk, b) for the mixer.  Replaces
+ * fw_triton_ (wind_rwkv/rwkv7/rwkv7_expand_loras.py:32-89) behind ExpandLoras.forward (:215-231).
+ * All tensors bf16, contiguous: w_in,k_in [B,T,C]; z_in,a_in,ma_in,mk_in [B,T,D]; W* [C,D];
+ * biases [C]; outputs [B,T,C].  Head size 64 (C % 64 == 0), T % 16 == 0, D in {16,32,64}.
+ *   w = -softplus(-(w_bias+w_in)) - 0.5 ;  z = tanh(z_in)@Wz^T + k_in ;  kk = z/||z||_head
+ *   a, ma, mk = sigmoid(x_in@W^T + bias) ;  k = k_in*(ma+a-ma*a)*exp(w*mk) ;  b = -kk*a
+ */
+int wkv7_expand_loras_fwd(const void* w_in, const void* k_in, const void* z_in, const void* a_in, const void* ma_in,
+                          const void* mk_in, const void* Wz, const void* Wa, const void* Wma, const void* Wmk,
+                          const void* w_bias, const void* a_bias, const void* ma_bias, const void* mk_bias,
+                          void* w_out, void* k_out, void* kk_out, void* b_out,
+                          int64_t B, int64_t T, int64_t C, int64_t D, void* stream);
+
+/* Bytes of workspace wkv7_expand_loras_bwd needs: 4*B*T*(C/64)*D*2 (per-head partials of the
+ * rank-D input gradients, bf16, as the reference keeps them, rwkv7_expand_loras.py:201,207-210). */
+int64_t wkv7_expand_loras_bwd_workspace_bytes(int64_t B, int64_t T, int64_t C, int64_t D);
+
+/*
+ * expand_loras backward.  Replaces bw_triton_ (rwkv7_expand_loras.py:91-211) behind
+ * ExpandLoras.backward (:232-239).  Input gradients bf16 (dw_in,dk_in [B,T,C]; dz_in..dmk_in
+ * [B,T,D]); weight and bias gradients fp32, overwritten.
+ */
+int wkv7_expand_loras_bwd(const void* w_in, const void* k_in, const void* z_in, const void* a_in, const void* ma_in,
+                          const void* mk_in, const void* Wz, const void* Wa, const void* Wma, const void* Wmk,
+                          const void* w_bias, const void* a_bias, const void* ma_bias, const void* mk_bias,
+                          const void* dw_out, const void* dk_out, const void* dkk_out, const void* db_out,
+                          void* dw_in, void* dk_in, void* dz_in, void* da_in, void* dma_in, void* dmk_in,
+                          float* dWz, float* dWa, float* dWma, float* dWmk,
+                          float* dw_bias, float* da_bias, float* dma_bias, float* dmk_bias,
+                          void* workspace, int64_t B, int64_t T, int64_t C, int64_t D, void* stream);
+
+/*
  * wkv7_attn_ln_bwd for callers that cannot hand over a workspace.  No counterpart in the
  * reference, where PyTorch allocates everything.
  *

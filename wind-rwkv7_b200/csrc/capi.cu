@@ -2,6 +2,8 @@
 // validation, the per-device status word, and dispatch to the kernel launchers.
 #include "../../include/wkv7_sm100.h"
 #include "wkv7_kernels.h"
+#include "ddlerp.h"
+#include "expand_loras.h"
 
 #include <mutex>
 
@@ -203,6 +205,124 @@ int wkv7_attn_ln_bwd_static(const void* r, const void* w, const void* k, const v
     if (!scratch) return WKV7_ERR_LAUNCH;
     return bwd_common(r, w, k, v, a, b, g, params, true, eps, dy, ckpt, dsT, sT, dr, dw, dk, dv, da, db, dg, dparams,
                       scratch, ds0, B, T, H, N, stride_b, stride_t, stride_h, io_dtype, stream);
+}
+
+static int ddlerp_check(int64_t B, int64_t T, int64_t C, int64_t D) {
+    if (B < 0 || T < 0 || C <= 0 || D <= 0) return WKV7_ERR_SHAPE;
+    if (T % 64 != 0 || C % 64 != 0) return WKV7_ERR_CHUNK;
+    if (D != 16 && D != 32 && D != 64) return WKV7_ERR_SHAPE;
+    return WKV7_OK;
+}
+
+int wkv7_ddlerp_fwd(const void* x, const void* alpha, const void* L, const void* R, const void* beta, void* m, void* y,
+                    int64_t B, int64_t T, int64_t C, int64_t D, void* stream) {
+    int rc = ddlerp_check(B, T, C, D);
+    if (rc) return rc;
+    if (B == 0 || T == 0) return WKV7_OK;
+    const void* ptrs[] = {x, alpha, L, R, beta, m, y};
+    for (const void* q : ptrs) {
+        if (!q) return WKV7_ERR_NULL;
+        if (!aligned16(q)) return WKV7_ERR_ALIGN;
+    }
+    wkv7::DdlerpFwdParams p{x, alpha, L, R, beta, m, y, B * T, T, C, (int)D};
+    return wkv7::launch_ddlerp_fwd(p, (cudaStream_t)stream);
+}
+
+int wkv7_ddlerp_bwd(const void* x, const void* alpha, const void* L, const void* R, const void* beta, const void* m,
+                    const void* dy0, const void* dy1, const void* dy2, const void* dy3, void* dpre_workspace, void* dx,
+                    float* dalpha, float* dL, float* dR, float* dbeta, int64_t B, int64_t T, int64_t C, int64_t D,
+                    void* stream) {
+    int rc = ddlerp_check(B, T, C, D);
+    if (rc) return rc;
+    const void* ptrs[] = {x, alpha, L, R, beta, m, dy0, dy1, dy2, dy3, dpre_workspace, dx, dalpha, dL, dR, dbeta};
+    for (const void* q : ptrs) {
+        if (!q) return WKV7_ERR_NULL;
+        if (!aligned16(q)) return WKV7_ERR_ALIGN;
+    }
+    wkv7::DdlerpBwdParams p{};
+    p.x = x; p.alpha = alpha; p.L = L; p.R = R; p.beta = beta; p.m = m;
+    p.dy[0] = dy0; p.dy[1] = dy1; p.dy[2] = dy2; p.dy[3] = dy3;
+    p.dpre = dpre_workspace; p.dx = dx; p.dalpha = dalpha; p.dL = dL; p.dR = dR; p.dbeta = dbeta;
+    p.rows = B * T; p.T = T; p.C = C; p.D = (int)D;
+    if (B == 0 || T == 0) {  // parameter gradients of an empty batch are zero
+        cudaStream_t s = (cudaStream_t)stream;
+        if (cudaMemsetAsync(dalpha, 0, sizeof(float) * C, s) != cudaSuccess || cudaMemsetAsync(dbeta, 0, sizeof(float) * 4 * C, s) != cudaSuccess ||
+            cudaMemsetAsync(dR, 0, sizeof(float) * 4 * C * D, s) != cudaSuccess || cudaMemsetAsync(dL, 0, sizeof(float) * 4 * D * C, s) != cudaSuccess)
+            return WKV7_ERR_LAUNCH;
+        return WKV7_OK;
+    }
+    return wkv7::launch_ddlerp_bwd(p, (cudaStream_t)stream);
+}
+
+static int loras_check(int64_t B, int64_t T, int64_t C, int64_t D) {
+    if (B < 0 || T < 0 || C <= 0 || D <= 0) return WKV7_ERR_SHAPE;
+    if (T % 16 != 0 || C % 64 != 0) return WKV7_ERR_CHUNK;
+    if (D != 16 && D != 32 && D != 64) return WKV7_ERR_SHAPE;
+    return WKV7_OK;
+}
+
+int wkv7_expand_loras_fwd(const void* w_in, const void* k_in, const void* z_in, const void* a_in, const void* ma_in,
+                          const void* mk_in, const void* Wz, const void* Wa, const void* Wma, const void* Wmk,
+                          const void* w_bias, const void* a_bias, const void* ma_bias, const void* mk_bias, void* w_out,
+                          void* k_out, void* kk_out, void* b_out, int64_t B, int64_t T, int64_t C, int64_t D, void* stream) {
+    int rc = loras_check(B, T, C, D);
+    if (rc) return rc;
+    if (B == 0 || T == 0) return WKV7_OK;
+    const void* ptrs[] = {w_in, k_in, z_in, a_in, ma_in, mk_in, Wz, Wa, Wma, Wmk, w_bias, a_bias, ma_bias, mk_bias, w_out, k_out, kk_out, b_out};
+    for (const void* q : ptrs) {
+        if (!q) return WKV7_ERR_NULL;
+        if (!aligned16(q)) return WKV7_ERR_ALIGN;
+    }
+    wkv7::LorasParams p{};
+    p.w_in = w_in; p.k_in = k_in; p.lin[0] = z_in; p.lin[1] = a_in; p.lin[2] = ma_in; p.lin[3] = mk_in;
+    p.W[0] = Wz; p.W[1] = Wa; p.W[2] = Wma; p.W[3] = Wmk;
+    p.w_bias = w_bias; p.bias[0] = a_bias; p.bias[1] = ma_bias; p.bias[2] = mk_bias;
+    p.w_out = w_out; p.k_out = k_out; p.kk_out = kk_out; p.b_out = b_out;
+    p.rows = B * T; p.T = T; p.C = C; p.D = (int)D;
+    return wkv7::launch_loras_fwd(p, (cudaStream_t)stream);
+}
+
+int64_t wkv7_expand_loras_bwd_workspace_bytes(int64_t B, int64_t T, int64_t C, int64_t D) {
+    if (B < 0 || T < 0 || C < 0 || D < 0) return 0;
+    return 4 * B * T * (C / 64) * D * 2;
+}
+
+int wkv7_expand_loras_bwd(const void* w_in, const void* k_in, const void* z_in, const void* a_in, const void* ma_in,
+                          const void* mk_in, const void* Wz, const void* Wa, const void* Wma, const void* Wmk,
+                          const void* w_bias, const void* a_bias, const void* ma_bias, const void* mk_bias,
+                          const void* dw_out, const void* dk_out, const void* dkk_out, const void* db_out, void* dw_in,
+                          void* dk_in, void* dz_in, void* da_in, void* dma_in, void* dmk_in, float* dWz, float* dWa,
+                          float* dWma, float* dWmk, float* dw_bias, float* da_bias, float* dma_bias, float* dmk_bias,
+                          void* workspace, int64_t B, int64_t T, int64_t C, int64_t D, void* stream) {
+    int rc = loras_check(B, T, C, D);
+    if (rc) return rc;
+    const void* ptrs[] = {w_in, k_in, z_in, a_in, ma_in, mk_in, Wz, Wa, Wma, Wmk, w_bias, a_bias, ma_bias, mk_bias,
+                          dw_out, dk_out, dkk_out, db_out, dw_in, dk_in, dz_in, da_in, dma_in, dmk_in,
+                          dWz, dWa, dWma, dWmk, dw_bias, da_bias, dma_bias, dmk_bias, workspace};
+    for (const void* q : ptrs) {
+        if (!q) return WKV7_ERR_NULL;
+        if (!aligned16(q)) return WKV7_ERR_ALIGN;
+    }
+    wkv7::LorasParams p{};
+    p.w_in = w_in; p.k_in = k_in; p.lin[0] = z_in; p.lin[1] = a_in; p.lin[2] = ma_in; p.lin[3] = mk_in;
+    p.W[0] = Wz; p.W[1] = Wa; p.W[2] = Wma; p.W[3] = Wmk;
+    p.w_bias = w_bias; p.bias[0] = a_bias; p.bias[1] = ma_bias; p.bias[2] = mk_bias;
+    p.dw_out = dw_out; p.dk_out = dk_out; p.dkk_out = dkk_out; p.db_out = db_out;
+    p.dw_in = dw_in; p.dk_in = dk_in; p.dlin[0] = dz_in; p.dlin[1] = da_in; p.dlin[2] = dma_in; p.dlin[3] = dmk_in;
+    p.dW[0] = dWz; p.dW[1] = dWa; p.dW[2] = dWma; p.dW[3] = dWmk;
+    p.dw_bias = dw_bias; p.dbias[0] = da_bias; p.dbias[1] = dma_bias; p.dbias[2] = dmk_bias;
+    p.partial = workspace;
+    p.rows = B * T; p.T = T; p.C = C; p.D = (int)D;
+    if (B == 0 || T == 0) {
+        cudaStream_t s = (cudaStream_t)stream;
+        float* w4[] = {dWz, dWa, dWma, dWmk};
+        float* b4[] = {dw_bias, da_bias, dma_bias, dmk_bias};
+        for (int i = 0; i < 4; ++i)
+            if (cudaMemsetAsync(w4[i], 0, sizeof(float) * C * D, s) != cudaSuccess || cudaMemsetAsync(b4[i], 0, sizeof(float) * C, s) != cudaSuccess)
+                return WKV7_ERR_LAUNCH;
+        return WKV7_OK;
+    }
+    return wkv7::launch_loras_bwd(p, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -1,0 +1,28 @@
+// Launcher interface of the ddlerp kernels (forward: ddlerp_fwd.cu, backward: ddlerp_bwd.cu).
+#pragma once
+#include "wkv7_common.cuh"
+
+namespace wkv7 {
+
+struct DdlerpFwdParams {
+    const void *x, *alpha, *L, *R, *beta;  // bf16: [rows,C], [C], [4D,C], [4,C,D], [4,C]
+    void* m;                                // bf16 [rows,4D]  tanh activations, kept for the backward
+    void* y;                                // bf16 [4,rows,C]
+    long long rows, T, C;                   // rows = B*T
+    int D;
+};
+
+struct DdlerpBwdParams {
+    const void *x, *alpha, *L, *R, *beta, *m;  // as the forward
+    const void* dy[4];                          // bf16 [rows,C] each
+    void* dpre;                                 // bf16 [rows,4D] workspace: gradient before the tanh
+    void* dx;                                   // bf16 [rows,C]
+    float *dalpha, *dL, *dR, *dbeta;            // fp32 [C], [4D,C], [4,C,D], [4,C]; zero-filled by the launcher
+    long long rows, T, C;
+    int D;
+};
+
+int launch_ddlerp_fwd(const DdlerpFwdParams& p, cudaStream_t stream);
+int launch_ddlerp_bwd(const DdlerpBwdParams& p, cudaStream_t stream);
+
+}  // namespace wkv7

@@ -1,0 +1,56 @@
+"""ddlerp: drop-in for wind_rwkv/rwkv7/rwkv7_ddlerp.py (`ddlerp(x, alpha, L, R, beta) -> (xrg, xwa, xk, xv)`).
+
+    xx = shift(x) - x ;  m = tanh((x + xx*alpha) @ L^T) ;  y_k = x + xx*(m_k @ R_k^T + beta_k)
+
+As upstream (rwkv7_ddlerp.py:309) the parameters are cast to bf16 for the kernels; their gradients
+come back in fp32 and autograd casts them to the parameter dtype.
+"""
+import torch as th
+
+from . import _lib
+
+
+class DDLerp(th.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, alpha, L, R, beta):
+        _lib.require_cuda(x, alpha, L, R, beta)
+        assert x.dtype == th.bfloat16, 'x must be bfloat16'
+        B, T, C = x.shape
+        D = R.shape[2]
+        assert list(alpha.shape) == [C] and list(beta.shape) == [4, 1, 1, C]
+        assert list(L.shape) == [4 * D, C] and list(R.shape) == [4, C, D]
+        assert T % 64 == 0 and C % 64 == 0, 'ddlerp needs T % 64 == 0 and C % 64 == 0'
+        x = x.contiguous()
+        Lb, Rb, ab, bb = [i.detach().to(th.bfloat16).contiguous() for i in [L, R, alpha, beta]]
+        m = th.empty(B, T, 4 * D, dtype=th.bfloat16, device=x.device)
+        y = th.empty(4, B, T, C, dtype=th.bfloat16, device=x.device)
+        rc = _lib.lib().wkv7_ddlerp_fwd(x.data_ptr(), ab.data_ptr(), Lb.data_ptr(), Rb.data_ptr(), bb.data_ptr(),
+                                        m.data_ptr(), y.data_ptr(), B, T, C, D, _lib.stream_of(x))
+        _lib.check(rc, 'wkv7_ddlerp_fwd')
+        ctx.save_for_backward(x, ab, Lb, Rb, bb, m)
+        ctx.param_dtypes = (alpha.dtype, L.dtype, R.dtype, beta.dtype)
+        return y.unbind(dim=0)
+
+    @staticmethod
+    def backward(ctx, dy0, dy1, dy2, dy3):
+        x, ab, Lb, Rb, bb, m = ctx.saved_tensors
+        B, T, C = x.shape
+        D = Rb.shape[2]
+        dys = [th.zeros_like(x) if d is None else d.to(th.bfloat16).contiguous() for d in (dy0, dy1, dy2, dy3)]
+        dev = x.device
+        dpre = th.empty(B, T, 4 * D, dtype=th.bfloat16, device=dev)
+        dx = th.empty_like(x)
+        dalpha = th.empty(C, dtype=th.float32, device=dev)
+        dL = th.empty(4 * D, C, dtype=th.float32, device=dev)
+        dR = th.empty(4, C, D, dtype=th.float32, device=dev)
+        dbeta = th.empty(4, 1, 1, C, dtype=th.float32, device=dev)
+        rc = _lib.lib().wkv7_ddlerp_bwd(x.data_ptr(), ab.data_ptr(), Lb.data_ptr(), Rb.data_ptr(), bb.data_ptr(),
+                                        m.data_ptr(), *[d.data_ptr() for d in dys], dpre.data_ptr(), dx.data_ptr(),
+                                        dalpha.data_ptr(), dL.data_ptr(), dR.data_ptr(), dbeta.data_ptr(),
+                                        B, T, C, D, _lib.stream_of(x))
+        _lib.check(rc, 'wkv7_ddlerp_bwd')
+        ta, tL, tR, tb = ctx.param_dtypes
+        return dx, dalpha.to(ta), dL.to(tL), dR.to(tR), dbeta.to(tb)
+
+
+ddlerp = DDLerp.apply
