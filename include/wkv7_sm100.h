@@ -38,7 +38,7 @@ extern "C" {
 #define WKV7_OK 0
 #define WKV7_ERR_SHAPE (-1)          /* negative or inconsistent dimensions */
 #define WKV7_ERR_HEAD_SIZE (-2)      /* only N == 64 is built */
-#define WKV7_ERR_CHUNK (-3)          /* T is not a multiple of 16 */
+#define WKV7_ERR_CHUNK (-3)          /* T is not a multiple of 16 (WKV7, expand_loras) or C not of 64 */
 #define WKV7_ERR_ALIGN (-4)          /* a pointer or stride breaks 16-byte row alignment */
 #define WKV7_ERR_DTYPE (-5)
 #define WKV7_ERR_NULL (-6)           /* a required pointer is null */
@@ -116,7 +116,8 @@ int wkv7_attn_ln_bwd(const void* r, const void* w, const void* k, const void* v,
  * (wind_rwkv/rwkv7/rwkv7_ddlerp.py:19-84) behind DDLerp.forward (:307-322).  All tensors bf16,
  * contiguous: x [B,T,C], alpha [C], L [4D,C], R [4,C,D], beta [4,C] (the reference casts its fp32
  * parameters to bf16 first, :309).  Outputs: m [B,T,4D] (tanh activations, input of the backward)
- * and y [4,B,T,C].  Requires T % 64 == 0, C % 64 == 0 (as the reference, :44-45), D in {16,32,64}.
+ * and y [4,B,T,C].  Requires C % 64 == 0 and D in {16,32,64}; any T (the reference needs T % 64 == 0
+ * for T >= 64, :44-45).
  *   xx = x_{t-1} - x_t ;  m = tanh((x + xx*alpha) @ L^T) ;  y_k = x + xx*(m_k @ R_k^T + beta_k)
  */
 int wkv7_ddlerp_fwd(const void* x, const void* alpha, const void* L, const void* R, const void* beta,

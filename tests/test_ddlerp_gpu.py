@@ -91,8 +91,15 @@ def test_golden(golden):
         assert rel_l2(t.grad, g['d' + n]) <= 2e-2, n
 
 
+def test_ragged_lengths():
+    """Sequence lengths that fill no whole tile: T = 32 (upstream's smallest case), 80 and 17."""
+    run_case(1, 32, 128, 16, seed=6)
+    run_case(3, 80, 128, 32, seed=7)
+    run_case(2, 17, 64, 16, seed=8)
+
+
 def test_rejects_bad_shapes():
     from wind_rwkv.rwkv7 import ddlerp
-    ins = [i.cuda() for i in data(1, 32, 128, 16, 0)]
+    ins = [i.cuda() for i in data(1, 32, 96, 16, 0)]
     with pytest.raises(AssertionError):
         ddlerp(*ins)

@@ -1,0 +1,81 @@
+"""The TimeMixer layer (ddlerp -> projections -> expand_loras -> attn_ln -> output projection) against
+upstream's fp32 RefTimeMixer (tests/test_time_mixer.py:13-55), restated in oracle/wkv7_ref.py and
+pinned by tests/golden/mixer_small.npz (which upstream's own class produced).
+
+The layer is a bf16 path end to end (bf16 matmuls, bf16 intermediates), checked the way upstream
+checks it: relative L2 error of the output and of every gradient (tests/utils.py:18-56) against the
+fp32 reference on the same fp32 parameters, tolerance 2e-2 (upstream warns above 1e-2 on its own
+bf16 kernels; the fixture's parameters have std 0.1, which amplifies bf16 rounding through the
+tanh/sigmoid LoRA stacks)."""
+from collections import namedtuple
+
+import numpy as np
+import pytest
+import torch as th
+
+from test_attn_gpu import rel_l2
+
+pytestmark = pytest.mark.gpu
+Config = namedtuple('Config', ['n_layer', 'n_head', 'n_embd'])
+
+
+def test_parameter_names_and_shapes_match_upstream(golden):
+    from wind_rwkv.rwkv7 import TimeMixer
+    g = golden('mixer_small.npz')
+    model = TimeMixer(Config(12, int(g['n_head']), 128), 6)
+    ours = {n: tuple(p.shape) for n, p in model.named_parameters()}
+    theirs = {k[2:]: v.shape for k, v in g.items() if k.startswith('p.')}
+    assert ours == theirs
+
+
+def test_golden_forward_backward(golden):
+    from wind_rwkv.rwkv7 import TimeMixer
+    g = golden('mixer_small.npz')
+    model = TimeMixer(Config(12, int(g['n_head']), 128), 6).cuda()
+    params = {k[2:]: th.from_numpy(v).cuda().requires_grad_() for k, v in g.items() if k.startswith('p.')}
+    x = th.from_numpy(g['x']).cuda().requires_grad_()
+    y = th.func.functional_call(model, params, (x,))
+    y.float().backward(th.from_numpy(g['dy']).cuda())
+    assert rel_l2(y, g['y']) <= 2e-2
+    assert rel_l2(x.grad, g['dx']) <= 2e-2
+    worst = {}
+    for n, p in params.items():
+        ref = g['dp.' + n]
+        if np.linalg.norm(ref) > 0:
+            worst[n] = rel_l2(p.grad, ref)
+    bad = {n: f'{e:.2e}' for n, e in worst.items() if e > 2e-2}
+    assert not bad, bad
+
+
+def test_config3_shape_runs_and_matches_oracle_on_a_slice():
+    """d = 768, H = 12, T = 1024 (config 3 of the workload list) at batch 2, random parameters of
+    std 0.02 around upstream's initial values; output and input gradient against the fp32 oracle."""
+    import wkv7_ref
+    from wind_rwkv.rwkv7 import TimeMixer
+    th.manual_seed(0)
+    model = TimeMixer(Config(12, 12, 768), 3).cuda()
+    with th.no_grad():
+        for n, p in model.named_parameters():
+            p.add_(th.randn_like(p) * 0.02)
+        model.Wo.normal_(std=0.02)
+    x = th.randn(2, 1024, 768, device='cuda').requires_grad_()
+    y = model(x)
+    dy = th.randn_like(y)
+    y.backward(dy)
+    assert bool(th.isfinite(y).all()) and bool(th.isfinite(x.grad).all())
+    pc = {n: p.detach().cpu() for n, p in model.named_parameters()}
+    xc = x.detach().cpu().requires_grad_()
+    yr = wkv7_ref.ref_time_mixer(pc, xc, 12)
+    yr.backward(dy.float().cpu())
+    assert rel_l2(y, yr.detach().numpy()) <= 2e-2
+    assert rel_l2(x.grad, xc.grad.numpy()) <= 2e-2
+    for n, p in model.named_parameters():
+        assert p.grad is not None and bool(th.isfinite(p.grad).all()), n
+
+
+def test_other_backends_are_refused():
+    from wind_rwkv.rwkv7 import TimeMixer, attn_triton
+    with pytest.raises(ValueError):
+        TimeMixer(Config(12, 2, 128), 0, attn_impl='triton')
+    with pytest.raises(NotImplementedError):
+        attn_triton(None, None, None, None, None, None, 64)

@@ -35,11 +35,16 @@ __global__ void __launch_bounds__(256) ddlerp_bwd_dpre_kernel(DdlerpBwdParams p)
     const int C = (int)p.C, nkb = C / 64;
     const int erow = tid >> 3, eseg = tid & 7;  // 8 threads per row, 8 channels each
     const long long grow = row0 + erow;
+    const bool live = grow < p.rows;
     const bool first = (grow % p.T) == 0;
     const bf16* x = (const bf16*)p.x;
 
     uint4 rx, rp, rdy[4];
     auto load_in = [&](int cb) {
+        if (!live) {
+            rx = rp = rdy[0] = rdy[1] = rdy[2] = rdy[3] = make_uint4(0, 0, 0, 0);
+            return;
+        }
         const long long off = grow * C + cb * 64 + eseg * 8;
         rx = *reinterpret_cast<const uint4*>(x + off);
         rp = first ? make_uint4(0, 0, 0, 0) : *reinterpret_cast<const uint4*>(x + off - C);
@@ -99,6 +104,7 @@ __global__ void __launch_bounds__(256) ddlerp_bwd_dpre_kernel(DdlerpBwdParams p)
     for (int j = 0; j < D / 8; ++j)
 #pragma unroll
         for (int hrow = 0; hrow < 2; ++hrow) {
+            if (row0 + 16 * wmt + g + 8 * hrow >= p.rows) continue;
             const long long off = (row0 + 16 * wmt + g + 8 * hrow) * (4 * D) + wk * D + 8 * j + 2 * t4;
             const float2 mv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(m + off));
             *reinterpret_cast<uint32_t*>(dp + off) =
@@ -153,22 +159,29 @@ __global__ void __launch_bounds__(256) ddlerp_bwd_main_kernel(DdlerpBwdParams p)
     float dR2[D / 8][4] = {};
     float dal[2][2] = {}, dbe[4][2][2] = {};
 
-    for (int t0 = T - 32; t0 >= 0; t0 -= 32) {
+    for (int t0 = ((T - 1) / 32) * 32; t0 >= 0; t0 -= 32) {
         const long long r0 = b0 + t0;
+        const int nrow = T - t0 < 32 ? T - t0 : 32;  // live rows of this tile (the last one may be short)
         // ---- loads -----------------------------------------------------------------------------
         for (int i = tid; i < 33 * 8; i += 256) {
             const int r = i / 8, ch = i % 8;
-            if (t0 == 0 && r == 0) *reinterpret_cast<uint4*>(&sm.xS[0][ch * 8]) = make_uint4(0, 0, 0, 0);
+            if ((t0 == 0 && r == 0) || r > nrow) *reinterpret_cast<uint4*>(&sm.xS[r][ch * 8]) = make_uint4(0, 0, 0, 0);
             else cp_async16(&sm.xS[r][ch * 8], x + (r0 + r - 1) * C + cb * 64 + ch * 8);
         }
         for (int i = tid; i < 4 * 32 * 8; i += 256) {
             const int k = i / 256, r = (i / 8) % 32, ch = i % 8;
-            cp_async16(&sm.dyS[k][r][ch * 8], (const bf16*)p.dy[k] + (r0 + r) * C + cb * 64 + ch * 8);
+            if (r >= nrow) *reinterpret_cast<uint4*>(&sm.dyS[k][r][ch * 8]) = make_uint4(0, 0, 0, 0);
+            else cp_async16(&sm.dyS[k][r][ch * 8], (const bf16*)p.dy[k] + (r0 + r) * C + cb * 64 + ch * 8);
         }
         for (int i = tid; i < 32 * (4 * D / 8); i += 256) {
             const int r = i / (4 * D / 8), ch = i % (4 * D / 8);
-            cp_async16(&sm.mS[r][ch * 8], (const bf16*)p.m + (r0 + r) * (4 * D) + ch * 8);
-            cp_async16(&sm.dpS[r][ch * 8], (const bf16*)p.dpre + (r0 + r) * (4 * D) + ch * 8);
+            if (r >= nrow) {
+                *reinterpret_cast<uint4*>(&sm.mS[r][ch * 8]) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(&sm.dpS[r][ch * 8]) = make_uint4(0, 0, 0, 0);
+            } else {
+                cp_async16(&sm.mS[r][ch * 8], (const bf16*)p.m + (r0 + r) * (4 * D) + ch * 8);
+                cp_async16(&sm.dpS[r][ch * 8], (const bf16*)p.dpre + (r0 + r) * (4 * D) + ch * 8);
+            }
         }
         cp_async_commit();
         cp_async_wait<0>();
@@ -260,7 +273,8 @@ __global__ void __launch_bounds__(256) ddlerp_bwd_main_kernel(DdlerpBwdParams p)
         // ---- dx out (coalesced), carry X_{t0} for the previous tile ----------------------------------
         {
             const int r = tid >> 3, ch = tid & 7;
-            *reinterpret_cast<uint4*>((bf16*)p.dx + (r0 + r) * C + cb * 64 + ch * 8) = *reinterpret_cast<const uint4*>(&sm.dxS[r][ch * 8]);
+            if (r < nrow)
+                *reinterpret_cast<uint4*>((bf16*)p.dx + (r0 + r) * C + cb * 64 + ch * 8) = *reinterpret_cast<const uint4*>(&sm.dxS[r][ch * 8]);
         }
         if (tid < 64) sm.XS[32][tid] = sm.XS[0][tid];
         __syncthreads();
@@ -326,14 +340,20 @@ __global__ void __launch_bounds__(256) ddlerp_bwd_dL_kernel(DdlerpBwdParams p, l
     for (long long r0 = rbeg; r0 < rend; r0 += 64) {
         const long long grow = r0 + erow;
         {
+            const bool live = grow < p.rows;
             const bool first = (grow % p.T) == 0;
             const uint4* a = reinterpret_cast<const uint4*>(x + grow * C + cb * 64 + eseg * 16);
             const uint4* b = reinterpret_cast<const uint4*>(x + (grow - 1) * C + cb * 64 + eseg * 16);
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 float xv[8], pv[8], uv[8];
-                unpack8(a[h], xv);
-                if (first) {
+                if (live) {
+                    unpack8(a[h], xv);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) xv[i] = 0.f;
+                }
+                if (first || !live) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) pv[i] = 0.f;
                 } else {
@@ -346,7 +366,8 @@ __global__ void __launch_bounds__(256) ddlerp_bwd_dL_kernel(DdlerpBwdParams p, l
         }
         for (int i = tid; i < 64 * (4 * D / 8); i += 256) {
             const int r = i / (4 * D / 8), ch = i % (4 * D / 8);
-            cp_async16(&sm.dpS[r][ch * 8], (const bf16*)p.dpre + (r0 + r) * (4 * D) + ch * 8);
+            if (r0 + r >= p.rows) *reinterpret_cast<uint4*>(&sm.dpS[r][ch * 8]) = make_uint4(0, 0, 0, 0);
+            else cp_async16(&sm.dpS[r][ch * 8], (const bf16*)p.dpre + (r0 + r) * (4 * D) + ch * 8);
         }
         cp_async_commit();
         cp_async_wait<0>();
@@ -395,7 +416,7 @@ template <int D> static int launch_ddlerp_bwd_t(const DdlerpBwdParams& p, cudaSt
         auto kern = ddlerp_bwd_dpre_kernel<D>;
         const int smem = (int)sizeof(DpreSmem<D>);
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kLaunchFailed;
-        kern<<<(unsigned)(p.rows / 32), 256, smem, stream>>>(p);
+        kern<<<(unsigned)((p.rows + 31) / 32), 256, smem, stream>>>(p);
         if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
     }
     {
@@ -411,7 +432,7 @@ template <int D> static int launch_ddlerp_bwd_t(const DdlerpBwdParams& p, cudaSt
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kLaunchFailed;
         // about two CTAs per SM in total; segments are whole 64-row tiles
         long long segs = (2 * 148 + C / 64 - 1) / (C / 64);
-        long long tiles = p.rows / 64;
+        long long tiles = (p.rows + 63) / 64;
         if (segs > tiles) segs = tiles;
         const long long rows_per_seg = ((tiles + segs - 1) / segs) * 64;
         segs = (p.rows + rows_per_seg - 1) / rows_per_seg;

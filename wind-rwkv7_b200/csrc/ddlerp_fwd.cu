@@ -47,10 +47,15 @@ __global__ void __launch_bounds__(256) ddlerp_fwd_kernel(DdlerpFwdParams p) {
     // elementwise mapping: 4 threads per token row, 16 channels each
     const int erow = tid >> 2, eseg = tid & 3;
     const long long grow = row0 + erow;
+    const bool live = grow < p.rows;       // the last tile may be partly empty
     const bool first = (grow % p.T) == 0;  // first token of a sequence: previous token is zero
     const bf16* xrow = x + grow * C + eseg * 16;
 
     auto load_x = [&](int kb, uint4 (&xr)[2], uint4 (&xp)[2]) {
+        if (!live) {
+            xr[0] = xr[1] = xp[0] = xp[1] = make_uint4(0, 0, 0, 0);
+            return;
+        }
         const uint4* a = reinterpret_cast<const uint4*>(xrow + kb * DKB);
         xr[0] = a[0]; xr[1] = a[1];
         if (first) {
@@ -118,7 +123,7 @@ __global__ void __launch_bounds__(256) ddlerp_fwd_kernel(DdlerpFwdParams p) {
             *reinterpret_cast<uint32_t*>(&sm.mT[r + 8][col]) = pack_bf16x2(tanh_f(acc[i][j][2]), tanh_f(acc[i][j][3]));
         }
     __syncthreads();  // mT complete; phase-1 buffers free
-    {
+    if (live) {
         bf16* mo = (bf16*)p.m + grow * (4 * D) + eseg * D;
 #pragma unroll
         for (int i = 0; i < D / 8; ++i)
@@ -181,7 +186,7 @@ __global__ void __launch_bounds__(256) ddlerp_fwd_kernel(DdlerpFwdParams p) {
         }
         __syncthreads();
 #pragma unroll
-        for (int kk = 0; kk < 2; ++kk) {
+        for (int kk = 0; kk < 2 && live; ++kk) {
             bf16* yo = (bf16*)p.y + ((long long)(2 * kp + kk) * p.rows + grow) * C + cb * DKB + eseg * 16;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -201,7 +206,7 @@ template <int D> static int launch_ddlerp_fwd_t(const DdlerpFwdParams& p, cudaSt
     auto kern = ddlerp_fwd_kernel<D>;
     const int smem = (int)sizeof(DdlerpFwdSmem<D>);
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kLaunchFailed;
-    kern<<<(unsigned)(p.rows / DT), 256, smem, stream>>>(p);
+    kern<<<(unsigned)((p.rows + DT - 1) / DT), 256, smem, stream>>>(p);
     return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
 

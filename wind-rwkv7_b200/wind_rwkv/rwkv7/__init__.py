@@ -4,4 +4,16 @@ from .rwkv7_expand_loras import expand_loras
 from .rwkv7_attn import attn, load_attn
 from .rwkv7_attn_ln import attn_ln, load_attn_ln
 
+from .time_mixer import TimeMixer
+
+
+def _excluded(name):
+    def f(*a, **k):
+        raise NotImplementedError(f'{name} is the reference\'s Triton backend; this build has one backend (sm_100a CUDA): use attn()')
+    return f
+
+
+attn_triton = _excluded('attn_triton')
+attn_triton_bighead = _excluded('attn_triton_bighead')
+
 __version__ = '0.1'

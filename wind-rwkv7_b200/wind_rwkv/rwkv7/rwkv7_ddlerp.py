@@ -19,7 +19,7 @@ class DDLerp(th.autograd.Function):
         D = R.shape[2]
         assert list(alpha.shape) == [C] and list(beta.shape) == [4, 1, 1, C]
         assert list(L.shape) == [4 * D, C] and list(R.shape) == [4, C, D]
-        assert T % 64 == 0 and C % 64 == 0, 'ddlerp needs T % 64 == 0 and C % 64 == 0'
+        assert C % 64 == 0, 'ddlerp needs C % 64 == 0'
         x = x.contiguous()
         Lb, Rb, ab, bb = [i.detach().to(th.bfloat16).contiguous() for i in [L, R, alpha, beta]]
         m = th.empty(B, T, 4 * D, dtype=th.bfloat16, device=x.device)
