@@ -213,3 +213,24 @@ def test_config1_full_size_properties():
     for n, x, ref in zip(NAMES, sub, go):
         check('d' + n, x.grad, ref, th.bfloat16)
     assert _lib.device_status() == 0
+
+
+def test_config4_long_context_prefill():
+    """T = 65536 with a non-zero fp32 initial state (the 2.9B prefill shape, H = 40) on one batch
+    entry: forward only, no checkpoints; y and the final state against the oracle, and the chained
+    property (two 32768-step calls) bit for bit."""
+    c_oracle, _lib, attn, synthetic, _ = _mods()
+    B, T, H = 1, 65536, 40
+    d = synthetic.wkv7_inputs(B, T, H, N, seed=4, dtype=th.bfloat16, device='cuda', s0_std=0.1)
+    ins = [d[n] for n in NAMES]
+    with th.no_grad():
+        y, sT = attn(*ins, N, s0=d['s0'], return_state=True)
+        y1, s1 = attn(*[x[:, :T // 2].contiguous() for x in ins], N, s0=d['s0'], return_state=True)
+        y2, s2 = attn(*[x[:, T // 2:].contiguous() for x in ins], N, s0=s1, return_state=True)
+    assert th.equal(th.cat([y1, y2], 1), y) and th.equal(s2, sT)
+    hs = slice(0, 4 * N)  # four heads through the oracle
+    cpu = [x[:, :, hs].double().cpu().numpy().reshape(B, T, 4, N) for x in ins]
+    yo, sTo = c_oracle.wkv7_fwd(*cpu, s0=d['s0'][:, :4].double().cpu().numpy())
+    check('y', y[:, :, hs], yo, th.bfloat16)
+    assert maxabs_rms(sT[:, :4], sTo) <= 2e-2
+    assert _lib.device_status() == 0

@@ -16,8 +16,10 @@ def _same_layout(ts):
     return all(t.stride() == s and t.stride(3) == 1 for t in ts)
 
 
-def fw_attn(w, q, k, v, a, b, s0):
-    """Forward launcher (upstream: rwkv7_attn.py:5-11). Returns y, sT (fp32), s (fp32 checkpoints)."""
+def fw_attn(w, q, k, v, a, b, s0, save_checkpoints=True):
+    """Forward launcher (upstream: rwkv7_attn.py:5-11). Returns y, sT (fp32), s (fp32 checkpoints).
+    With save_checkpoints=False (no backward will follow) the checkpoint tensor is empty and the
+    kernel skips its stores."""
     B, T, H, C = w.shape
     _lib.require_cuda(w, q, k, v, a, b, s0)
     if not _same_layout([w, q, k, v, a, b]):
@@ -26,10 +28,10 @@ def fw_attn(w, q, k, v, a, b, s0):
     if y.stride() != v.stride():
         y = th.empty_strided(v.shape, v.stride(), dtype=v.dtype, device=v.device)
     sT = th.empty(B, H, C, C, dtype=th.float32, device=w.device)
-    s = th.empty(B, H, T // _lib.CHUNK, C, C, dtype=th.float32, device=w.device)
+    s = th.empty(B, H, T // _lib.CHUNK if save_checkpoints else 0, C, C, dtype=th.float32, device=w.device)
     sb, st, sh = _lib.strides4(w)
     rc = _lib.lib().wkv7_fwd(q.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
-                             _lib.ptr(s0), y.data_ptr(), sT.data_ptr(), s.data_ptr(),
+                             _lib.ptr(s0), y.data_ptr(), sT.data_ptr(), s.data_ptr() if save_checkpoints else None,
                              B, T, H, C, sb, st, sh, _lib.io_dtype(w), _lib.stream_of(w))
     _lib.check(rc, 'wkv7_fwd')
     return y, sT, s
@@ -71,7 +73,7 @@ class WindRWKV7(th.autograd.Function):
     def forward(ctx, w, q, k, v, a, b, s0):
         _check_inputs(w, q, k, v, a, b, s0)
         s0f = None if s0 is None else s0.float().contiguous()
-        y, sT, s = fw_attn(w, q, k, v, a, b, s0f)
+        y, sT, s = fw_attn(w, q, k, v, a, b, s0f, save_checkpoints=any(ctx.needs_input_grad))
         ctx.save_for_backward(w, q, k, v, a, b, s, sT)
         ctx.s0_dtype = None if s0 is None else s0.dtype
         ctx.mark_non_differentiable(s)

@@ -12,19 +12,19 @@ from .rwkv7_attn import _check_inputs, _same_layout
 EPS = 64e-5
 
 
-def fw_attn_ln(w, q, k, v, a, b, g, params, s0):
-    """Forward launcher (upstream: rwkv7_attn_ln.py:5-11)."""
+def fw_attn_ln(w, q, k, v, a, b, g, params, s0, save_checkpoints=True):
+    """Forward launcher (upstream: rwkv7_attn_ln.py:5-11); save_checkpoints as in rwkv7_attn.fw_attn."""
     B, T, H, C = w.shape
     _lib.require_cuda(w, q, k, v, a, b, g, params, s0)
     if not _same_layout([w, q, k, v, a, b, g]):
         w, q, k, v, a, b, g = [i.contiguous() for i in (w, q, k, v, a, b, g)]
     y = th.empty_strided(v.shape, v.stride(), dtype=v.dtype, device=v.device)
     sT = th.empty(B, H, C, C, dtype=th.float32, device=w.device)
-    s = th.empty(B, H, T // _lib.CHUNK, C, C, dtype=th.float32, device=w.device)
+    s = th.empty(B, H, T // _lib.CHUNK if save_checkpoints else 0, C, C, dtype=th.float32, device=w.device)
     sb, st, sh = _lib.strides4(w)
     rc = _lib.lib().wkv7_attn_ln_fwd(q.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(),
                                      b.data_ptr(), g.data_ptr(), params.data_ptr(), _lib.ptr(s0), y.data_ptr(),
-                                     sT.data_ptr(), s.data_ptr(), EPS, B, T, H, C, sb, st, sh,
+                                     sT.data_ptr(), s.data_ptr() if save_checkpoints else None, EPS, B, T, H, C, sb, st, sh,
                                      _lib.io_dtype(w), _lib.stream_of(w))
     _lib.check(rc, 'wkv7_attn_ln_fwd')
     return y, sT, s
@@ -61,7 +61,7 @@ class WindRWKV7(th.autograd.Function):
         assert params.dtype == th.float32 and list(params.shape) == [3, H * C]
         params = params.contiguous()
         s0f = None if s0 is None else s0.float().contiguous()
-        y, sT, s = fw_attn_ln(w, q, k, v, a, b, g, params, s0f)
+        y, sT, s = fw_attn_ln(w, q, k, v, a, b, g, params, s0f, save_checkpoints=any(ctx.needs_input_grad))
         ctx.save_for_backward(w, q, k, v, a, b, g, params, s, sT)
         ctx.s0_dtype = None if s0 is None else s0.dtype
         ctx.mark_non_differentiable(s)
