@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "wkv7_common.cuh"
+
 namespace wkv7 {
 
 using bf16 = __nv_bfloat16;
@@ -44,7 +46,7 @@ __device__ __forceinline__ void ldB_nk(uint32_t (&b)[2], const bf16* p, int ld, 
     b[1] = *reinterpret_cast<const uint32_t*>(r0 + 8);
 }
 
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return smem_u32(p); }
 
 // B fragment from shared memory laid out [k][n] (row = contraction index): transposing ldmatrix.
 // Rows k0..k0+15, columns n0..n0+7; rows must be 16-byte aligned.
@@ -62,12 +64,6 @@ __device__ __forceinline__ void ldA_km_trans(uint32_t (&a)[4], const bf16* p, in
                  : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
                  : "r"(smem_addr(row)));
 }
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(smem)), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ float tanh_f(float x) { return 1.f - 2.f / (__expf(2.f * x) + 1.f); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }

@@ -40,11 +40,14 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 // ---- TF32 operands ---------------------------------------------------------------------------
 // PREC == 1: one TF32 MMA per product (operands rounded to 10 mantissa bits, fp32 accumulate).
 // PREC == 3: hi/lo split, three MMAs per product (error ~2^-21: the fp32 path).
-__device__ __forceinline__ uint32_t tf32_rna(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return r;
-}
+// Round to nearest (ties away from zero) to 10 mantissa bits with two integer instructions.  The
+// conversion instruction (cvt.rna.tf32.f32) and MUFU share the XU pipe, which profiling showed
+// ~90% busy in these kernels; integer adds run on a pipe with headroom.  Finite inputs only.
+__device__ __forceinline__ uint32_t tf32_rna(float x) { return (__float_as_uint(x) + 0x1000u) & 0xffffe000u; }
+
+// Value as it is kept in shared memory for later use as an MMA operand: in the single-TF32 class
+// it is rounded once by its producer, so that the (many) consumers need no conversion.
+template <int PREC> __device__ __forceinline__ float pre(float x) { return PREC == 1 ? __uint_as_float(tf32_rna(x)) : x; }
 
 template <int PREC> struct Op {  // one scalar operand
     uint32_t h, l;
@@ -53,6 +56,12 @@ template <int PREC> struct Op {  // one scalar operand
         if (PREC == 3) l = tf32_rna(x - __uint_as_float(h));
         else l = 0;
     }
+    // x was stored through pre<PREC>() or is exactly representable in TF32 (a bf16 value)
+    __device__ __forceinline__ void setr(float x) {
+        if (PREC == 1) { h = __float_as_uint(x); l = 0; }
+        else set(x);
+    }
+    template <bool R> __device__ __forceinline__ void put(float x) { if (R) setr(x); else set(x); }
 };
 
 template <int PREC> struct FragA { Op<PREC> x[4]; };  // 16x8, (g,t) (g+8,t) (g,t+4) (g+8,t+4)
@@ -92,40 +101,155 @@ template <int PREC> __device__ __forceinline__ FragA<PREC> fragA_from_acc(const 
 }
 
 // A operand from memory laid out [m][k] (row stride ld floats), rows m0+g, m0+g+8, block k0.
-template <int PREC>
+// The loaders' last template argument R says the source was stored through pre<PREC>().
+template <int PREC, bool R = false>
 __device__ __forceinline__ FragA<PREC> fragA_mk(const float* p, int ld, int m0, int k0, int g, int t) {
     FragA<PREC> f;
     float2 lo = *reinterpret_cast<const float2*>(p + (m0 + g) * ld + k0 + 2 * t);
     float2 hi = *reinterpret_cast<const float2*>(p + (m0 + g + 8) * ld + k0 + 2 * t);
-    f.x[0].set(lo.x); f.x[1].set(hi.x); f.x[2].set(lo.y); f.x[3].set(hi.y);
+    f.x[0].template put<R>(lo.x); f.x[1].template put<R>(hi.x); f.x[2].template put<R>(lo.y); f.x[3].template put<R>(hi.y);
     return f;
 }
 
 // A operand from memory laid out [k][m] (the transpose), rows k0+2t, k0+2t+1, columns m0+g, m0+g+8.
-template <int PREC>
+template <int PREC, bool R = false>
 __device__ __forceinline__ FragA<PREC> fragA_km(const float* p, int ld, int m0, int k0, int g, int t) {
     FragA<PREC> f;
     const float* r0 = p + (k0 + 2 * t) * ld + m0 + g;
-    f.x[0].set(r0[0]); f.x[1].set(r0[8]); f.x[2].set(r0[ld]); f.x[3].set(r0[ld + 8]);
+    f.x[0].template put<R>(r0[0]); f.x[1].template put<R>(r0[8]); f.x[2].template put<R>(r0[ld]); f.x[3].template put<R>(r0[ld + 8]);
     return f;
 }
 
 // B operand from memory laid out [n][k]: row n0+g, block k0 (one 8-byte load).
-template <int PREC>
+template <int PREC, bool R = false>
 __device__ __forceinline__ FragB<PREC> fragB_nk(const float* p, int ld, int n0, int k0, int g, int t) {
     FragB<PREC> f;
     float2 v = *reinterpret_cast<const float2*>(p + (n0 + g) * ld + k0 + 2 * t);
-    f.x[0].set(v.x); f.x[1].set(v.y);
+    f.x[0].template put<R>(v.x); f.x[1].template put<R>(v.y);
     return f;
 }
 
 // B operand from memory laid out [k][n]: rows k0+2t, k0+2t+1, column n0+g.
-template <int PREC>
+template <int PREC, bool R = false>
 __device__ __forceinline__ FragB<PREC> fragB_kn(const float* p, int ld, int n0, int k0, int g, int t) {
     FragB<PREC> f;
     const float* r0 = p + (k0 + 2 * t) * ld + n0 + g;
-    f.x[0].set(r0[0]); f.x[1].set(r0[ld]);
+    f.x[0].template put<R>(r0[0]); f.x[1].template put<R>(r0[ld]);
     return f;
+}
+
+// exp(x) on the FMA and integer pipes only (no MUFU): 2^t with t = x*log2(e) split into a rounded
+// integer part (added to the exponent field) and a fraction in [-0.5, 0.5] (degree-6 polynomial,
+// relative error ~2e-7).  t is clamped to +-125, so the result never leaves the normal range.
+__device__ __forceinline__ float exp_poly(float x) {
+    float t = fminf(fmaxf(x * 1.4426950408889634f, -125.f), 125.f);
+    const float tm = t + 12582912.f;  // 1.5 * 2^23: the low mantissa bits of tm hold round(t)
+    const float f = t - (tm - 12582912.f);
+    float p = 1.5403530e-4f;
+    p = fmaf(p, f, 1.3333558e-3f);
+    p = fmaf(p, f, 9.6181291e-3f);
+    p = fmaf(p, f, 5.5504109e-2f);
+    p = fmaf(p, f, 2.4022651e-1f);
+    p = fmaf(p, f, 6.9314718e-1f);
+    p = fmaf(p, f, 1.f);
+    return __int_as_float(__float_as_int(p) + ((__float_as_int(tm) - 0x4B400000) << 23));
+}
+// exp() by precision class: polynomial for the single-TF32 class, libdevice expf for the fp32 class.
+template <int PREC> __device__ __forceinline__ float exp_p(float x) { return PREC == 3 ? expf(x) : exp_poly(x); }
+
+// ---- decay scan (state-independent chunk preparation, shared by forward and backward) ----------
+// 8 consecutive IO elements (16 or 32 bytes) -> floats
+template <typename T> __device__ __forceinline__ void load8(const unsigned char* p, float (&f)[8]);
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const unsigned char* p, float (&f)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+template <> __device__ __forceinline__ void load8<float>(const unsigned char* p, float (&f)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 16);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+__device__ __forceinline__ void store8(float* p, const float (&f)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
+
+// One thread = one time step x 8 adjacent key channels (lane = row + 16 * channel-half, warp =
+// 16-channel group).  The running log-decay along the 16 time rows is a 4-step warp-shuffle scan,
+// eight independent channels per thread keep the pipes busy, and all shared-memory traffic is 16
+// bytes wide.  Writes wq = q*P_t, wa = a*P_{t-1}, kwi = k/P_t, bwi = b/P_t (row stride OPS), the
+// chunk decay fw = P_L, and optionally the running log-decay and the per-step log-decay.
+// tq/tw/tk/ta/tb: staging tiles with row stride `rowb` bytes.
+template <typename IoT, int PREC>
+__device__ __forceinline__ void decay_scan(const unsigned char* tq, const unsigned char* tw, const unsigned char* tk,
+                                           const unsigned char* ta, const unsigned char* tb, int rowb, float* wq, float* wa,
+                                           float* kwi, float* bwi, float* fw, float* cum_out, float* lw_out, int warp, int lane) {
+    const int row = lane & 15, j0 = 16 * warp + 8 * (lane >> 4);
+    const int off = row * rowb + j0 * (int)sizeof(IoT);
+    float lw[8], cum[8], q[8], k[8], a[8], b[8];
+    load8<IoT>(tw + off, lw);
+    load8<IoT>(tq + off, q);
+    load8<IoT>(tk + off, k);
+    load8<IoT>(ta + off, a);
+    load8<IoT>(tb + off, b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { lw[i] = -exp_p<PREC>(lw[i]); cum[i] = lw[i]; }
+#pragma unroll
+    for (int d = 1; d < 16; d <<= 1)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float up = __shfl_up_sync(0xffffffffu, cum[i], d, 16);
+            if (row >= d) cum[i] += up;
+        }
+    float o[4][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float incl = exp_p<PREC>(cum[i]), inv = exp_p<PREC>(-cum[i]), non = exp_p<PREC>(cum[i] - lw[i]);
+        o[0][i] = pre<PREC>(q[i] * incl);
+        o[1][i] = pre<PREC>(a[i] * non);
+        o[2][i] = pre<PREC>(k[i] * inv);
+        o[3][i] = pre<PREC>(b[i] * inv);
+        if (row == 15) fw[j0 + i] = incl;
+    }
+    store8(wq + row * OPS + j0, o[0]);
+    store8(wa + row * OPS + j0, o[1]);
+    store8(kwi + row * OPS + j0, o[2]);
+    store8(bwi + row * OPS + j0, o[3]);
+    if (cum_out) store8(cum_out + row * OPS + j0, cum);
+    if (lw_out) store8(lw_out + row * OPS + j0, lw);
+}
+
+// Column `col` of AI = (I - AB)^-1 for a strictly lower-triangular 16x16 AB, one lane per column.
+// ABt holds AB TRANSPOSED (ABt[s][tq] = AB[tq][s], row stride SCS), so that everything step s needs
+// is one contiguous row.  Right-looking substitution: as soon as entry s is final it is pushed
+// into all later rows, so the dependent chain is 16 steps long rather than 120.
+template <int PREC> __device__ __forceinline__ void tri_inverse_column(const float* ABt, float* AI, int col) {
+    float r[L];
+#pragma unroll
+    for (int tq = 0; tq < L; ++tq) r[tq] = (tq == col) ? 1.f : 0.f;
+    float c[L], cn[L];  // row s of ABt, and row s+1 fetched one step ahead of its use
+    auto fetch = [&](float (&dst)[L], int s) {
+#pragma unroll
+        for (int v = 0; v < L / 4; ++v) {
+            const float4 x = *reinterpret_cast<const float4*>(ABt + s * SCS + 4 * v);
+            dst[4 * v] = x.x; dst[4 * v + 1] = x.y; dst[4 * v + 2] = x.z; dst[4 * v + 3] = x.w;
+        }
+    };
+    fetch(c, 0);
+#pragma unroll
+    for (int s = 0; s < L; ++s) {
+        if (s + 1 < L) fetch(cn, s + 1);
+        const float ms = r[s];
+        AI[s * SCS + col] = pre<PREC>(ms);
+#pragma unroll
+        for (int tq = s + 1; tq < L; ++tq) r[tq] = fmaf(c[tq], ms, r[tq]);
+#pragma unroll
+        for (int tq = 0; tq < L; ++tq) c[tq] = cn[tq];
+    }
 }
 
 // ---- mbarrier + bulk async copy (TMA engine, untiled) -----------------------------------------
@@ -170,8 +294,13 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
                  : "memory");
 }
 
-// exp() by precision class: the single-TF32 path tolerates the fast intrinsic.
-template <int PREC> __device__ __forceinline__ float exp_p(float x) { return PREC == 3 ? expf(x) : __expf(x); }
+// 16-byte asynchronous copy global -> shared through the load/store unit (no TMA request)
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N_> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N_) : "memory"); }
+
 
 // Tensor addressing shared by all launchers: element (b,t,h,0) of a [B,T,H,N] tensor.
 struct Strides {

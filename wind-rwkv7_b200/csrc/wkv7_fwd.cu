@@ -17,6 +17,9 @@
 //     S' = (S0 + V^T kwi + U^T bwi) * fw[None,:]
 // Inputs arrive through bulk-async row copies (TMA engine) completing on mbarriers.
 #include "wkv7_kernels.h"
+#ifdef WKV7_TIMING
+#include <cstdio>
+#endif
 
 namespace wkv7 {
 
@@ -75,30 +78,31 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
     }
     __syncthreads();
 
-    // Producer: warp 0 issues one bulk copy per 16-step row of every input tensor.
+    // EXPERIMENT: all threads fetch 16-byte pieces with cp.async
+    constexpr int CH = ROW_BYTES / 16;
     auto issue_in = [&](int c) {
-        if (lane == 0) mbar_arrive_expect_tx(&sm.bar_in, 5 * L * ROW_BYTES);
-        __syncwarp();
-        for (int i = lane; i < 5 * L; i += 32) {
-            int ten = i / L, row = i % L;
-            bulk_g2s(sm.st_in[ten] + row * Lay::ROWB, gin[ten] + ((long long)c * L + row) * p.st.t, ROW_BYTES, &sm.bar_in);
+        for (int i = tid; i < 5 * L * CH; i += THREADS) {
+            int ten = i / (L * CH), row = (i / CH) % L, ch = i % CH;
+            cp_async16(sm.st_in[ten] + row * Lay::ROWB + ch * 16,
+                       reinterpret_cast<const unsigned char*>(gin[ten] + ((long long)c * L + row) * p.st.t) + ch * 16);
         }
     };
     auto issue_v = [&](int c) {
         int s = c & 1;
-        if (lane == 0) mbar_arrive_expect_tx(&sm.bar_v[s], (LN ? 2 : 1) * L * ROW_BYTES);
-        __syncwarp();
-        for (int i = lane; i < (LN ? 2 : 1) * L; i += 32) {
-            int ten = i / L, row = i % L;
+        for (int i = tid; i < (LN ? 2 : 1) * L * CH; i += THREADS) {
+            int ten = i / (L * CH), row = (i / CH) % L, ch = i % CH;
             const IoT* src = (ten == 0 ? gv : gg) + ((long long)c * L + row) * p.st.t;
             unsigned char* dst = (ten == 0 ? sm.st_v[s] : sm.st_g[LN ? s : 0]) + row * Lay::ROWB;
-            bulk_g2s(dst, src, ROW_BYTES, &sm.bar_v[s]);
+            cp_async16(dst + ch * 16, reinterpret_cast<const unsigned char*>(src) + ch * 16);
         }
     };
-    if (warp == 0 && nchunks > 0) {
+    if (nchunks > 0) {
         issue_in(0);
         issue_v(0);
+        cp_async_commit();
+        cp_async_wait<0>();
     }
+    __syncthreads();
 
     // State: warp owns value rows 16*warp + {g, g+8}; tile nt covers key columns 8nt..8nt+7,
     // thread holds columns 8nt+2*t4, +1.
@@ -117,29 +121,19 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
         }
     }
 
+#ifdef WKV7_TIMING
+    long long tacc[8] = {}, tprev = clock64();
+#define TICK(i) { long long now_ = clock64(); tacc[i] += now_ - tprev; tprev = now_; }
+#else
+#define TICK(i)
+#endif
     bool failed = false;
     for (int c = 0; c < nchunks; ++c) {
         // ---------------- P1: decay scan and scaled operands (thread = key channel x half) ------
-        bool ok = mbar_wait(&sm.bar_in, c & 1);
+        bool ok = true;
         {
-            const int j = tid & 63, half = tid >> 6;
-            float cum = 0.f;
-            if (half)
-#pragma unroll
-                for (int r = 0; r < 8; ++r) cum -= exp_p<PREC>(st_elem<IoT>(sm.st_in[1], r, j));
-            float prev = half ? exp_p<PREC>(cum) : 1.f;
-#pragma unroll
-            for (int r8 = 0; r8 < 8; ++r8) {
-                const int r = half * 8 + r8;
-                cum -= exp_p<PREC>(st_elem<IoT>(sm.st_in[1], r, j));
-                const float incl = exp_p<PREC>(cum), inv = exp_p<PREC>(-cum);
-                sm.wq[r * OPS + j] = st_elem<IoT>(sm.st_in[0], r, j) * incl;
-                sm.wa[r * OPS + j] = st_elem<IoT>(sm.st_in[3], r, j) * prev;
-                sm.kwi[r * OPS + j] = st_elem<IoT>(sm.st_in[2], r, j) * inv;
-                sm.bwi[r * OPS + j] = st_elem<IoT>(sm.st_in[4], r, j) * inv;
-                prev = incl;
-            }
-            if (half) sm.fw[j] = prev;
+            decay_scan<IoT, PREC>(sm.st_in[0], sm.st_in[1], sm.st_in[2], sm.st_in[3], sm.st_in[4], Lay::ROWB, sm.wq, sm.wa,
+                                  sm.kwi, sm.bwi, sm.fw, nullptr, nullptr, warp, lane);
             if (LN) {  // bonus dot  sum_j r_j k_j bonus_j  per time step: 8 threads per row
                 const int row = tid >> 3, part = tid & 7;
                 float acc = 0.f;
@@ -154,13 +148,17 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
                 if (part == 0) sm.bdot[row] = acc;
             }
         }
+        TICK(0)
         if (__syncthreads_or(!ok)) { failed = true; break; }  // (A)
+        TICK(1)
 
-        if (warp == 0 && c + 1 < nchunks) {
+        if (c + 1 < nchunks) {
             issue_in(c + 1);
             issue_v(c + 1);
         }
+        cp_async_commit();
 
+        TICK(2)
         // ---------------- P2: masked score matrices, one per warp ------------------------------
         {
             const float* Am = (warp & 1) ? sm.wa : sm.wq;
@@ -170,36 +168,34 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
             float d[2][4] = {};
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
-                FragA<PREC> a = fragA_mk<PREC>(Am, OPS, 0, 8 * kk, g, t4);
+                FragA<PREC> a = fragA_mk<PREC, true>(Am, OPS, 0, 8 * kk, g, t4);
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) mma<PREC>(d[nt], a, fragB_nk<PREC>(Bm, OPS, 8 * nt, 8 * kk, g, t4));
+                for (int nt = 0; nt < 2; ++nt) mma<PREC>(d[nt], a, fragB_nk<PREC, true>(Bm, OPS, 8 * nt, 8 * kk, g, t4));
             }
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 const int s = 8 * nt + 2 * t4;
                 auto keep = [&](int tq, int ss) { return strict ? ss < tq : ss <= tq; };
-                float2 lo = make_float2(keep(g, s) ? d[nt][0] : 0.f, keep(g, s + 1) ? d[nt][1] : 0.f);
-                float2 hi2 = make_float2(keep(g + 8, s) ? d[nt][2] : 0.f, keep(g + 8, s + 1) ? d[nt][3] : 0.f);
-                *reinterpret_cast<float2*>(dst + g * SCS + s) = lo;
-                *reinterpret_cast<float2*>(dst + (g + 8) * SCS + s) = hi2;
+                // AB only feeds the inverse and stays unrounded; the other three are MMA operands
+                auto val = [&](float x) { return warp == 3 ? x : pre<PREC>(x); };
+                float2 lo = make_float2(keep(g, s) ? val(d[nt][0]) : 0.f, keep(g, s + 1) ? val(d[nt][1]) : 0.f);
+                float2 hi2 = make_float2(keep(g + 8, s) ? val(d[nt][2]) : 0.f, keep(g + 8, s + 1) ? val(d[nt][3]) : 0.f);
+                if (warp == 3) {  // AB is kept transposed for the inverse
+                    dst[s * SCS + g] = lo.x; dst[(s + 1) * SCS + g] = lo.y;
+                    dst[s * SCS + g + 8] = hi2.x; dst[(s + 1) * SCS + g + 8] = hi2.y;
+                } else {
+                    *reinterpret_cast<float2*>(dst + g * SCS + s) = lo;
+                    *reinterpret_cast<float2*>(dst + (g + 8) * SCS + s) = hi2;
+                }
             }
         }
         // ---------------- P3: AI = (I - AB)^-1 by forward substitution (the warp that made AB) --
         if (warp == 3) {
             __syncwarp();
-            if (lane < L) {
-                float m[L];
-#pragma unroll
-                for (int tq = 0; tq < L; ++tq) {
-                    float acc = (tq == lane) ? 1.f : 0.f;
-#pragma unroll
-                    for (int s = 0; s < tq; ++s) acc = fmaf(sm.AB[tq * SCS + s], m[s], acc);
-                    m[tq] = acc;
-                    sm.AI[tq * SCS + lane] = acc;
-                }
-            }
+            if (lane < L) tri_inverse_column<PREC>(sm.AB, sm.AI, lane);
         }
 
+        TICK(3)
         // ---------------- chain, part 1: needs only S and the scaled operands ------------------
         if (p.ckpt) {
             float* ck = p.ckpt + (bh * nchunks + c) * (long long)(N * N);
@@ -215,11 +211,13 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
             FragA<PREC> a = fragA_from_acc<PREC>(S[kk]);
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt)
-                mma<PREC>(XY[nt], a, fragB_nk<PREC>(nt < 2 ? sm.wa : sm.wq, OPS, 8 * (nt & 1), 8 * kk, g, t4));
+                mma<PREC>(XY[nt], a, fragB_nk<PREC, true>(nt < 2 ? sm.wa : sm.wq, OPS, 8 * (nt & 1), 8 * kk, g, t4));
         }
 
-        bool okv = mbar_wait(&sm.bar_v[c & 1], (c >> 1) & 1);
+        bool okv = true;
+        TICK(4)
         if (__syncthreads_or(!okv)) { failed = true; break; }  // (B) scores, AI and v visible
+        TICK(5)
 
         // ---------------- chain, part 2 ----------------------------------------------------------
         const unsigned char* vt = sm.st_v[c & 1];
@@ -227,17 +225,18 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk) {
             const int tr = 8 * kk + 2 * t4, vc = 16 * warp + g;
-            vf[kk].x[0].set(st_elem<IoT>(vt, tr, vc));
-            vf[kk].x[1].set(st_elem<IoT>(vt, tr, vc + 8));
-            vf[kk].x[2].set(st_elem<IoT>(vt, tr + 1, vc));
-            vf[kk].x[3].set(st_elem<IoT>(vt, tr + 1, vc + 8));
+            constexpr bool EXACT = sizeof(IoT) == 2;  // a bf16 value is a TF32 value
+            vf[kk].x[0].template put<EXACT>(st_elem<IoT>(vt, tr, vc));
+            vf[kk].x[1].template put<EXACT>(st_elem<IoT>(vt, tr, vc + 8));
+            vf[kk].x[2].template put<EXACT>(st_elem<IoT>(vt, tr + 1, vc));
+            vf[kk].x[3].template put<EXACT>(st_elem<IoT>(vt, tr + 1, vc + 8));
         }
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int kk = 0; kk <= nt; ++kk) {
-                mma<PREC>(XY[nt], vf[kk], fragB_nk<PREC>(sm.AK, SCS, 8 * nt, 8 * kk, g, t4));
-                mma<PREC>(XY[2 + nt], vf[kk], fragB_nk<PREC>(sm.QK, SCS, 8 * nt, 8 * kk, g, t4));
+                mma<PREC>(XY[nt], vf[kk], fragB_nk<PREC, true>(sm.AK, SCS, 8 * nt, 8 * kk, g, t4));
+                mma<PREC>(XY[2 + nt], vf[kk], fragB_nk<PREC, true>(sm.QK, SCS, 8 * nt, 8 * kk, g, t4));
             }
         float U[2][4] = {};
         {
@@ -245,13 +244,13 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                for (int kk = 0; kk <= nt; ++kk) mma<PREC>(U[nt], xa[kk], fragB_nk<PREC>(sm.AI, SCS, 8 * nt, 8 * kk, g, t4));
+                for (int kk = 0; kk <= nt; ++kk) mma<PREC>(U[nt], xa[kk], fragB_nk<PREC, true>(sm.AI, SCS, 8 * nt, 8 * kk, g, t4));
         }
         FragA<PREC> ua[2] = {fragA_from_acc<PREC>(U[0]), fragA_from_acc<PREC>(U[1])};
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int kk = 0; kk <= nt; ++kk) mma<PREC>(XY[2 + nt], ua[kk], fragB_nk<PREC>(sm.QB, SCS, 8 * nt, 8 * kk, g, t4));
+            for (int kk = 0; kk <= nt; ++kk) mma<PREC>(XY[2 + nt], ua[kk], fragB_nk<PREC, true>(sm.QB, SCS, 8 * nt, 8 * kk, g, t4));
 
         // ---------------- output -----------------------------------------------------------------
         if (LN) {
@@ -325,19 +324,27 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
             if (sizeof(IoT) == 4) dst[1] = src[1];
         }
 
+        TICK(6)
         // ---------------- state update -----------------------------------------------------------
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
             for (int kk = 0; kk < 2; ++kk) {
-                mma<PREC>(S[nt], vf[kk], fragB_kn<PREC>(sm.kwi, OPS, 8 * nt, 8 * kk, g, t4));
-                mma<PREC>(S[nt], ua[kk], fragB_kn<PREC>(sm.bwi, OPS, 8 * nt, 8 * kk, g, t4));
+                mma<PREC>(S[nt], vf[kk], fragB_kn<PREC, true>(sm.kwi, OPS, 8 * nt, 8 * kk, g, t4));
+                mma<PREC>(S[nt], ua[kk], fragB_kn<PREC, true>(sm.bwi, OPS, 8 * nt, 8 * kk, g, t4));
             }
             const float2 f = *reinterpret_cast<const float2*>(sm.fw + 8 * nt + 2 * t4);
             S[nt][0] *= f.x; S[nt][1] *= f.y; S[nt][2] *= f.x; S[nt][3] *= f.y;
         }
+        cp_async_wait<0>();
         __syncthreads();  // (E) operand and score buffers are free again
+        TICK(7)
     }
+#ifdef WKV7_TIMING
+    if (blockIdx.x == 0 && (lane == 0))
+        printf("warp %d: P1 %lld | syncA %lld | issue %lld | P2P3 %lld | ckpt+step1 %lld | syncB %lld | steps2-5 %lld | step6+syncE %lld  (cycles per chunk)\n", warp,
+               tacc[0] / nchunks, tacc[1] / nchunks, tacc[2] / nchunks, tacc[3] / nchunks, tacc[4] / nchunks, tacc[5] / nchunks, tacc[6] / nchunks, tacc[7] / nchunks);
+#endif
 
     if (failed) {
         // A bounded wait ran out: record it, give in-flight copies one more bounded chance to
