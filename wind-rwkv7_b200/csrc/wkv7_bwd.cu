@@ -29,6 +29,9 @@
 // Stage C (contractions over the value index, warp owns 16 key columns): the four score
 // gradients and DA, DQ, DB, DK with S0 and dSf read from shared memory.
 #include "wkv7_kernels.h"
+#ifdef WKV7_TIMING
+#include <cstdio>
+#endif
 
 namespace wkv7 {
 
@@ -216,6 +219,12 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
         }
     }
 
+#ifdef WKV7_TIMING
+    long long tacc[10] = {}, tprev = clock64();
+#define TICK(i) { long long now_ = clock64(); tacc[i] += now_ - tprev; tprev = now_; }
+#else
+#define TICK(i)
+#endif
     bool failed = false;
     for (int it = 0; it < nchunks; ++it) {
         const int c = nchunks - 1 - it;
@@ -239,7 +248,9 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
                 if (part == 0) sm.bdot[row] = acc;
             }
         }
+        TICK(0)
         if (__syncthreads_or(!ok)) { failed = true; break; }  // (A)
+        TICK(1)
 
         if (c > 0) {
             issue_in(c - 1);
@@ -281,7 +292,9 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
         }
 
         bool ok2 = true;
+        TICK(2)
         if (__syncthreads_or(!ok2)) { failed = true; break; }  // (B)
+        TICK(3)
 
         // ---------------- stage B: rows = value index -----------------------------------------
         const unsigned char* vt = sm.st_v[vs];
@@ -526,7 +539,9 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             }
             if (g == 0) *reinterpret_cast<float2*>(&sm.Gp[it & 1][warp][8 * nt + 2 * t4]) = make_float2(gx, gy2);
         }
+        TICK(4)
         __syncthreads();  // (C1)
+        TICK(5)
 
         // ---------------- stage C: contractions over the value index --------------------------
         float DA[2][4] = {}, DQ[2][4] = {}, DB[2][4] = {}, DK[2][4] = {};
@@ -565,7 +580,9 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
                     make_float2(keep(g + 8, s) ? pre<PREC>(d[nt][2]) : 0.f, keep(g + 8, s + 1) ? pre<PREC>(d[nt][3]) : 0.f);
             }
         }
+        TICK(6)
         __syncthreads();  // (C2) score gradients visible; S0s free
+        TICK(7)
         if (c > 0) issue_s0(c - 1);
         cp_async_commit();
 
@@ -588,6 +605,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             }
         }
 
+        TICK(8)
         // ---------------- epilogue: thread holds rows g, g+8 x key columns n0+2*t4, +1 ---------
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
@@ -614,7 +632,9 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int i = e + 2 * hrow;
-                    const float incl = exp_p<PREC>(cuv[e]), inv = exp_p<PREC>(-cuv[e]), non = exp_p<PREC>(cuv[e] - lwa[e]);
+                    const float incl = exp_p<PREC>(fmaxf(cuv[e], -80.f));
+                    const float inv = PREC == 3 ? 1.f / incl : rcp_newton(incl);
+                    const float non = exp_p<PREC>(fmaxf(cuv[e] - lwa[e], -80.f));
                     o_a[e] = non * DA[nt][i];
                     o_q[e] = incl * DQ[nt][i];
                     o_b[e] = inv * DB[nt][i];
@@ -661,7 +681,14 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
         }
         cp_async_wait<0>();
         __syncthreads();  // (E)
+        TICK(9)
     }
+#ifdef WKV7_TIMING
+    if (blockIdx.x == 0 && lane == 0)
+        printf("bwd warp %d: P1 %lld | syncA %lld | P2P3 %lld | syncB %lld | stageB %lld | syncC1 %lld | Ca %lld | syncC2 %lld | Cb %lld | epi+syncE %lld\n", warp,
+               tacc[0] / nchunks, tacc[1] / nchunks, tacc[2] / nchunks, tacc[3] / nchunks, tacc[4] / nchunks, tacc[5] / nchunks, tacc[6] / nchunks,
+               tacc[7] / nchunks, tacc[8] / nchunks, tacc[9] / nchunks);
+#endif
 
     if (failed) {
         if (tid == 0) atomicExch(p.status, (int)kDeviceTimeout);

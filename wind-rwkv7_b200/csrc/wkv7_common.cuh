@@ -138,21 +138,32 @@ __device__ __forceinline__ FragB<PREC> fragB_kn(const float* p, int ld, int n0, 
     return f;
 }
 
-// exp(x) on the FMA and integer pipes only (no MUFU): 2^t with t = x*log2(e) split into a rounded
-// integer part (added to the exponent field) and a fraction in [-0.5, 0.5] (degree-6 polynomial,
-// relative error ~2e-7).  t is clamped to +-125, so the result never leaves the normal range.
+// exp(x) on the FMA and integer pipes only.  Measured on B200, one MUFU (ex2 / rcp) warp
+// instruction occupies its pipe for roughly as long as fifteen FMA-pipe instructions, and these
+// kernels need up to four exponentials per input element, so the special-function unit was their
+// bottleneck.  2^t with t = x*log2(e): round(t) goes into the exponent field (the low mantissa bits
+// of t + 1.5*2^23 are round(t); shifted left by 23 they land on the exponent, the constant's own
+// bits fall off the top), the fraction in [-0.5, 0.5] through a degree-5 polynomial (relative
+// error 2e-6, far below TF32 operand rounding).  x is clamped to [-80, 80].
 __device__ __forceinline__ float exp_poly(float x) {
-    float t = fminf(fmaxf(x * 1.4426950408889634f, -125.f), 125.f);
-    const float tm = t + 12582912.f;  // 1.5 * 2^23: the low mantissa bits of tm hold round(t)
+    const float t = fminf(fmaxf(x, -80.f), 80.f) * 1.4426950408889634f;
+    const float tm = t + 12582912.f;
     const float f = t - (tm - 12582912.f);
-    float p = 1.5403530e-4f;
-    p = fmaf(p, f, 1.3333558e-3f);
+    float p = 1.3333558e-3f;
     p = fmaf(p, f, 9.6181291e-3f);
     p = fmaf(p, f, 5.5504109e-2f);
     p = fmaf(p, f, 2.4022651e-1f);
     p = fmaf(p, f, 6.9314718e-1f);
     p = fmaf(p, f, 1.f);
-    return __int_as_float(__float_as_int(p) + ((__float_as_int(tm) - 0x4B400000) << 23));
+    return __int_as_float(__float_as_int(p) + (__float_as_int(tm) << 23));
+}
+// 1/x for positive normal x without MUFU: exponent-flip seed (12% error), three Newton steps.
+__device__ __forceinline__ float rcp_newton(float x) {
+    float y = __int_as_float(0x7EF311C7 - __float_as_int(x));
+    y = y * fmaf(-x, y, 2.f);
+    y = y * fmaf(-x, y, 2.f);
+    y = y * fmaf(-x, y, 2.f);
+    return y;
 }
 // exp() by precision class: polynomial for the single-TF32 class, libdevice expf for the fp32 class.
 template <int PREC> __device__ __forceinline__ float exp_p(float x) { return PREC == 3 ? expf(x) : exp_poly(x); }
@@ -205,10 +216,16 @@ __device__ __forceinline__ void decay_scan(const unsigned char* tq, const unsign
             const float up = __shfl_up_sync(0xffffffffu, cum[i], d, 16);
             if (row >= d) cum[i] += up;
         }
+    // P_t from one exp (argument clamped so that P_t and 1/P_t stay finite), 1/P_t from a
+    // Newton reciprocal, P_{t-1} from the row above.
     float o[4][8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const float incl = exp_p<PREC>(cum[i]), inv = exp_p<PREC>(-cum[i]), non = exp_p<PREC>(cum[i] - lw[i]);
+        const float cc = fmaxf(cum[i], -80.f);
+        const float incl = exp_p<PREC>(cc);
+        const float inv = PREC == 3 ? 1.f / incl : rcp_newton(incl);
+        const float up = __shfl_up_sync(0xffffffffu, incl, 1, 16);
+        const float non = row == 0 ? 1.f : up;
         o[0][i] = pre<PREC>(q[i] * incl);
         o[1][i] = pre<PREC>(a[i] * non);
         o[2][i] = pre<PREC>(k[i] * inv);
@@ -227,29 +244,35 @@ __device__ __forceinline__ void decay_scan(const unsigned char* tq, const unsign
 // ABt holds AB TRANSPOSED (ABt[s][tq] = AB[tq][s], row stride SCS), so that everything step s needs
 // is one contiguous row.  Right-looking substitution: as soon as entry s is final it is pushed
 // into all later rows, so the dependent chain is 16 steps long rather than 120.
+template <int S_> __device__ __forceinline__ void tri_fetch_row(float (&dst)[L], const float* ABt) {
+    // entries tq > S_ of row S_ of ABt, in 16-byte pieces
+#pragma unroll
+    for (int v = (S_ + 1) / 4; v < L / 4; ++v) {
+        const float4 x = *reinterpret_cast<const float4*>(ABt + S_ * SCS + 4 * v);
+        dst[4 * v] = x.x; dst[4 * v + 1] = x.y; dst[4 * v + 2] = x.z; dst[4 * v + 3] = x.w;
+    }
+}
+template <int PREC, int S_>
+__device__ __forceinline__ void tri_step(float (&r)[L], const float (&c)[L], float (&cn)[L], const float* ABt, float* AI, int col) {
+    if (S_ + 1 < L) tri_fetch_row<(S_ + 1 < L ? S_ + 1 : 0)>(cn, ABt);  // one step ahead of its use
+    const float ms = r[S_];
+    AI[S_ * SCS + col] = pre<PREC>(ms);
+#pragma unroll
+    for (int tq = S_ + 1; tq < L; ++tq) r[tq] = fmaf(c[tq], ms, r[tq]);
+}
 template <int PREC> __device__ __forceinline__ void tri_inverse_column(const float* ABt, float* AI, int col) {
-    float r[L];
+    float r[L], ca[L], cb[L];
 #pragma unroll
     for (int tq = 0; tq < L; ++tq) r[tq] = (tq == col) ? 1.f : 0.f;
-    float c[L], cn[L];  // row s of ABt, and row s+1 fetched one step ahead of its use
-    auto fetch = [&](float (&dst)[L], int s) {
-#pragma unroll
-        for (int v = 0; v < L / 4; ++v) {
-            const float4 x = *reinterpret_cast<const float4*>(ABt + s * SCS + 4 * v);
-            dst[4 * v] = x.x; dst[4 * v + 1] = x.y; dst[4 * v + 2] = x.z; dst[4 * v + 3] = x.w;
-        }
-    };
-    fetch(c, 0);
-#pragma unroll
-    for (int s = 0; s < L; ++s) {
-        if (s + 1 < L) fetch(cn, s + 1);
-        const float ms = r[s];
-        AI[s * SCS + col] = pre<PREC>(ms);
-#pragma unroll
-        for (int tq = s + 1; tq < L; ++tq) r[tq] = fmaf(c[tq], ms, r[tq]);
-#pragma unroll
-        for (int tq = 0; tq < L; ++tq) c[tq] = cn[tq];
-    }
+    tri_fetch_row<0>(ca, ABt);
+    tri_step<PREC, 0>(r, ca, cb, ABt, AI, col);   tri_step<PREC, 1>(r, cb, ca, ABt, AI, col);
+    tri_step<PREC, 2>(r, ca, cb, ABt, AI, col);   tri_step<PREC, 3>(r, cb, ca, ABt, AI, col);
+    tri_step<PREC, 4>(r, ca, cb, ABt, AI, col);   tri_step<PREC, 5>(r, cb, ca, ABt, AI, col);
+    tri_step<PREC, 6>(r, ca, cb, ABt, AI, col);   tri_step<PREC, 7>(r, cb, ca, ABt, AI, col);
+    tri_step<PREC, 8>(r, ca, cb, ABt, AI, col);   tri_step<PREC, 9>(r, cb, ca, ABt, AI, col);
+    tri_step<PREC, 10>(r, ca, cb, ABt, AI, col);  tri_step<PREC, 11>(r, cb, ca, ABt, AI, col);
+    tri_step<PREC, 12>(r, ca, cb, ABt, AI, col);  tri_step<PREC, 13>(r, cb, ca, ABt, AI, col);
+    tri_step<PREC, 14>(r, ca, cb, ABt, AI, col);  tri_step<PREC, 15>(r, cb, ca, ABt, AI, col);
 }
 
 // ---- mbarrier + bulk async copy (TMA engine, untiled) -----------------------------------------
