@@ -32,8 +32,8 @@ BWD_BYTES_PER_TOKEN_HEAD = 13 * N * 2   # r,w,k,v,a,b,dy in + six gradients out,
 # Fallback copy of the pool's measured STREAM-style bandwidth, used when MEASURED_PEAKS.json is absent.
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one backward launch at this workload, from the
-# ncu capture summarised under profiles/ (null until captured).
-BWD_DRAM_TRAFFIC_BYTES = None
+# ncu capture summarised in profiles/wkv7_fwd_bwd_config1.md (1.510 GB read + 0.593 GB written).
+BWD_DRAM_TRAFFIC_BYTES = 2_103_864_000
 
 
 def hbm_peak():
@@ -271,6 +271,99 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_other(args):
+    """Secondary workloads (not the headline line): device-resident, forward + backward through the
+    public API, CUDA events, algorithmic-byte roofline.  One JSON line each."""
+    from wind_rwkv.rwkv7 import TimeMixer, attn, attn_ln, ddlerp, expand_loras, synthetic
+    dev = th.device('cuda', 0)
+    th.cuda.set_device(0)
+    gen = th.Generator(device=dev).manual_seed(3)
+    rn = lambda *sh, std=1.0: th.randn(*sh, generator=gen, device=dev) * std
+    bf = th.bfloat16
+    wl = args.workload
+    if wl == 'attn_ln':      # config 2: B16 T4096 H32
+        B, Tn, Hn = args.batch if args.batch != B_PER_GPU else 16, 4096, 32
+        d = synthetic.wkv7_inputs(B, Tn, Hn, N, seed=2, dtype=bf, device=dev)
+        g, params = synthetic.attn_ln_extras(B, Tn, Hn, N, seed=2, dtype=bf, device=dev)
+        ins = [d[n].requires_grad_() for n in 'rwkvab'] + [g.requires_grad_(), params.requires_grad_()]
+        fwd = lambda: attn_ln(*ins, N)
+        gouts = [d['dy']]
+        tokens, alg = B * Tn, B * Tn * Hn * (8 + 15) * N * 2
+        name = f'attn_ln fwd+bwd B{B} T{Tn} H{Hn} N{N} bf16 (config 2)'
+    elif wl == 'prefill':    # config 4: forward only with state carry
+        B, Tn, Hn = args.batch if args.batch != B_PER_GPU else 8, 65536, 40
+        d = synthetic.wkv7_inputs(B, Tn, Hn, N, seed=4, dtype=bf, device=dev, s0_std=0.1)
+        ins = [d[n] for n in 'rwkvab']
+        fwd = lambda: attn(*ins, N, s0=d['s0'], return_state=True)[0]
+        gouts = None
+        tokens, alg = B * Tn, B * Tn * Hn * 7 * N * 2
+        name = f'WKV7 prefill forward B{B} T{Tn} H{Hn} N{N} bf16, s0 -> sT (config 4)'
+    elif wl == 'ddlerp':
+        B, Tn, C, D = args.batch if args.batch != B_PER_GPU else 32, 1024, 768, 32
+        x = rn(B, Tn, C).to(bf).requires_grad_()
+        prm = [rn(C, std=0.3).requires_grad_(), rn(4 * D, C, std=0.02).requires_grad_(), rn(4, C, D, std=0.02).requires_grad_(),
+               rn(4, 1, 1, C, std=0.3).requires_grad_()]
+        ins = [x] + prm
+        fwd = lambda: ddlerp(*ins)
+        gouts = [rn(B, Tn, C).to(bf) for _ in range(4)]
+        tokens, alg = B * Tn, B * Tn * 22 * C
+        name = f'ddlerp fwd+bwd B{B} T{Tn} C{C} D{D} bf16'
+    elif wl == 'expand_loras':
+        B, Tn, C, D = args.batch if args.batch != B_PER_GPU else 32, 1024, 768, 16
+        acts = [rn(B, Tn, C).to(bf).requires_grad_() for _ in range(2)] + [rn(B, Tn, D).to(bf).requires_grad_() for _ in range(4)]
+        prm = [rn(C, D, std=0.1).requires_grad_() for _ in range(4)] + [rn(C, std=0.5).requires_grad_() for _ in range(4)]
+        ins = acts + prm
+        fwd = lambda: expand_loras(*ins, N)
+        gouts = [rn(B, Tn, C).to(bf) for _ in range(4)]
+        tokens, alg = B * Tn, B * Tn * (28 * C + 24 * D)
+        name = f'expand_loras fwd+bwd B{B} T{Tn} C{C} D{D} bf16'
+    elif wl == 'mixer':      # config 3
+        from collections import namedtuple
+        B, Tn, C = args.batch if args.batch != B_PER_GPU else 32, 1024, 768
+        th.manual_seed(0)
+        model = TimeMixer(namedtuple('Config', ['n_layer', 'n_head', 'n_embd'])(12, C // N, C), 3).to(dev)
+        with th.no_grad():
+            for prm_ in model.parameters():
+                prm_.add_(th.randn_like(prm_) * 0.02)
+        x = rn(B, Tn, C).requires_grad_()
+        ins = [x] + list(model.parameters())
+        fwd = lambda: model(x)
+        gouts = [rn(B, Tn, C).to(bf)]
+        tokens, alg = B * Tn, None
+        name = f'TimeMixer layer fwd+bwd B{B} T{Tn} d{C} H{C // N} bf16 (config 3)'
+    else:
+        raise ValueError(wl)
+
+    def step():
+        out = fwd()
+        if gouts is not None:
+            outs = out if isinstance(out, tuple) else (out,)
+            th.autograd.backward(outs, gouts)
+            for t in ins:
+                t.grad = None
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    th.cuda.synchronize()
+    e0, e1 = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        th.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    peak, which = hbm_peak()
+    line = {'metric': name + ', Mtokens/s', 'value': tokens / (ms * 1e-3) / 1e6, 'unit': 'Mtokens/s', 'n_gpus': 1,
+            'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms, 'higher_is_better': True,
+            'dtype': 'bf16', 'data': 'synthetic', 'config': {'workload': name},
+            'roofline': None if alg is None else {'bound': 'hbm', 'achieved': alg / (ms * 1e-3) / 1e9, 'peak': peak, 'unit': 'GB/s',
+                                                   'frac': alg / (ms * 1e-3) / 1e9 / peak, 'peak_source': which,
+                                                   'algorithmic_bytes': alg, 'note': 'whole step (all kernels of the op, forward and backward)'},
+            'clocks': clocks.summary()}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -280,9 +373,13 @@ def main():
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer leg (profiling runs)')
     ap.add_argument('--batch', type=int, default=B_PER_GPU, help='batch per GPU (default: the benchmark shape)')
+    ap.add_argument('--workload', default='wkv7', choices=['wkv7', 'attn_ln', 'prefill', 'ddlerp', 'expand_loras', 'mixer'],
+                    help='wkv7 (default) is the headline line; the others time secondary workloads on one GPU')
     args = ap.parse_args()
     if args.impl == 'reference':
         run_reference(args)
+    elif args.workload != 'wkv7':
+        run_other(args)
     else:
         run_ours(args)
 

@@ -57,7 +57,8 @@ const char* wkv7_status_string(int status);
 int64_t wkv7_checkpoint_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
 
 /* Reads and clears the device-side status word of the current device (synchronises the
- * device).  Kernels bound every wait; one that gave up leaves WKV7_ERR_DEVICE_TIMEOUT here. */
+ * device).  Reserved for kernels with bounded device-side waits; the current kernels never
+ * spin-wait, so this returns 0. */
 int wkv7_device_status(void);
 
 /*

@@ -65,7 +65,6 @@ template <typename IoT, int PREC, bool LN> struct BwdSmem {
     alignas(16) float Gp[2][WARPS][N];
     alignas(16) float lnp[LN ? 3 * N : 4];
     float bdot[L], sbon[L];
-    alignas(8) uint64_t bar_in, bar_vdy[2], bar_s0;
 };
 static_assert(sizeof(BwdSmem<__nv_bfloat16, 1, false>) <= 115712, "bf16 backward must fit two CTAs per SM");
 static_assert(sizeof(BwdSmem<__nv_bfloat16, 1, true>) <= 115712, "bf16 attn_ln backward must fit two CTAs per SM");
@@ -143,13 +142,6 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
     const float* ckpt = p.ckpt + bh * nchunks * (long long)(N * N);
     constexpr uint32_t ROW_BYTES = N * sizeof(IoT);
 
-    if (tid == 0) {
-        mbar_init(&sm.bar_in, 1);
-        mbar_init(&sm.bar_vdy[0], 1);
-        mbar_init(&sm.bar_vdy[1], 1);
-        mbar_init(&sm.bar_s0, 1);
-        mbar_fence_init();
-    }
     if (LN) {
         for (int i = tid; i < 3 * N; i += THREADS) sm.lnp[i] = p.params[(long long)(i / N) * p.H * N + hi * N + (i % N)];
     }
@@ -225,12 +217,10 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
 #else
 #define TICK(i)
 #endif
-    bool failed = false;
     for (int it = 0; it < nchunks; ++it) {
         const int c = nchunks - 1 - it;
         const int vs = it & 1;
         // ---------------- P1: decay scan and scaled operands -------------------------------------
-        bool ok = true;
         {
             decay_scan<IoT, PREC>(sm.st_in[0], sm.st_in[1], sm.st_in[2], sm.st_in[3], sm.st_in[4], Lay::ROWB, sm.wq, sm.wa,
                                   sm.kwi, sm.bwi, sm.fw, sm.cum, PREC == 3 ? sm.lw : nullptr, warp, lane);
@@ -249,7 +239,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             }
         }
         TICK(0)
-        if (__syncthreads_or(!ok)) { failed = true; break; }  // (A)
+        __syncthreads();  // (A)
         TICK(1)
 
         if (c > 0) {
@@ -291,9 +281,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             if (lane < L) tri_inverse_column<PREC>(sm.AB, sm.AI, lane);
         }
 
-        bool ok2 = true;
         TICK(2)
-        if (__syncthreads_or(!ok2)) { failed = true; break; }  // (B)
+        __syncthreads();  // (B)
         TICK(3)
 
         // ---------------- stage B: rows = value index -----------------------------------------
@@ -690,10 +679,6 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
                tacc[7] / nchunks, tacc[8] / nchunks, tacc[9] / nchunks);
 #endif
 
-    if (failed) {
-        if (tid == 0) atomicExch(p.status, (int)kDeviceTimeout);
-        return;
-    }
     if (LN) {
         // per-(batch, head) partial parameter gradients: ws[b][0..2][h*N + channel]
         float* ws = p.dparams_ws + bi * 3 * p.H * N + hi * N;

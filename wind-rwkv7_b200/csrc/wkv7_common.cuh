@@ -1,6 +1,6 @@
-// Shared device helpers for the sm_100a WKV7 kernels: TF32 warp-MMA fragments,
-// bulk-async (TMA engine) row copies with mbarrier completion, bounded waits,
-// and the status codes of the C ABI.
+// Shared device helpers for the sm_100a WKV7 kernels: TF32 warp-MMA fragments, the chunk
+// preparation (decay scan, triangular inverse), MUFU-free exp / reciprocal, cp.async copies, and
+// the status codes of the C ABI.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -26,7 +26,7 @@ enum Status : int {
     kNullPointer = -6,
     kLaunchFailed = -7,    // cudaGetLastError() after launch was not cudaSuccess
     kTooLarge = -8,
-    kDeviceTimeout = -9,   // a bounded device-side wait gave up (see wkv7_device_status)
+    kDeviceTimeout = -9,   // a bounded device-side wait gave up (no current kernel spin-waits)
 };
 
 // ---- IO element access ----------------------------------------------------------------------
@@ -275,47 +275,7 @@ template <int PREC> __device__ __forceinline__ void tri_inverse_column(const flo
     tri_step<PREC, 14>(r, ca, cb, ABt, AI, col);  tri_step<PREC, 15>(r, cb, ca, ABt, AI, col);
 }
 
-// ---- mbarrier + bulk async copy (TMA engine, untiled) -----------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-
-// Bounded wait on a phase parity: gives up after about a second of SM clocks.  Returns false if
-// the limit ran out (the caller records it and leaves its loop); never spins forever.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t addr = smem_u32(bar);
-    long long start = 0;
-    for (int it = 0;; ++it) {
-        uint32_t done;
-        asm volatile(
-            "{\n"
-            ".reg .pred p;\n"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-            "selp.u32 %0, 1, 0, p;\n"
-            "}\n"
-            : "=r"(done)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (done) return true;
-        if (it == 64) start = clock64();
-        if (it > 64 && clock64() - start > 2000000000LL) return false;
-    }
-}
-
-// One contiguous row global -> shared; 16-byte aligned on both sides, size a multiple of 16.
-__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(dst_smem)),
-                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
 
 // 16-byte asynchronous copy global -> shared through the load/store unit (no TMA request)
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {

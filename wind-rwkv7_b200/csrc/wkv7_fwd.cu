@@ -15,7 +15,9 @@
 //     QK = tril(wq kwi^T)  QB = tril(wq bwi^T)  AK = stril(wa kwi^T)  AB = stril(wa bwi^T)
 //     X = AK V + wa S0^T ;  U = (I-AB)^-1 X ;  Y = QK V + QB U + wq S0^T
 //     S' = (S0 + V^T kwi + U^T bwi) * fw[None,:]
-// Inputs arrive through bulk-async row copies (TMA engine) completing on mbarriers.
+// Inputs are fetched one chunk ahead with 16-byte cp.async copies issued by all threads (an
+// earlier version issued one bulk-async copy per 128-byte row; at 96 requests per chunk the
+// request rate of the copy engine, about 120 cycles each, was the bottleneck).
 #include "wkv7_kernels.h"
 #ifdef WKV7_TIMING
 #include <cstdio>
@@ -41,7 +43,6 @@ template <typename IoT, bool LN> struct FwdSmem {
     float bdot[L];
     float red[WARPS][L][2];
     alignas(16) IoT ysc[WARPS][L * Lay::YS];
-    alignas(8) uint64_t bar_in, bar_v[2];
 };
 
 template <typename IoT> __device__ __forceinline__ float st_elem(const unsigned char* tile, int row, int col) {
@@ -67,18 +68,13 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
     IoT* gy = (IoT*)p.y + base;
     constexpr uint32_t ROW_BYTES = N * sizeof(IoT);
 
-    if (tid == 0) {
-        mbar_init(&sm.bar_in, 1);
-        mbar_init(&sm.bar_v[0], 1);
-        mbar_init(&sm.bar_v[1], 1);
-        mbar_fence_init();
-    }
     if (LN) {
         for (int i = tid; i < 3 * N; i += THREADS) sm.lnp[i] = p.params[(long long)(i / N) * p.H * N + hi * N + (i % N)];
     }
     __syncthreads();
 
-    // EXPERIMENT: all threads fetch 16-byte pieces with cp.async
+    // q, w, k, a, b are dead once the scan has run, so the next chunk's copies are issued right
+    // after the first barrier of the iteration; v (and g) are read late and double buffered.
     constexpr int CH = ROW_BYTES / 16;
     auto issue_in = [&](int c) {
         for (int i = tid; i < 5 * L * CH; i += THREADS) {
@@ -127,10 +123,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
 #else
 #define TICK(i)
 #endif
-    bool failed = false;
     for (int c = 0; c < nchunks; ++c) {
-        // ---------------- P1: decay scan and scaled operands (thread = key channel x half) ------
-        bool ok = true;
+        // ---------------- P1: decay scan and scaled operands ------------------------------------
         {
             decay_scan<IoT, PREC>(sm.st_in[0], sm.st_in[1], sm.st_in[2], sm.st_in[3], sm.st_in[4], Lay::ROWB, sm.wq, sm.wa,
                                   sm.kwi, sm.bwi, sm.fw, nullptr, nullptr, warp, lane);
@@ -149,7 +143,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
             }
         }
         TICK(0)
-        if (__syncthreads_or(!ok)) { failed = true; break; }  // (A)
+        __syncthreads();  // (A)
         TICK(1)
 
         if (c + 1 < nchunks) {
@@ -214,9 +208,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
                 mma<PREC>(XY[nt], a, fragB_nk<PREC, true>(nt < 2 ? sm.wa : sm.wq, OPS, 8 * (nt & 1), 8 * kk, g, t4));
         }
 
-        bool okv = true;
         TICK(4)
-        if (__syncthreads_or(!okv)) { failed = true; break; }  // (B) scores, AI and v visible
+        __syncthreads();  // (B) scores and AI visible
         TICK(5)
 
         // ---------------- chain, part 2 ----------------------------------------------------------
@@ -346,15 +339,6 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
                tacc[0] / nchunks, tacc[1] / nchunks, tacc[2] / nchunks, tacc[3] / nchunks, tacc[4] / nchunks, tacc[5] / nchunks, tacc[6] / nchunks, tacc[7] / nchunks);
 #endif
 
-    if (failed) {
-        // A bounded wait ran out: record it, give in-flight copies one more bounded chance to
-        // land (they target this CTA's shared memory), and leave without touching the outputs.
-        if (tid == 0) {
-            atomicExch(p.status, (int)kDeviceTimeout);
-            mbar_wait(&sm.bar_in, 0);
-        }
-        return;
-    }
     if (p.sT) {
         float* sT = p.sT + bh * N * N;
 #pragma unroll
