@@ -17,7 +17,26 @@ namespace wkv7 {
 
 constexpr int HC = 64;  // channels per head
 
-__device__ __forceinline__ float softplus_f(float u) { return fmaxf(u, 0.f) + log1pf(__expf(-fabsf(u))); }
+// The gates of one element.  Nine transcendental evaluations in the textbook form; here seven,
+// split over two pipes because the special-function unit is the bottleneck of this op on B200: the
+// three sigmoids share ONE reciprocal (1/(pa*pm*pk), arguments clamped to +-25 so the product stays
+// finite), softplus is exp + log2, and three of the five exponentials run as polynomials on the
+// FMA pipe.   a, ma, mk = sigmoid(xa, xm, xk);  w = -softplus(-v) - 0.5;  E = exp(w * mk).
+struct Gates { float a, ma, mk, w, E, ev; };  // ev = exp(-v) (for the backward: sigmoid(-v) = ev / (1 + ev))
+__device__ __forceinline__ Gates lora_gates(float xa, float xm, float xk, float v) {
+    Gates o;
+    const float pa = 1.f + exp_poly(-fminf(fmaxf(xa, -25.f), 25.f));
+    const float pm = 1.f + exp_poly(-fminf(fmaxf(xm, -25.f), 25.f));
+    const float pk = 1.f + __expf(-fminf(fmaxf(xk, -25.f), 25.f));
+    const float r = __fdividef(1.f, pa * pm * pk);
+    o.a = r * pm * pk;
+    o.ma = r * pa * pk;
+    o.mk = r * pa * pm;
+    o.ev = exp_poly(-v);  // exp_poly clamps its argument to +-80
+    o.w = -0.6931471805599453f * __log2f(1.f + o.ev) - 0.5f;
+    o.E = __expf(o.w * o.mk);
+    return o;
+}
 
 template <int D> struct LorasFwdSmem {
     bf16 W[4][HC][D + 8];  // [channel][rank]
@@ -112,15 +131,13 @@ __global__ void __launch_bounds__(128) loras_fwd_kernel(LorasParams p) {
 #pragma unroll
             for (int x = 0; x < 2; ++x) {
                 const int i = 2 * hrow + x;
-                const float a = sigmoid_f(fa[i] + (x ? ab.y : ab.x));
-                const float ma = sigmoid_f(fm[i] + (x ? mb.y : mb.x));
-                const float mk = sigmoid_f(fk[i] + (x ? kb.y : kb.x));
-                const float w = -softplus_f(-((x ? wb.y : wb.x) + (x ? wi.y : wi.x))) - 0.5f;
+                const Gates gt = lora_gates(fa[i] + (x ? ab.y : ab.x), fm[i] + (x ? mb.y : mb.x), fk[i] + (x ? kb.y : kb.x),
+                                            (x ? wb.y : wb.x) + (x ? wi.y : wi.x));
                 const float kk = z[j][i] * inorm;
-                ow[x] = w;
-                ok[x] = (x ? ki.y : ki.x) * (ma + a - ma * a) * __expf(w * mk);
+                ow[x] = gt.w;
+                ok[x] = (x ? ki.y : ki.x) * (gt.ma + gt.a - gt.ma * gt.a) * gt.E;
                 okk[x] = kk;
-                ob[x] = -kk * a;
+                ob[x] = -kk * gt.a;
             }
             *reinterpret_cast<uint32_t*>((bf16*)p.w_out + e) = pack_bf16x2(ow[0], ow[1]);
             *reinterpret_cast<uint32_t*>((bf16*)p.k_out + e) = pack_bf16x2(ok[0], ok[1]);
@@ -218,7 +235,7 @@ __global__ void __launch_bounds__(128) loras_bwd_kernel(LorasParams p) {
                     for (int x = 0; x < 2; ++x) {
                         const int i = 2 * hrow + x;
                         z[j][i] += x ? ki.y : ki.x;
-                        const float a = sigmoid_f(fa[i] + (x ? ab.y : ab.x));
+                        const float a = rcp_newton(1.f + exp_poly(-fminf(fmaxf(fa[i] + (x ? ab.y : ab.x), -25.f), 25.f)));
                         dzo[j][i] = (x ? dk.y : dk.x) - (x ? db.y : db.x) * a;  // gradient of kk
                         ss[hrow] += z[j][i] * z[j][i];
                         dn[hrow] += dzo[j][i] * z[j][i];
@@ -259,13 +276,11 @@ __global__ void __launch_bounds__(128) loras_bwd_kernel(LorasParams p) {
 #pragma unroll
                     for (int x = 0; x < 2; ++x) {
                         const int i = 2 * hrow + x;
-                        const float a = sigmoid_f(fa[i] + (x ? ab.y : ab.x));
-                        const float ma = sigmoid_f(fm[i] + (x ? mb.y : mb.x));
-                        const float mk = sigmoid_f(fk[i] + (x ? kb.y : kb.x));
                         const float v = (x ? wb.y : wb.x) + (x ? wi.y : wi.x);
-                        const float w = -softplus_f(-v) - 0.5f;
+                        const Gates gt = lora_gates(fa[i] + (x ? ab.y : ab.x), fm[i] + (x ? mb.y : mb.x), fk[i] + (x ? kb.y : kb.x), v);
+                        const float a = gt.a, ma = gt.ma, mk = gt.mk, w = gt.w, E = gt.E;
                         const float kin = x ? ki.y : ki.x;
-                        const float E = __expf(w * mk), kmix = ma + a - ma * a;
+                        const float kmix = ma + a - ma * a;
                         const float zz = z[j][i], kk = zz * inorm[hrow];
                         const float dkE = (x ? gk.y : gk.x) * E;
                         const float de = dkE * kin * kmix;                       // gradient of w*mk
@@ -275,7 +290,7 @@ __global__ void __launch_bounds__(128) loras_bwd_kernel(LorasParams p) {
                         const float da = -(x ? gb.y : gb.x) * kk + dkE * (kin - kin * ma);
                         const float in3 = inorm[hrow] * inorm[hrow] * inorm[hrow];
                         const float dz = dzo[j][i] * inorm[hrow] - in3 * dn[hrow] * zz;
-                        o_dw[x] = dwt * sigmoid_f(-v);
+                        o_dw[x] = dwt * gt.ev * rcp_newton(1.f + gt.ev);  // * sigmoid(-v)
                         o_dk[x] = dkE * kmix + dz;
                         o_z[x] = dz;
                         o_a[x] = da * a * (1.f - a);

@@ -254,7 +254,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             float* dst = warp == 0 ? sm.QK : warp == 1 ? sm.AK : warp == 2 ? sm.QB : sm.AB;
             const bool strict = warp & 1;
             float d[2][4] = {};
-#pragma unroll
+#pragma unroll 2
             for (int kk = 0; kk < 8; ++kk) {
                 FragA<PREC> a = fragA_mk<PREC, true>(Am, OPS, 0, 8 * kk, g, t4);
 #pragma unroll
@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
         float dvx[2][4] = {};  // LN: bonus-term contribution to dv
         {
             float X[2][4] = {}, Y[2][4] = {};
-#pragma unroll
+#pragma unroll 2
             for (int kk = 0; kk < 8; ++kk) {
                 FragA<PREC> a = fragA_mk<PREC>(sm.S0s, SS, 16 * warp, 8 * kk, g, t4);
 #pragma unroll
@@ -540,7 +540,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             float d[2][4] = {};
             const bool strict = warp & 1;
             float* dst = sm.sgrad + warp * (L * SCS);  // 0 dQK, 1 dAK, 2 dQB, 3 dAB
-#pragma unroll
+#pragma unroll 2
             for (int kk = 0; kk < 8; ++kk) {
                 FragA<PREC> aD = fragA_mk<PREC, true>(sm.Dt, OPS, 0, 8 * kk, g, t4);
                 FragA<PREC> aY = LN ? fragA_mk<PREC, true>(sm.Yt, OPS, 0, 8 * kk, g, t4) : fragA_mk_st<IoT, PREC>(dyt, 8 * kk, g, t4);
@@ -600,6 +600,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
         for (int nt = 0; nt < 2; ++nt) {
             const int key = 16 * warp + 8 * nt + 2 * t4;
             float x[2][2], e2[2][2], lwv[2][2];  // [row half][column]
+            float incl_lo[2] = {1.f, 1.f};  // P_t of this thread's first-half row, per column
 #pragma unroll
             for (int hrow = 0; hrow < 2; ++hrow) {
                 const int tq = g + 8 * hrow;
@@ -623,7 +624,13 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
                     const int i = e + 2 * hrow;
                     const float incl = exp_p<PREC>(fmaxf(cuv[e], -80.f));
                     const float inv = PREC == 3 ? 1.f / incl : rcp_newton(incl);
-                    const float non = exp_p<PREC>(fmaxf(cuv[e] - lwa[e], -80.f));
+                    // P_{t-1} is P_t of the row above, which the lane four below holds (row 7 for
+                    // this thread's row 8 sits in lane 28 + t4, first half); row -1 is 1.
+                    const float up_same = __shfl_up_sync(0xffffffffu, incl, 4);
+                    const float up_lo7 = __shfl_sync(0xffffffffu, incl_lo[e], 28 + t4);
+                    const float non = PREC == 3 ? exp_p<PREC>(cuv[e] - lwa[e])
+                                                : (g > 0 ? up_same : (hrow == 0 ? 1.f : up_lo7));
+                    if (hrow == 0) incl_lo[e] = incl;
                     o_a[e] = non * DA[nt][i];
                     o_q[e] = incl * DQ[nt][i];
                     o_b[e] = inv * DB[nt][i];

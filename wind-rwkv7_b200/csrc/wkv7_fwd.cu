@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
             float* dst = warp == 0 ? sm.QK : warp == 1 ? sm.AK : warp == 2 ? sm.QB : sm.AB;
             const bool strict = warp & 1;
             float d[2][4] = {};
-#pragma unroll
+#pragma unroll 2
             for (int kk = 0; kk < 8; ++kk) {
                 FragA<PREC> a = fragA_mk<PREC, true>(Am, OPS, 0, 8 * kk, g, t4);
 #pragma unroll
