@@ -94,3 +94,18 @@ def strides4(x):
 def device_status():
     """Reads and clears the device status word (synchronises)."""
     return lib().wkv7_device_status()
+
+
+def opaque_op(name, fn, fake, schema_types):
+    """Registers `fn` (a launcher that allocates its outputs and calls the C ABI) as the functional
+    custom op wkv7_sm100::<name> with `fake` as its shape function, so that torch.compile can keep
+    it in a full graph (upstream gets the same effect from its mutable-alias TORCH_LIBRARY schemas,
+    attn.cpp:24-27).  Eager calls do not go through the dispatcher; see `call`."""
+    op = th.library.custom_op(f'wkv7_sm100::{name}', fn, mutates_args=(), schema=schema_types)
+    op.register_fake(fake)
+    return op
+
+
+def call(op, fn, *args):
+    """`fn(*args)` directly in eager mode, the registered custom op while torch.compile traces."""
+    return op(*args) if th.compiler.is_compiling() else fn(*args)

@@ -53,6 +53,23 @@ def bw_attn(w, q, k, v, a, b, s, dy, dsT, sT):
     return dw, dq, dk, dv, da, db, ds0
 
 
+def _fake_fw(w, q, k, v, a, b, s0, save_checkpoints=True):
+    B, T, H, C = w.shape
+    return (th.empty_like(v), w.new_empty((B, H, C, C), dtype=th.float32),
+            w.new_empty((B, H, T // _lib.CHUNK if save_checkpoints else 0, C, C), dtype=th.float32))
+
+
+def _fake_bw(w, q, k, v, a, b, s, dy, dsT, sT):
+    B, T, H, C = w.shape
+    return tuple(th.empty_like(w) for _ in range(6)) + (w.new_empty((B, H, C, C), dtype=th.float32),)
+
+
+_fw_op = _lib.opaque_op('attn_fwd', fw_attn, _fake_fw,
+                        '(Tensor w, Tensor q, Tensor k, Tensor v, Tensor a, Tensor b, Tensor? s0, bool save_checkpoints=True) -> (Tensor, Tensor, Tensor)')
+_bw_op = _lib.opaque_op('attn_bwd', bw_attn, _fake_bw,
+                        '(Tensor w, Tensor q, Tensor k, Tensor v, Tensor a, Tensor b, Tensor s, Tensor dy, Tensor? dsT, Tensor sT) -> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)')
+
+
 def _check_inputs(w, q, k, v, a, b, s0):
     B, T, H, C = w.shape
     assert T % _lib.CHUNK == 0, 'T must be a multiple of 16'
@@ -71,9 +88,11 @@ class WindRWKV7(th.autograd.Function):
 
     @staticmethod
     def forward(ctx, w, q, k, v, a, b, s0):
-        _check_inputs(w, q, k, v, a, b, s0)
+        if not th.compiler.is_compiling():  # as upstream, checks are skipped while tracing
+            _check_inputs(w, q, k, v, a, b, s0)
         s0f = None if s0 is None else s0.float().contiguous()
-        y, sT, s = fw_attn(w, q, k, v, a, b, s0f, save_checkpoints=any(ctx.needs_input_grad))
+        save = True if th.compiler.is_compiling() else any(ctx.needs_input_grad)
+        y, sT, s = _lib.call(_fw_op, fw_attn, w, q, k, v, a, b, s0f, save)
         ctx.save_for_backward(w, q, k, v, a, b, s, sT)
         ctx.s0_dtype = None if s0 is None else s0.dtype
         ctx.mark_non_differentiable(s)
@@ -85,12 +104,13 @@ class WindRWKV7(th.autograd.Function):
     @staticmethod
     def backward(ctx, dy, dsT, ds):
         w, q, k, v, a, b, s, sT = ctx.saved_tensors
-        assert ds is None
+        if not th.compiler.is_compiling():
+            assert ds is None
         if dy is None:
             dy = th.zeros_like(v)
         if dsT is not None:
             dsT = dsT.float().contiguous()
-        dw, dq, dk, dv, da, db, ds0 = bw_attn(w, q, k, v, a, b, s, dy, dsT, sT)
+        dw, dq, dk, dv, da, db, ds0 = _lib.call(_bw_op, bw_attn, w, q, k, v, a, b, s, dy, dsT, sT)
         if ctx.s0_dtype is None:
             ds0 = None
         elif ctx.s0_dtype != th.float32:

@@ -50,18 +50,37 @@ def bw_attn_ln(w, q, k, v, a, b, g, params, s, dy, dsT, sT):
     return dw, dq, dk, dv, da, db, dg, dparams, ds0
 
 
+def _fake_fw(w, q, k, v, a, b, g, params, s0, save_checkpoints=True):
+    B, T, H, C = w.shape
+    return (th.empty_like(v), w.new_empty((B, H, C, C), dtype=th.float32),
+            w.new_empty((B, H, T // _lib.CHUNK if save_checkpoints else 0, C, C), dtype=th.float32))
+
+
+def _fake_bw(w, q, k, v, a, b, g, params, s, dy, dsT, sT):
+    B, T, H, C = w.shape
+    return tuple(th.empty_like(w) for _ in range(7)) + (th.empty_like(params), w.new_empty((B, H, C, C), dtype=th.float32))
+
+
+_fw_op = _lib.opaque_op('attn_ln_fwd', fw_attn_ln, _fake_fw,
+                        '(Tensor w, Tensor q, Tensor k, Tensor v, Tensor a, Tensor b, Tensor g, Tensor params, Tensor? s0, bool save_checkpoints=True) -> (Tensor, Tensor, Tensor)')
+_bw_op = _lib.opaque_op('attn_ln_bwd', bw_attn_ln, _fake_bw,
+                        '(Tensor w, Tensor q, Tensor k, Tensor v, Tensor a, Tensor b, Tensor g, Tensor params, Tensor s, Tensor dy, Tensor? dsT, Tensor sT) -> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)')
+
+
 class WindRWKV7(th.autograd.Function):
     """(w,q,k,v,a,b,g,params,s0) -> (y, sT, s), as upstream's autograd function (rwkv7_attn_ln.py:19-47)."""
 
     @staticmethod
     def forward(ctx, w, q, k, v, a, b, g, params, s0):
-        _check_inputs(w, q, k, v, a, b, s0)
-        B, T, H, C = w.shape
-        assert g.shape == w.shape and g.dtype == w.dtype
-        assert params.dtype == th.float32 and list(params.shape) == [3, H * C]
+        if not th.compiler.is_compiling():  # as upstream, checks are skipped while tracing
+            _check_inputs(w, q, k, v, a, b, s0)
+            B, T, H, C = w.shape
+            assert g.shape == w.shape and g.dtype == w.dtype
+            assert params.dtype == th.float32 and list(params.shape) == [3, H * C]
         params = params.contiguous()
         s0f = None if s0 is None else s0.float().contiguous()
-        y, sT, s = fw_attn_ln(w, q, k, v, a, b, g, params, s0f, save_checkpoints=any(ctx.needs_input_grad))
+        save = True if th.compiler.is_compiling() else any(ctx.needs_input_grad)
+        y, sT, s = _lib.call(_fw_op, fw_attn_ln, w, q, k, v, a, b, g, params, s0f, save)
         ctx.save_for_backward(w, q, k, v, a, b, g, params, s, sT)
         ctx.s0_dtype = None if s0 is None else s0.dtype
         ctx.mark_non_differentiable(s)
@@ -73,12 +92,13 @@ class WindRWKV7(th.autograd.Function):
     @staticmethod
     def backward(ctx, dy, dsT, ds):
         w, q, k, v, a, b, g, params, s, sT = ctx.saved_tensors
-        assert ds is None
+        if not th.compiler.is_compiling():
+            assert ds is None
         if dy is None:
             dy = th.zeros_like(v)
         if dsT is not None:
             dsT = dsT.float().contiguous()
-        dw, dq, dk, dv, da, db, dg, dparams, ds0 = bw_attn_ln(w, q, k, v, a, b, g, params, s, dy, dsT, sT)
+        dw, dq, dk, dv, da, db, dg, dparams, ds0 = _lib.call(_bw_op, bw_attn_ln, w, q, k, v, a, b, g, params, s, dy, dsT, sT)
         if ctx.s0_dtype is None:
             ds0 = None
         elif ctx.s0_dtype != th.float32:
