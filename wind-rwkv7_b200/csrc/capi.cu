@@ -1,5 +1,6 @@
 // extern "C" entry points of libwkv7_sm100.so (declared in include/wkv7_sm100.h): host-side
 // validation, the per-device status word, and dispatch to the kernel launchers.
+#include <cstdlib>
 #include "../../include/wkv7_sm100.h"
 #include "wkv7_kernels.h"
 #include "ddlerp.h"
@@ -38,6 +39,19 @@ float* static_scratch() {
         cache[dev] = ptr;
     }
     return cache[dev];
+}
+
+// Forward implementation for bf16 attn: the tcgen05 kernel with 2 to 4 preparation groups (negative:
+// operands rounded to TF32 by the producer instead of truncated by the tensor core), or (0) the
+// warp-MMA kernel.  WKV7_FWD_TC = 0 | 2..4 | -2..-4 overrides the default; read once.
+int fwd_tc_groups() {
+    static const int v = [] {
+        const char* e = std::getenv("WKV7_FWD_TC");
+        if (!e) return 2;
+        const int x = std::atoi(e);
+        return (x >= -4 && x <= 4 && (x >= 2 || x <= -2)) ? x : 0;
+    }();
+    return v;
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -115,6 +129,10 @@ static int fwd_common(const void* r, const void* w, const void* k, const void* v
     p.eps = eps;
     p.status = status_ptr();
     if (!p.status) return WKV7_ERR_LAUNCH;
+    if (io_dtype == WKV7_BF16 && !ln) {
+        const int groups = fwd_tc_groups();
+        if (groups) return wkv7::launch_fwd_tc(p, groups, (cudaStream_t)stream);
+    }
     return wkv7::launch_fwd(p, io_dtype, ln, (cudaStream_t)stream);
 }
 

@@ -1,0 +1,546 @@
+// WKV7 forward on the 5th-generation tensor cores (tcgen05, accumulators in tensor memory), bf16 IO.
+//
+// Same mathematics as wkv7_fwd.cu (the reference's forward_kernel, wind_rwkv/rwkv7/attn.cu:11-106),
+// different machine mapping.  One CTA walks one (batch, head) chain.  The 64x64 state S[value][key]
+// lives in tensor memory for the whole sequence and is never held in registers: per 16-step chunk
+// one elected thread issues 26 tcgen05.mma instructions (M = 64 value rows, TF32 operands, fp32
+// accumulate)
+//     hop 1   [X | Yp] = S [wa;wq]^T + V^T [AK;QK]^T        A = S straight from tensor memory
+//     hop 2   U  = X AI^T                                    A = X from tensor memory
+//     hop 3   Y  = Yp + U QB^T                               A = U from tensor memory
+//     hop 4   S' = S diag(fw) + V^T kwf + U bwf              eight N = 8 products apply the decay
+// with kwf = kwi*fw, bwf = bwi*fw, so the column scaling of the state never touches a CUDA core.
+// An accumulator that the next product reads as its A operand needs an explicit completion wait
+// (tcgen05.commit -> mbarrier); only same-accumulator chains are ordered by the tensor pipe, so the
+// decay product and the V^T kwf product are issued inside those waits.
+//
+// Everything state-independent is done by G "preparation groups" of four warps, each working on
+// its own chunk (c, c+G, ...): cp.async of the six input tiles, the decay scan, the operand tiles
+// in the shared-memory layouts the tensor core reads directly, the four 16x16 score matrices as
+// ONE tcgen05 product ([wa;wq] x [kwi;bwi]^T, M = 64 of which 32 rows are used), masking, the
+// triangular inverse, and afterwards the read-back of Y (and of the chunk-end state for the
+// checkpoints) from tensor memory.  The chain thread only waits for "operands of chunk c ready" and
+// "results of chunk c-1 read", so the 16-step dependency is ~1000 cycles per chunk while the
+// preparation of later chunks proceeds in parallel.
+//
+// Shared-memory operand layouts (no TMA: the tiles are produced by threads, not copied):
+//   K-major (contraction index contiguous): 16-byte chunks [row/8][k/4][row%8][k%4], descriptor
+//     LBO = 128 B (next k-chunk), SBO = bytes per 8-row group, no swizzle.
+//   MN-major TF32 (V, kwf, bwf: contraction index = time): only the 128-byte swizzle with 32-byte
+//     base exists for 32-bit MN-major operands: rows of 32 channels (128 B) per time step, the
+//     32-byte unit index XOR-ed with (t % 4); LBO = stride between the two 32-channel halves,
+//     SBO = 512 B (four time steps).
+// Every wait on an mbarrier is bounded; a wait that runs out raises an abort flag that makes all
+// later waits of the CTA return at once, records kDeviceTimeout and lets the CTA finish (tensor
+// memory is still released).
+#include "wkv7_kernels.h"
+#ifdef WKV7_TIMING
+#include <cstdio>
+#define TCK(i) { long long now_ = clock64(); tacc[i] += now_ - tprev; tprev = now_; }
+#else
+#define TCK(i)
+#endif
+
+namespace wkv7 {
+namespace tc {
+
+constexpr int ROWB = 2 * N + 16;    // staging row of a bf16 input tile (bytes, padded against bank conflicts)
+constexpr int RAW_TILE = L * ROWB;  // 2304
+
+// per-group shared memory (byte offsets; tensor-core tiles first, all 1024-byte aligned)
+constexpr int G_WAQ = 0;       // [wa;wq]   32 rows x 64, K-major            8192
+constexpr int G_KB = 8192;     // [kwi;bwi] 32 rows x 64, K-major            8192 (directly after WAQ: the M = 64 score
+                               //                                                 product reads rows 32..63 from here, unused)
+constexpr int G_V = 16384;     // V   [time][value]  MN-major                4096
+constexpr int G_KWF = 20480;   // kwf [time][key]    MN-major                4096
+constexpr int G_BWF = 24576;   // bwf [time][key]    MN-major                4096
+constexpr int G_SC = 28672;    // [AK;QK]  32 rows x 16, K-major             2048
+constexpr int G_AI = 30720;    // AI       16 x 16, K-major                  1024
+constexpr int G_QB = 31744;    // QB       16 x 16, K-major                  1024
+constexpr int G_DF = 32768;    // eight 8x8 diagonal blocks of fw, K-major   2048
+constexpr int G_ABT = 34816;   // AB transposed, fp32 [16][SCS]              1536
+constexpr int G_RAW = 36352;   // q, w, k, a, b, v staging                   6 * 2304
+constexpr int G_BYTES = 50176; // 49 KB
+
+// tensor-memory columns (32-bit each, 128 lanes; the M = 64 products use lanes 0-15 of each 32-lane quarter)
+constexpr int C_S = 0;      // two 64-column state buffers
+constexpr int C_XY = 128;   // X (16) | Y (16)
+constexpr int C_U = 160;    // U (16)
+constexpr int C_SCORE = 176;  // + 32 * group: [AK|AB] in lanes 0-15, [QK|QB] in lanes 32-47
+
+constexpr long long WAIT_LIMIT = 1LL << 28;  // cycles (~0.15 s): far beyond any legitimate wait
+
+struct Ctrl {
+    uint64_t full[4], done[4], rdone[4], score[4], hop;
+    uint32_t tmem_base;
+    volatile int abort;
+};
+
+__device__ __forceinline__ uint32_t elect_one() {
+    uint32_t p;
+    asm volatile("{\n.reg .pred P;\nelect.sync _|P, 0xffffffff;\nselp.u32 %0, 1, 0, P;\n}\n" : "=r"(p));
+    return p;
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait for the phase with the given parity.  Returns at once when the CTA has aborted.
+// SLEEP: the thread is suspended by the hardware (try_wait with a time hint) instead of polling, so
+// that the many warps that wait for the chain do not take issue slots from the warps that work; the
+// chain's own short waits poll.
+template <bool SLEEP>
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, Ctrl* ctrl, int* status) {
+    const uint32_t addr = smem_u32(bar);
+    long long start = 0;
+    for (int spin = 0;; ++spin) {
+        uint32_t ok;
+        if (SLEEP)
+            asm volatile("{\n.reg .pred P;\nmbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\nselp.u32 %0, 1, 0, P;\n}\n"
+                         : "=r"(ok) : "r"(addr), "r"(parity), "r"(4000u) : "memory");
+        else
+            asm volatile("{\n.reg .pred P;\nmbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\nselp.u32 %0, 1, 0, P;\n}\n"
+                         : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return;
+        if (ctrl->abort) return;
+        if (spin == 0) start = clock64();
+        else if ((SLEEP || (spin & 63) == 0) && clock64() - start > WAIT_LIMIT) {
+            ctrl->abort = 1;
+            atomicExch(status, (int)kDeviceTimeout);
+            return;
+        }
+    }
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void group_bar(int grp) { asm volatile("bar.sync %0, 128;" ::"r"(grp + 1) : "memory"); }
+
+// shared-memory matrix descriptor (sm_100 version field set); byte offsets are added to the low word
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr, uint32_t sbo) {
+    return (uint64_t)((saddr >> 4) & 0x3fff) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
+}
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr) {  // 128-byte swizzle with 32-byte base
+    return (uint64_t)((saddr >> 4) & 0x3fff) | ((uint64_t)(2048 >> 4) << 16) | ((uint64_t)(512 >> 4) << 32) | (1ull << 46) | (1ull << 61);
+}
+// instruction descriptor: fp32 accumulate, TF32 operands, M = 64
+__host__ __device__ constexpr uint32_t idesc(int n, bool a_mn, bool b_mn) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | (4u << 24);
+}
+__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t id, uint32_t acc) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(d), "l"(a), "l"(b), "r"(id), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a, uint64_t b, uint32_t id, uint32_t acc) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(d), "r"(a), "l"(b), "r"(id), "r"(acc) : "memory");
+}
+// 16 consecutive columns of this thread's lane
+__device__ __forceinline__ void tmem_ld16(uint32_t ta, uint32_t* v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]),"=r"(v[1]),"=r"(v[2]),"=r"(v[3]),"=r"(v[4]),"=r"(v[5]),"=r"(v[6]),"=r"(v[7]),"=r"(v[8]),"=r"(v[9]),"=r"(v[10]),"=r"(v[11]),"=r"(v[12]),"=r"(v[13]),"=r"(v[14]),"=r"(v[15]) : "r"(ta));
+}
+__device__ __forceinline__ void tmem_st16(uint32_t ta, const uint32_t* v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};"
+        :: "r"(v[0]),"r"(v[1]),"r"(v[2]),"r"(v[3]),"r"(v[4]),"r"(v[5]),"r"(v[6]),"r"(v[7]),"r"(v[8]),"r"(v[9]),"r"(v[10]),"r"(v[11]),"r"(v[12]),"r"(v[13]),"r"(v[14]),"r"(v[15]), "r"(ta) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// byte offset of the 16-byte chunk holding (row, k..k+3) in a K-major tile; sbo = bytes per 8-row group
+__device__ __forceinline__ int kchunk(int row, int kc, int sbo) { return (row >> 3) * sbo + kc * 128 + (row & 7) * 16; }
+
+// Column `col` of AI = (I - AB)^-1 (AB strictly lower triangular), written into the K-major AI tile
+// as element (row S_, k = col).  Right-looking substitution as in tri_inverse_column().
+template <int S_> __device__ __forceinline__ void tri_step_tc(float (&r)[L], const float (&c)[L], float (&cn)[L], const float* ABt, unsigned char* AI, int col) {
+    if (S_ + 1 < L) tri_fetch_row<(S_ + 1 < L ? S_ + 1 : 0)>(cn, ABt);
+    const float ms = r[S_];
+    *reinterpret_cast<float*>(AI + kchunk(S_, col >> 2, 512) + (col & 3) * 4) = ms;
+#pragma unroll
+    for (int tq = S_ + 1; tq < L; ++tq) r[tq] = fmaf(c[tq], ms, r[tq]);
+}
+__device__ __forceinline__ void tri_inverse_tc(const float* ABt, unsigned char* AI, int col) {
+    float r[L], ca[L], cb[L];
+#pragma unroll
+    for (int tq = 0; tq < L; ++tq) r[tq] = (tq == col) ? 1.f : 0.f;
+    tri_fetch_row<0>(ca, ABt);
+    tri_step_tc<0>(r, ca, cb, ABt, AI, col);   tri_step_tc<1>(r, cb, ca, ABt, AI, col);
+    tri_step_tc<2>(r, ca, cb, ABt, AI, col);   tri_step_tc<3>(r, cb, ca, ABt, AI, col);
+    tri_step_tc<4>(r, ca, cb, ABt, AI, col);   tri_step_tc<5>(r, cb, ca, ABt, AI, col);
+    tri_step_tc<6>(r, ca, cb, ABt, AI, col);   tri_step_tc<7>(r, cb, ca, ABt, AI, col);
+    tri_step_tc<8>(r, ca, cb, ABt, AI, col);   tri_step_tc<9>(r, cb, ca, ABt, AI, col);
+    tri_step_tc<10>(r, ca, cb, ABt, AI, col);  tri_step_tc<11>(r, cb, ca, ABt, AI, col);
+    tri_step_tc<12>(r, ca, cb, ABt, AI, col);  tri_step_tc<13>(r, cb, ca, ABt, AI, col);
+    tri_step_tc<14>(r, ca, cb, ABt, AI, col);  tri_step_tc<15>(r, cb, ca, ABt, AI, col);
+}
+
+__device__ __forceinline__ float rnd(float x) { return __uint_as_float(tf32_rna(x)); }
+// two 16-byte chunks of an operand tile; R: round to TF32 (nearest) first, otherwise the tensor core
+// truncates the low 13 mantissa bits when it reads the operand
+template <bool R> __device__ __forceinline__ void store8t(unsigned char* p0, unsigned char* p1, const float (&f)[8]) {
+    if (R) {
+        *reinterpret_cast<float4*>(p0) = make_float4(rnd(f[0]), rnd(f[1]), rnd(f[2]), rnd(f[3]));
+        *reinterpret_cast<float4*>(p1) = make_float4(rnd(f[4]), rnd(f[5]), rnd(f[6]), rnd(f[7]));
+    } else {
+        *reinterpret_cast<float4*>(p0) = make_float4(f[0], f[1], f[2], f[3]);
+        *reinterpret_cast<float4*>(p1) = make_float4(f[4], f[5], f[6], f[7]);
+    }
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int G, bool RND>
+__global__ void __launch_bounds__(32 * (4 * G + 1), G <= 2 ? 2 : 1) wkv7_fwd_tc_kernel(FwdParams p) {
+    using IoT = __nv_bfloat16;
+    constexpr int NCOLS = (C_SCORE + 32 * G <= 256) ? 256 : 512;
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* sm = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+    Ctrl* ctrl = reinterpret_cast<Ctrl*>(sm + G * G_BYTES);
+
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // provably warp-uniform
+    const long long bh = blockIdx.x;
+    const long long bi = bh / p.H, hi = bh % p.H;
+    const long long base = bi * p.st.b + hi * p.st.h;
+    const int nchunks = (int)(p.T / L);
+
+    if (tid == 0) {
+        for (int g = 0; g < G; ++g) {
+            mbar_init(&ctrl->full[g], 128);
+            mbar_init(&ctrl->done[g], 1);
+            mbar_init(&ctrl->rdone[g], 128);
+            mbar_init(&ctrl->score[g], 1);
+        }
+        mbar_init(&ctrl->hop, 1);
+        ctrl->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // the off-diagonal zeros of the decay blocks are written once
+    for (int i = tid; i < G * (2048 / 16); i += blockDim.x)
+        *reinterpret_cast<uint4*>(sm + (i / 128) * G_BYTES + G_DF + (i % 128) * 16) = make_uint4(0, 0, 0, 0);
+    if (warp == 4 * G) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctrl->tmem_base)), "r"(NCOLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = ctrl->tmem_base;
+
+    // initial state -> tensor memory buffer 0 (and checkpoint 0): warp w of group 0 owns lanes 32w..32w+31,
+    // of which lanes 0-15 hold value rows 16w..16w+15
+    if (warp < 4) {
+        const int i = 16 * warp + (lane & 15);
+        const float* s0 = p.s0 ? p.s0 + bh * N * N + i * N : nullptr;
+        float* ck = (p.ckpt && lane < 16) ? p.ckpt + bh * nchunks * (long long)(N * N) + i * N : nullptr;
+#pragma unroll
+        for (int cb = 0; cb < N; cb += 16) {
+            uint32_t v[16];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 x = s0 ? *reinterpret_cast<const float4*>(s0 + cb + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[4 * q] = __float_as_uint(x.x); v[4 * q + 1] = __float_as_uint(x.y); v[4 * q + 2] = __float_as_uint(x.z); v[4 * q + 3] = __float_as_uint(x.w);
+                if (ck) *reinterpret_cast<float4*>(ck + cb + 4 * q) = x;
+            }
+            tmem_st16(tmem + ((uint32_t)(32 * warp) << 16) + C_S + cb, v);
+        }
+        tmem_st_wait();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    if (warp == 4 * G) {
+        // ------------------------------ chain: one elected thread ------------------------------
+        if (elect_one()) {
+            const uint32_t sb = smem_u32(sm);
+            uint32_t hop_phase = 0;
+#ifdef WKV7_TIMING
+            long long tacc[8] = {}, tprev = clock64();
+#endif
+            for (int c = 0; c < nchunks; ++c) {
+                const int g = c % G, k = c / G;
+                const uint32_t gb = sb + g * G_BYTES;
+                const uint64_t dWAQ = desc_kmajor(gb + G_WAQ, 2048), dSC = desc_kmajor(gb + G_SC, 512), dAI = desc_kmajor(gb + G_AI, 512),
+                               dQB = desc_kmajor(gb + G_QB, 512), dDF = desc_kmajor(gb + G_DF, 256);
+                const uint64_t dV = desc_mnmajor(gb + G_V), dKWF = desc_mnmajor(gb + G_KWF), dBWF = desc_mnmajor(gb + G_BWF);
+                const uint32_t Sa = tmem + C_S + 64 * (c & 1), Sn = tmem + C_S + 64 * ((c + 1) & 1), XY = tmem + C_XY, U = tmem + C_U;
+                TCK(0)
+                mbar_wait<true>(&ctrl->full[g], k & 1, ctrl, p.status);
+                TCK(1)
+                if (c > 0) mbar_wait<true>(&ctrl->rdone[(c - 1) % G], ((c - 1) / G) & 1, ctrl, p.status);
+                tc_fence_after();
+                TCK(2)
+                // hop 1
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) mma_ts(XY, Sa + 8 * ks, dWAQ + (uint64_t)(ks * 16), idesc(32, false, false), ks > 0);
+#pragma unroll
+                for (int ks = 0; ks < 2; ++ks) mma_ss(XY, dV + (uint64_t)(ks * 64), dSC + (uint64_t)(ks * 16), idesc(32, true, false), 1);
+                tc_commit(&ctrl->hop);
+                // decay of the old state goes into the other buffer while hop 1 drains
+#pragma unroll
+                for (int s = 0; s < 8; ++s) mma_ts(Sn + 8 * s, Sa + 8 * s, dDF + (uint64_t)(s * 16), idesc(8, false, false), 0);
+                TCK(3)
+                mbar_wait<false>(&ctrl->hop, hop_phase++ & 1, ctrl, p.status);
+                tc_fence_after();
+                TCK(4)
+                // hop 2
+#pragma unroll
+                for (int ks = 0; ks < 2; ++ks) mma_ts(U, XY + 8 * ks, dAI + (uint64_t)(ks * 16), idesc(16, false, false), ks > 0);
+                tc_commit(&ctrl->hop);
+#pragma unroll
+                for (int ks = 0; ks < 2; ++ks) mma_ss(Sn, dV + (uint64_t)(ks * 64), dKWF + (uint64_t)(ks * 64), idesc(64, true, true), 1);
+                mbar_wait<false>(&ctrl->hop, hop_phase++ & 1, ctrl, p.status);
+                tc_fence_after();
+                TCK(5)
+                // hop 3 and the U part of the state update
+#pragma unroll
+                for (int ks = 0; ks < 2; ++ks) mma_ts(XY + 16, U + 8 * ks, dQB + (uint64_t)(ks * 16), idesc(16, false, false), 1);
+#pragma unroll
+                for (int ks = 0; ks < 2; ++ks) mma_ts(Sn, U + 8 * ks, dBWF + (uint64_t)(ks * 64), idesc(64, false, true), 1);
+                tc_commit(&ctrl->done[g]);
+                tc_commit(&ctrl->hop);
+                TCK(6)
+                mbar_wait<false>(&ctrl->hop, hop_phase++ & 1, ctrl, p.status);  // S' is the next chunk's A operand
+                tc_fence_after();
+                TCK(7)
+            }
+#ifdef WKV7_TIMING
+            if (blockIdx.x == 0)
+                printf("chain: loop %lld | wait full %lld | wait rdone %lld | issue hop1+decay %lld | wait hop1 %lld | hop2+kwf issue+wait %lld | issue hop3 %lld | wait last %lld (cycles per chunk)\n",
+                       tacc[0] / nchunks, tacc[1] / nchunks, tacc[2] / nchunks, tacc[3] / nchunks, tacc[4] / nchunks, tacc[5] / nchunks, tacc[6] / nchunks, tacc[7] / nchunks);
+#endif
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ preparation group ---------------------------------------
+        const int grp = warp >> 2, wg = warp & 3, gt = tid & 127;
+        unsigned char* gs = sm + grp * G_BYTES;
+        const uint32_t tlane = tmem + ((uint32_t)(32 * wg) << 16);
+        const IoT* gin[6] = {(const IoT*)p.r + base, (const IoT*)p.w + base, (const IoT*)p.k + base,
+                             (const IoT*)p.a + base, (const IoT*)p.b + base, (const IoT*)p.v + base};
+        IoT* gy = (IoT*)p.y + base;
+        auto issue_raw = [&](int c) {
+            const int r = gt >> 3, seg = gt & 7;
+            const long long goff = ((long long)c * L + r) * p.st.t;
+#pragma unroll
+            for (int ten = 0; ten < 6; ++ten)
+                cp_async16(gs + G_RAW + ten * RAW_TILE + r * ROWB + seg * 16, reinterpret_cast<const unsigned char*>(gin[ten] + goff) + seg * 16);
+            cp_async_commit();
+        };
+        const int row = lane & 15, j0 = 16 * wg + 8 * (lane >> 4);
+        if (grp < nchunks) issue_raw(grp);
+        int k = 0;
+#ifdef WKV7_TIMING
+        long long tacc[10] = {}, tprev = clock64();
+#endif
+        for (int c = grp; c < nchunks; c += G, ++k) {
+            cp_async_wait<0>();
+            group_bar(grp);
+            TCK(0)
+            // ---------------- decay scan and operand tiles ----------------------------------------
+            // One thread = one time step x 8 adjacent key channels.  The three transcendentals per
+            // element go to the special-function unit: with the matrix products on tcgen05 the FMA
+            // pipe and the issue slots are what this kernel runs out of, not MUFU throughput.
+            {
+                const unsigned char* raw = gs + G_RAW + row * ROWB + j0 * 2;
+                float cum[8], q[8], kk[8], a[8], b[8], v[8];
+                load8<IoT>(raw + 1 * RAW_TILE, cum);
+                load8<IoT>(raw + 0 * RAW_TILE, q);
+                load8<IoT>(raw + 2 * RAW_TILE, kk);
+                load8<IoT>(raw + 3 * RAW_TILE, a);
+                load8<IoT>(raw + 4 * RAW_TILE, b);
+                load8<IoT>(raw + 5 * RAW_TILE, v);
+                // log2 of the per-step decay: -exp(w) * log2(e); running sum along the 16 time rows
+#pragma unroll
+                for (int i = 0; i < 8; ++i) cum[i] = ex2_approx(cum[i] * 1.4426950408889634f) * -1.4426950408889634f;
+#pragma unroll
+                for (int d = 1; d < 16; d <<= 1)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float up = __shfl_up_sync(0xffffffffu, cum[i], d, 16);
+                        if (row >= d) cum[i] += up;
+                    }
+                float o[6][8], fwv[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float cc = fmaxf(cum[i], -115.f);  // keeps P_t and 1/P_t finite (2^-115 ~ e^-80)
+                    const float incl = ex2_approx(cc);
+                    const float inv = ex2_approx(-cc);
+                    const float up = __shfl_up_sync(0xffffffffu, incl, 1, 16);
+                    const float non = row == 0 ? 1.f : up;
+                    const float fw = __shfl_sync(0xffffffffu, incl, 15, 16);
+                    o[0][i] = q[i] * incl;   // wq
+                    o[1][i] = a[i] * non;    // wa
+                    o[2][i] = kk[i] * inv;   // kwi
+                    o[3][i] = b[i] * inv;    // bwi
+                    o[4][i] = o[2][i] * fw;  // kwf
+                    o[5][i] = o[3][i] * fw;  // bwf
+                    fwv[i] = fw;
+                }
+                const int jc = j0 >> 2;
+                store8t<RND>(gs + G_WAQ + kchunk(row, jc, 2048), gs + G_WAQ + kchunk(row, jc + 1, 2048), o[1]);
+                store8t<RND>(gs + G_WAQ + kchunk(16 + row, jc, 2048), gs + G_WAQ + kchunk(16 + row, jc + 1, 2048), o[0]);
+                store8t<RND>(gs + G_KB + kchunk(row, jc, 2048), gs + G_KB + kchunk(row, jc + 1, 2048), o[2]);
+                store8t<RND>(gs + G_KB + kchunk(16 + row, jc, 2048), gs + G_KB + kchunk(16 + row, jc + 1, 2048), o[3]);
+                const int mo = (j0 >> 5) * 2048 + row * 128 + ((((j0 & 31) >> 3) ^ (row & 3)) << 5);
+                store8t<RND>(gs + G_KWF + mo, gs + G_KWF + mo + 16, o[4]);
+                store8t<RND>(gs + G_BWF + mo, gs + G_BWF + mo + 16, o[5]);
+                store8t<false>(gs + G_V + mo, gs + G_V + mo + 16, v);  // bf16 values are exact in TF32
+                if (row == 15) {
+                    unsigned char* df = gs + G_DF + (j0 >> 3) * 256;
+#pragma unroll
+                    for (int n = 0; n < 8; ++n) *reinterpret_cast<float*>(df + (n >> 2) * 128 + n * 16 + (n & 3) * 4) = RND ? rnd(fwv[n]) : fwv[n];
+                }
+            }
+            TCK(1)
+            fence_async_smem();
+            TCK(8)
+            group_bar(grp);
+            if (c + G < nchunks) issue_raw(c + G);
+            TCK(2)
+            // ---------------- the four score matrices as one product ---------------------------------
+            if (wg == 0 && elect_one()) {
+                const uint64_t dA = desc_kmajor(smem_u32(gs + G_WAQ), 2048), dB = desc_kmajor(smem_u32(gs + G_KB), 2048);
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) mma_ss(tmem + C_SCORE + 32 * grp, dA + (uint64_t)(ks * 16), dB + (uint64_t)(ks * 16), idesc(32, false, false), ks > 0);
+                tc_commit(&ctrl->score[grp]);
+            }
+            __syncwarp();
+            if (wg < 2) {
+                mbar_wait<true>(&ctrl->score[grp], k & 1, ctrl, p.status);
+                tc_fence_after();
+                TCK(3)
+                uint32_t sv[32];
+                tmem_ld16(tlane + C_SCORE + 32 * grp, sv);
+                tmem_ld16(tlane + C_SCORE + 32 * grp + 16, sv + 16);
+                tmem_ld_wait();
+                const int t = lane;
+                if (wg == 0) {
+                    // lane t: row t of AK (strictly lower) and of AB (strictly lower, kept transposed for the inverse)
+                    if (lane < 16) {
+                        float* ABt = reinterpret_cast<float*>(gs + G_ABT);
+#pragma unroll
+                        for (int qd = 0; qd < 4; ++qd) {
+                            float4 o;
+                            o.x = (4 * qd + 0 < t) ? rnd(__uint_as_float(sv[4 * qd + 0])) : 0.f;
+                            o.y = (4 * qd + 1 < t) ? rnd(__uint_as_float(sv[4 * qd + 1])) : 0.f;
+                            o.z = (4 * qd + 2 < t) ? rnd(__uint_as_float(sv[4 * qd + 2])) : 0.f;
+                            o.w = (4 * qd + 3 < t) ? rnd(__uint_as_float(sv[4 * qd + 3])) : 0.f;
+                            *reinterpret_cast<float4*>(gs + G_SC + kchunk(t, qd, 512)) = o;
+                        }
+#pragma unroll
+                        for (int s = 0; s < 16; ++s) ABt[s * SCS + t] = (s < t) ? __uint_as_float(sv[16 + s]) : 0.f;
+                    }
+                    __syncwarp();
+                    if (lane < 16) tri_inverse_tc(reinterpret_cast<const float*>(gs + G_ABT), gs + G_AI, lane);
+                } else if (lane < 16) {
+                    // lane t: row t of QK and QB (lower triangular including the diagonal)
+#pragma unroll
+                    for (int qd = 0; qd < 4; ++qd) {
+                        float4 o, o2;
+                        o.x = (4 * qd + 0 <= t) ? rnd(__uint_as_float(sv[4 * qd + 0])) : 0.f;
+                        o.y = (4 * qd + 1 <= t) ? rnd(__uint_as_float(sv[4 * qd + 1])) : 0.f;
+                        o.z = (4 * qd + 2 <= t) ? rnd(__uint_as_float(sv[4 * qd + 2])) : 0.f;
+                        o.w = (4 * qd + 3 <= t) ? rnd(__uint_as_float(sv[4 * qd + 3])) : 0.f;
+                        o2.x = (4 * qd + 0 <= t) ? rnd(__uint_as_float(sv[16 + 4 * qd + 0])) : 0.f;
+                        o2.y = (4 * qd + 1 <= t) ? rnd(__uint_as_float(sv[16 + 4 * qd + 1])) : 0.f;
+                        o2.z = (4 * qd + 2 <= t) ? rnd(__uint_as_float(sv[16 + 4 * qd + 2])) : 0.f;
+                        o2.w = (4 * qd + 3 <= t) ? rnd(__uint_as_float(sv[16 + 4 * qd + 3])) : 0.f;
+                        *reinterpret_cast<float4*>(gs + G_SC + kchunk(16 + t, qd, 512)) = o;
+                        *reinterpret_cast<float4*>(gs + G_QB + kchunk(t, qd, 512)) = o2;
+                    }
+                }
+            }
+            TCK(4)
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(&ctrl->full[grp]);
+            // ---------------- results of this chunk -------------------------------------------------
+            mbar_wait<true>(&ctrl->done[grp], k & 1, ctrl, p.status);
+            tc_fence_after();
+            TCK(5)
+            const bool last = c + 1 == nchunks;
+            float* sdst = last ? (p.sT ? p.sT + bh * N * N : nullptr)
+                               : (p.ckpt ? p.ckpt + (bh * nchunks + c + 1) * (long long)(N * N) : nullptr);
+#ifdef WKV7_TC_NOCKPT
+            sdst = nullptr;
+#endif
+            uint32_t yv[16], sv2[64];
+            tmem_ld16(tlane + C_XY + 16, yv);
+            if (sdst) {
+#pragma unroll
+                for (int cb = 0; cb < 64; cb += 16) tmem_ld16(tlane + C_S + 64 * ((c + 1) & 1) + cb, sv2 + cb);
+            }
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(&ctrl->rdone[grp]);
+            TCK(6)
+            // Y^T sits one value row per thread; it goes through shared memory (the [kwi;bwi] tile is dead
+            // once the score product has completed) so that each thread stores 16 contiguous bytes.
+            unsigned char* ys = gs + G_KB;
+            if (lane < 16) {
+                const int i = 16 * wg + lane;
+#pragma unroll
+                for (int t = 0; t < 16; ++t) *reinterpret_cast<IoT*>(ys + t * ROWB + i * 2) = __float2bfloat16_rn(__uint_as_float(yv[t]));
+                if (sdst) {
+                    // 32-byte stores: every lane writes whole sectors of its own 256-byte state row
+                    float* d = sdst + i * N;
+#pragma unroll
+                    for (int q8 = 0; q8 < 8; ++q8)
+                        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(d + 8 * q8), "r"(sv2[8 * q8]), "r"(sv2[8 * q8 + 1]),
+                                     "r"(sv2[8 * q8 + 2]), "r"(sv2[8 * q8 + 3]), "r"(sv2[8 * q8 + 4]), "r"(sv2[8 * q8 + 5]), "r"(sv2[8 * q8 + 6]), "r"(sv2[8 * q8 + 7]) : "memory");
+                }
+            }
+            group_bar(grp);
+            {
+                const int r = gt >> 3, seg = gt & 7;
+                *reinterpret_cast<uint4*>(gy + ((long long)c * L + r) * p.st.t + seg * 8) = *reinterpret_cast<const uint4*>(ys + r * ROWB + seg * 16);
+            }
+            TCK(7)
+        }
+#ifdef WKV7_TIMING
+        if (blockIdx.x == 0 && lane == 0 && k > 0)
+            printf("group %d warp %d: load wait %lld | P1 %lld | bar+prefetch %lld | score issue+wait %lld | P2 %lld | wait done %lld | tmem read %lld | stores %lld | P1 fence %lld (cycles per own chunk)\n",
+                   grp, wg,  tacc[0] / k, tacc[1] / k, tacc[2] / k, tacc[3] / k, tacc[4] / k, tacc[5] / k, tacc[6] / k, tacc[7] / k, tacc[8] / k);
+#endif
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4 * G) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(NCOLS) : "memory");
+    }
+}
+
+template <int G, bool RND> static int launch_t(const FwdParams& p, cudaStream_t stream) {
+    auto kern = wkv7_fwd_tc_kernel<G, RND>;
+    const int smem = G * G_BYTES + (int)sizeof(Ctrl) + 1024;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kLaunchFailed;
+    kern<<<(unsigned)(p.B * p.H), 32 * (4 * G + 1), smem, stream>>>(p);
+    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
+}  // namespace tc
+
+int launch_fwd_tc(const FwdParams& p, int groups, cudaStream_t stream) {
+    switch (groups) {
+        case 2: return tc::launch_t<2, false>(p, stream);
+        case 3: return tc::launch_t<3, false>(p, stream);
+        case 4: return tc::launch_t<4, false>(p, stream);
+        case -2: return tc::launch_t<2, true>(p, stream);
+        case -3: return tc::launch_t<3, true>(p, stream);
+        case -4: return tc::launch_t<4, true>(p, stream);
+        default: return kBadShape;
+    }
+}
+
+}  // namespace wkv7
