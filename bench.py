@@ -281,7 +281,8 @@ def run_ours(args):
                          'unit': 'GB/s', 'frac': achieved / peak, 'peak_source': which,
                          'traffic': BWD_DRAM_TRAFFIC_BYTES, 'algorithmic_bytes': bwd_bytes,
                          'kernel_ms': bwd_ms,
-                         'fwd': {'kernel': 'wkv7_fwd_kernel', 'kernel_ms': fwd_ms, 'algorithmic_bytes': fwd_bytes,
+                         'fwd': {'kernel': 'wkv7_fwd_tc_kernel (tcgen05)' if _lib.lib().wkv7_get_fwd_impl() else 'wkv7_fwd_kernel (mma.sync)',
+                                 'kernel_ms': fwd_ms, 'algorithmic_bytes': fwd_bytes,
                                  'achieved': fwd_bytes / (fwd_ms * 1e-3) / 1e9,
                                  'frac': fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak},
                          'step_frac': (fwd_bytes + bwd_bytes) / (ms_per_step * 1e-3) / 1e9 / peak},

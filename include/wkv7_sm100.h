@@ -57,9 +57,21 @@ const char* wkv7_status_string(int status);
 int64_t wkv7_checkpoint_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
 
 /* Reads and clears the device-side status word of the current device (synchronises the
- * device).  Reserved for kernels with bounded device-side waits; the current kernels never
- * spin-wait, so this returns 0. */
+ * device).  The tcgen05 forward waits on mbarriers with a cycle limit; a wait that runs out makes the
+ * CTA finish early and leaves WKV7_ERR_DEVICE_TIMEOUT here.  0 otherwise. */
 int wkv7_device_status(void);
+
+/*
+ * Which kernel wkv7_fwd runs for io_dtype WKV7_BF16 (no reference counterpart: the reference has one
+ * forward kernel per dtype).  0: the warp-MMA kernel (mma.sync TF32, state in registers).  2, 3, 4: the
+ * tcgen05 kernel (state in tensor memory) with that many preparation groups per CTA; negative values
+ * select the same kernel without the producer-side rounding of operands to TF32 (the tensor core then
+ * truncates them: 0.4 % faster, about twice the state error).  The default is 4, or the value of the environment variable WKV7_FWD_TC when the library
+ * is loaded.  Returns WKV7_ERR_SHAPE for any other value.  wkv7_attn_ln_fwd and the fp32 dtypes always
+ * use the warp-MMA kernel.
+ */
+int wkv7_set_fwd_impl(int impl);
+int wkv7_get_fwd_impl(void);
 
 /*
  * WKV7 forward.  Replaces cuda_forward / forward_kernel of the reference

@@ -23,6 +23,16 @@ N = 64
 NAMES = 'rwkvab'
 
 
+@pytest.fixture(params=[4, 0], ids=['tcgen05', 'mma'], autouse=True)
+def fwd_impl(request):
+    """Every test of this file runs with both bf16 forward kernels: the tcgen05 kernel (state in tensor
+    memory, 4 preparation groups: the default) and the warp-MMA kernel.  The fp32 paths ignore it."""
+    from wind_rwkv.rwkv7 import _lib
+    old = _lib.set_fwd_impl(request.param)
+    yield request.param
+    _lib.set_fwd_impl(old)
+
+
 def _mods():
     import c_oracle
     from wind_rwkv.rwkv7 import _lib, attn, synthetic
@@ -97,6 +107,20 @@ def test_single_chunk(dtype):
 @pytest.mark.parametrize('dtype', [th.float32, th.bfloat16])
 def test_state_in_and_state_gradient(dtype):
     run_case(2, 256, 3, dtype, s0=True, dsT=True, seed=3)
+
+
+@pytest.mark.parametrize('impl', [2, 3, -2, -3, -4])
+def test_tcgen05_variants(impl):
+    """The other builds of the tcgen05 forward: 2 and 3 preparation groups, and operands left for the tensor
+    core to truncate (negative) instead of rounded to TF32 by their producer."""
+    from wind_rwkv.rwkv7 import _lib
+    old = _lib.set_fwd_impl(impl)
+    try:
+        run_case(2, 256, 3, th.bfloat16, s0=True, dsT=True, seed=4)
+        run_case(1, 16, 1, th.bfloat16, seed=6)   # fewer chunks than groups
+        run_case(1, 48, 2, th.bfloat16, s0=True, seed=7)
+    finally:
+        _lib.set_fwd_impl(old)
 
 
 @pytest.mark.parametrize('dtype', [th.float32, th.bfloat16])

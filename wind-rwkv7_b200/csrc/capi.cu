@@ -1,5 +1,6 @@
 // extern "C" entry points of libwkv7_sm100.so (declared in include/wkv7_sm100.h): host-side
 // validation, the per-device status word, and dispatch to the kernel launchers.
+#include <atomic>
 #include <cstdlib>
 #include "../../include/wkv7_sm100.h"
 #include "wkv7_kernels.h"
@@ -41,16 +42,16 @@ float* static_scratch() {
     return cache[dev];
 }
 
-// Forward implementation for bf16 attn: the tcgen05 kernel with 2 to 4 preparation groups (negative:
-// operands rounded to TF32 by the producer instead of truncated by the tensor core), or (0) the
-// warp-MMA kernel.  WKV7_FWD_TC = 0 | 2..4 | -2..-4 overrides the default; read once.
-int fwd_tc_groups() {
-    static const int v = [] {
+// Forward implementation for bf16 attn (see wkv7_set_fwd_impl in the header): 0 = warp-MMA kernel,
+// +-2..4 = tcgen05 kernel with that many preparation groups.
+bool valid_fwd_impl(int x) { return x == 0 || (x >= 2 && x <= 4) || (x <= -2 && x >= -4); }
+std::atomic<int>& fwd_impl() {
+    static std::atomic<int> v([] {
         const char* e = std::getenv("WKV7_FWD_TC");
-        if (!e) return 2;
+        if (!e) return 4;
         const int x = std::atoi(e);
-        return (x >= -4 && x <= 4 && (x >= 2 || x <= -2)) ? x : 0;
-    }();
+        return valid_fwd_impl(x) ? x : 0;
+    }());
     return v;
 }
 
@@ -94,6 +95,14 @@ int64_t wkv7_checkpoint_bytes(int64_t B, int64_t T, int64_t H, int64_t N) {
     return B * H * (T / wkv7::L) * N * N * (int64_t)sizeof(float);
 }
 
+int wkv7_set_fwd_impl(int impl) {
+    if (!valid_fwd_impl(impl)) return WKV7_ERR_SHAPE;
+    fwd_impl().store(impl, std::memory_order_relaxed);
+    return WKV7_OK;
+}
+
+int wkv7_get_fwd_impl(void) { return fwd_impl().load(std::memory_order_relaxed); }
+
 int wkv7_device_status(void) {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, g_status_word, sizeof(int)) != cudaSuccess) return WKV7_ERR_LAUNCH;
@@ -130,7 +139,7 @@ static int fwd_common(const void* r, const void* w, const void* k, const void* v
     p.status = status_ptr();
     if (!p.status) return WKV7_ERR_LAUNCH;
     if (io_dtype == WKV7_BF16 && !ln) {
-        const int groups = fwd_tc_groups();
+        const int groups = fwd_impl().load(std::memory_order_relaxed);
         if (groups) return wkv7::launch_fwd_tc(p, groups, (cudaStream_t)stream);
     }
     return wkv7::launch_fwd(p, io_dtype, ln, (cudaStream_t)stream);

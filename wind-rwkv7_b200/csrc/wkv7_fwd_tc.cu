@@ -19,9 +19,16 @@
 // in the shared-memory layouts the tensor core reads directly, the four 16x16 score matrices as
 // ONE tcgen05 product ([wa;wq] x [kwi;bwi]^T, M = 64 of which 32 rows are used), masking, the
 // triangular inverse, and afterwards the read-back of Y (and of the chunk-end state for the
-// checkpoints) from tensor memory.  The chain thread only waits for "operands of chunk c ready" and
-// "results of chunk c-1 read", so the 16-step dependency is ~1000 cycles per chunk while the
-// preparation of later chunks proceeds in parallel.
+// checkpoints) from tensor memory.  A group's loop is software-pipelined: the decay scan of its next
+// chunk is computed into registers while the chain works on its previous chunk, and the read-back of
+// that chunk's results happens just before the operand tiles are overwritten.
+//
+// Warp roles (128 (G+1) threads): warps 0..4G-1 are the preparation groups, warp 4G issues the chain,
+// the remaining three warps of its warp group only exist so that setmaxnreg can be used: the chain
+// warp group shrinks to 32 registers per thread and the preparation warps grow to 112 (a kernel-wide
+// 96, which is all that 20 warps leave, makes the decay scan spill, and the spills cost more than
+// the whole scan).  The chain thread waits for "operands of chunk c ready" and "results of chunk c-2
+// read", so the 16-step dependency is ~1100 cycles per chunk.
 //
 // Shared-memory operand layouts (no TMA: the tiles are produced by threads, not copied):
 //   K-major (contraction index contiguous): 16-byte chunks [row/8][k/4][row%8][k%4], descriptor
@@ -44,8 +51,8 @@
 namespace wkv7 {
 namespace tc {
 
-constexpr int ROWB = 2 * N + 16;    // staging row of a bf16 input tile (bytes, padded against bank conflicts)
-constexpr int RAW_TILE = L * ROWB;  // 2304
+constexpr int ROWB = 2 * N;         // staging row of a bf16 input tile: 128 bytes, its eight 16-byte segments XOR-ed with (row % 8)
+constexpr int RAW_TILE = L * ROWB;  // 2048
 
 // per-group shared memory (byte offsets; tensor-core tiles first, all 1024-byte aligned)
 constexpr int G_WAQ = 0;       // [wa;wq]   32 rows x 64, K-major            8192
@@ -59,14 +66,14 @@ constexpr int G_AI = 30720;    // AI       16 x 16, K-major                  102
 constexpr int G_QB = 31744;    // QB       16 x 16, K-major                  1024
 constexpr int G_DF = 32768;    // eight 8x8 diagonal blocks of fw, K-major   2048
 constexpr int G_ABT = 34816;   // AB transposed, fp32 [16][SCS]              1536
-constexpr int G_RAW = 36352;   // q, w, k, a, b, v staging                   6 * 2304
-constexpr int G_BYTES = 50176; // 49 KB
+constexpr int G_RAW = 36352;   // q, w, k, a, b, v staging                   6 * 2048
+constexpr int G_BYTES = 49152; // 48 KB (36352 + 12288 = 48640, rounded up to 1 KB)
 
 // tensor-memory columns (32-bit each, 128 lanes; the M = 64 products use lanes 0-15 of each 32-lane quarter)
 constexpr int C_S = 0;      // two 64-column state buffers
-constexpr int C_XY = 128;   // X (16) | Y (16)
-constexpr int C_U = 160;    // U (16)
-constexpr int C_SCORE = 176;  // + 32 * group: [AK|AB] in lanes 0-15, [QK|QB] in lanes 32-47
+constexpr int C_XY = 128;   // two buffers of X (16) | Y (16)
+constexpr int C_U = 192;    // U (16)
+constexpr int C_SCORE = 208;  // + 32 * group: [AK|AB] in lanes 0-15, [QK|QB] in lanes 32-47
 
 constexpr long long WAIT_LIMIT = 1LL << 28;  // cycles (~0.15 s): far beyond any legitimate wait
 
@@ -191,6 +198,20 @@ template <bool R> __device__ __forceinline__ void store8t(unsigned char* p0, uns
         *reinterpret_cast<float4*>(p1) = make_float4(f[4], f[5], f[6], f[7]);
     }
 }
+// 32 bytes of an MN-major tile in two 16-byte stores; `flip` swaps the order of the two halves so that the
+// eight lanes of a quarter-warp (rows r..r+7, where r and r+4 share a 32-byte unit) never hit the same bank
+template <bool R> __device__ __forceinline__ void store8mn(unsigned char* p, const float (&f)[8], bool flip) {
+    float x[4], y[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float lo = R ? rnd(f[i]) : f[i], hi = R ? rnd(f[4 + i]) : f[4 + i];
+        x[i] = flip ? hi : lo;  // goes out first
+        y[i] = flip ? lo : hi;
+    }
+    const int off = flip ? 16 : 0;
+    *reinterpret_cast<float4*>(p + off) = make_float4(x[0], x[1], x[2], x[3]);
+    *reinterpret_cast<float4*>(p + (16 - off)) = make_float4(y[0], y[1], y[2], y[3]);
+}
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -198,9 +219,16 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 template <int G, bool RND>
-__global__ void __launch_bounds__(32 * (4 * G + 1), G <= 2 ? 2 : 1) wkv7_fwd_tc_kernel(FwdParams p) {
+__global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams p) {
     using IoT = __nv_bfloat16;
-    constexpr int NCOLS = (C_SCORE + 32 * G <= 256) ? 256 : 512;
+    constexpr int NCOLS = 512;
+    static_assert(C_SCORE + 32 * G <= NCOLS, "tensor memory columns");
+    // Register reallocation (G == 4 only).  setmaxnreg.inc blocks, without a bound, until the CTA's
+    // register pool can satisfy it, and the pool is what the CTA was launched with: 640 threads x 96
+    // registers (65536 / 640 rounded down to a multiple of 8; build.py checks that ptxas reports 96).
+    // The raised and lowered counts must therefore fit into that pool exactly or with room to spare.
+    constexpr int LAUNCH_REGS = 96, PREP_REGS = 112, CHAIN_REGS = 32;
+    static_assert(G != 4 || 128 * G * PREP_REGS + 128 * CHAIN_REGS <= 128 * (G + 1) * LAUNCH_REGS, "setmaxnreg would never be satisfied");
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* sm = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
     Ctrl* ctrl = reinterpret_cast<Ctrl*>(sm + G * G_BYTES);
@@ -226,7 +254,7 @@ __global__ void __launch_bounds__(32 * (4 * G + 1), G <= 2 ? 2 : 1) wkv7_fwd_tc_
     // the off-diagonal zeros of the decay blocks are written once
     for (int i = tid; i < G * (2048 / 16); i += blockDim.x)
         *reinterpret_cast<uint4*>(sm + (i / 128) * G_BYTES + G_DF + (i % 128) * 16) = make_uint4(0, 0, 0, 0);
-    if (warp == 4 * G) {
+    if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctrl->tmem_base)), "r"(NCOLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -258,9 +286,10 @@ __global__ void __launch_bounds__(32 * (4 * G + 1), G <= 2 ? 2 : 1) wkv7_fwd_tc_
     __syncthreads();
     tc_fence_after();
 
-    if (warp == 4 * G) {
-        // ------------------------------ chain: one elected thread ------------------------------
-        if (elect_one()) {
+    if (warp >= 4 * G) {
+        // ------------------------------ chain warp group -----------------------------------------
+        if (G == 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(CHAIN_REGS));
+        if (warp == 4 * G && elect_one()) {
             const uint32_t sb = smem_u32(sm);
             uint32_t hop_phase = 0;
 #ifdef WKV7_TIMING
@@ -272,11 +301,12 @@ __global__ void __launch_bounds__(32 * (4 * G + 1), G <= 2 ? 2 : 1) wkv7_fwd_tc_
                 const uint64_t dWAQ = desc_kmajor(gb + G_WAQ, 2048), dSC = desc_kmajor(gb + G_SC, 512), dAI = desc_kmajor(gb + G_AI, 512),
                                dQB = desc_kmajor(gb + G_QB, 512), dDF = desc_kmajor(gb + G_DF, 256);
                 const uint64_t dV = desc_mnmajor(gb + G_V), dKWF = desc_mnmajor(gb + G_KWF), dBWF = desc_mnmajor(gb + G_BWF);
-                const uint32_t Sa = tmem + C_S + 64 * (c & 1), Sn = tmem + C_S + 64 * ((c + 1) & 1), XY = tmem + C_XY, U = tmem + C_U;
+                const uint32_t Sa = tmem + C_S + 64 * (c & 1), Sn = tmem + C_S + 64 * ((c + 1) & 1), XY = tmem + C_XY + 32 * (c & 1), U = tmem + C_U;
                 TCK(0)
                 mbar_wait<true>(&ctrl->full[g], k & 1, ctrl, p.status);
                 TCK(1)
-                if (c > 0) mbar_wait<true>(&ctrl->rdone[(c - 1) % G], ((c - 1) / G) & 1, ctrl, p.status);
+                // the Y buffer and the state buffer about to be overwritten were last read for chunk c-2
+                if (c > 1) mbar_wait<true>(&ctrl->rdone[(c - 2) % G], ((c - 2) / G) & 1, ctrl, p.status);
                 tc_fence_after();
                 TCK(2)
                 // hop 1
@@ -285,7 +315,7 @@ __global__ void __launch_bounds__(32 * (4 * G + 1), G <= 2 ? 2 : 1) wkv7_fwd_tc_
 #pragma unroll
                 for (int ks = 0; ks < 2; ++ks) mma_ss(XY, dV + (uint64_t)(ks * 64), dSC + (uint64_t)(ks * 16), idesc(32, true, false), 1);
                 tc_commit(&ctrl->hop);
-                // decay of the old state goes into the other buffer while hop 1 drains
+                // the decay of the old state goes into the other buffer while hop 1 drains
 #pragma unroll
                 for (int s = 0; s < 8; ++s) mma_ts(Sn + 8 * s, Sa + 8 * s, dDF + (uint64_t)(s * 16), idesc(8, false, false), 0);
                 TCK(3)
@@ -322,6 +352,7 @@ __global__ void __launch_bounds__(32 * (4 * G + 1), G <= 2 ? 2 : 1) wkv7_fwd_tc_
         __syncwarp();
     } else {
         // ------------------------------ preparation group ---------------------------------------
+        if (G == 4) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(PREP_REGS));
         const int grp = warp >> 2, wg = warp & 3, gt = tid & 127;
         unsigned char* gs = sm + grp * G_BYTES;
         const uint32_t tlane = tmem + ((uint32_t)(32 * wg) << 16);
@@ -333,12 +364,64 @@ __global__ void __launch_bounds__(32 * (4 * G + 1), G <= 2 ? 2 : 1) wkv7_fwd_tc_
             const long long goff = ((long long)c * L + r) * p.st.t;
 #pragma unroll
             for (int ten = 0; ten < 6; ++ten)
-                cp_async16(gs + G_RAW + ten * RAW_TILE + r * ROWB + seg * 16, reinterpret_cast<const unsigned char*>(gin[ten] + goff) + seg * 16);
+                cp_async16(gs + G_RAW + ten * RAW_TILE + r * ROWB + ((seg ^ (r & 7)) << 4), reinterpret_cast<const unsigned char*>(gin[ten] + goff) + seg * 16);
             cp_async_commit();
+        };
+        // Results of own chunk number kk (chunk cc): Y^T into registers, the chunk-end state straight to the
+        // checkpoint (or the final state) in two halves, then "results read" for the chain.
+        auto read_results = [&](int cc, int kk) {
+            mbar_wait<true>(&ctrl->done[grp], kk & 1, ctrl, p.status);
+            tc_fence_after();
+            const bool last = cc + 1 == nchunks;
+            float* sdst = last ? (p.sT ? p.sT + bh * N * N : nullptr)
+                               : (p.ckpt ? p.ckpt + (bh * nchunks + cc + 1) * (long long)(N * N) : nullptr);
+#ifdef WKV7_TC_NOCKPT
+            sdst = nullptr;
+#endif
+            {
+                // Y^T sits one value row per thread.  Lanes i and i^1 swap half of their 16 time steps, so that
+                // every lane holds (row i&~1, row i|1) pairs for 8 time steps and stores them as bf16x2.
+                uint32_t yv[16];
+                tmem_ld16(tlane + C_XY + 32 * (cc & 1) + 16, yv);
+                tmem_ld_wait();
+                const int odd = lane & 1;
+                IoT* yo = gy + ((long long)cc * L + odd) * p.st.t + 16 * wg + (lane & 14);
+#pragma unroll
+                for (int m = 0; m < 8; ++m) {
+                    const float mine = __uint_as_float(odd ? yv[2 * m + 1] : yv[2 * m]);
+                    const float give = __uint_as_float(odd ? yv[2 * m] : yv[2 * m + 1]);
+                    const float got = __shfl_xor_sync(0xffffffffu, give, 1);
+                    const __nv_bfloat162 pr = odd ? __floats2bfloat162_rn(got, mine) : __floats2bfloat162_rn(mine, got);
+                    if (lane < 16) *reinterpret_cast<__nv_bfloat162*>(yo + (long long)(2 * m) * p.st.t) = pr;
+                }
+            }
+            if (sdst) {
+                float* d = sdst + (16 * wg + (lane & 15)) * N;
+#pragma unroll
+                for (int qt = 0; qt < 4; ++qt) {
+                    uint32_t sv[16];
+                    tmem_ld16(tlane + C_S + 64 * ((cc + 1) & 1) + 16 * qt, sv);
+                    tmem_ld_wait();
+                    if (qt == 3) {
+                        tc_fence_before();
+                        mbar_arrive(&ctrl->rdone[grp]);
+                    }
+                    // 32-byte stores: every lane writes whole sectors of its own 256-byte state row
+                    if (lane < 16) {
+#pragma unroll
+                        for (int q8 = 0; q8 < 2; ++q8)
+                            asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(d + 16 * qt + 8 * q8), "r"(sv[8 * q8]), "r"(sv[8 * q8 + 1]),
+                                         "r"(sv[8 * q8 + 2]), "r"(sv[8 * q8 + 3]), "r"(sv[8 * q8 + 4]), "r"(sv[8 * q8 + 5]), "r"(sv[8 * q8 + 6]), "r"(sv[8 * q8 + 7]) : "memory");
+                    }
+                }
+            } else {
+                tc_fence_before();
+                mbar_arrive(&ctrl->rdone[grp]);
+            }
         };
         const int row = lane & 15, j0 = 16 * wg + 8 * (lane >> 4);
         if (grp < nchunks) issue_raw(grp);
-        int k = 0;
+        int k = 0, cprev = -1;
 #ifdef WKV7_TIMING
         long long tacc[10] = {}, tprev = clock64();
 #endif
@@ -346,13 +429,14 @@ __global__ void __launch_bounds__(32 * (4 * G + 1), G <= 2 ? 2 : 1) wkv7_fwd_tc_
             cp_async_wait<0>();
             group_bar(grp);
             TCK(0)
-            // ---------------- decay scan and operand tiles ----------------------------------------
+            // ---------------- decay scan, into registers ---------------------------------------------
             // One thread = one time step x 8 adjacent key channels.  The three transcendentals per
             // element go to the special-function unit: with the matrix products on tcgen05 the FMA
             // pipe and the issue slots are what this kernel runs out of, not MUFU throughput.
+            float o[4][8], v[8], fwv[8];  // kwf, bwf are formed from kwi, bwi and fw when the tiles are written
             {
-                const unsigned char* raw = gs + G_RAW + row * ROWB + j0 * 2;
-                float cum[8], q[8], kk[8], a[8], b[8], v[8];
+                const unsigned char* raw = gs + G_RAW + row * ROWB + (((j0 >> 3) ^ (row & 7)) << 4);
+                float cum[8], q[8], kk[8], a[8], b[8];
                 load8<IoT>(raw + 1 * RAW_TILE, cum);
                 load8<IoT>(raw + 0 * RAW_TILE, q);
                 load8<IoT>(raw + 2 * RAW_TILE, kk);
@@ -369,7 +453,6 @@ __global__ void __launch_bounds__(32 * (4 * G + 1), G <= 2 ? 2 : 1) wkv7_fwd_tc_
                         const float up = __shfl_up_sync(0xffffffffu, cum[i], d, 16);
                         if (row >= d) cum[i] += up;
                     }
-                float o[6][8], fwv[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const float cc = fmaxf(cum[i], -115.f);  // keeps P_t and 1/P_t finite (2^-115 ~ e^-80)
@@ -382,31 +465,36 @@ __global__ void __launch_bounds__(32 * (4 * G + 1), G <= 2 ? 2 : 1) wkv7_fwd_tc_
                     o[1][i] = a[i] * non;    // wa
                     o[2][i] = kk[i] * inv;   // kwi
                     o[3][i] = b[i] * inv;    // bwi
-                    o[4][i] = o[2][i] * fw;  // kwf
-                    o[5][i] = o[3][i] * fw;  // bwf
                     fwv[i] = fw;
                 }
+            }
+            TCK(1)
+            // ---------------- results of the previous own chunk (its operand tiles are free afterwards) --
+            if (cprev >= 0) read_results(cprev, k - 1);
+            TCK(2)
+            // ---------------- operand tiles -----------------------------------------------------------
+            {
                 const int jc = j0 >> 2;
                 store8t<RND>(gs + G_WAQ + kchunk(row, jc, 2048), gs + G_WAQ + kchunk(row, jc + 1, 2048), o[1]);
                 store8t<RND>(gs + G_WAQ + kchunk(16 + row, jc, 2048), gs + G_WAQ + kchunk(16 + row, jc + 1, 2048), o[0]);
                 store8t<RND>(gs + G_KB + kchunk(row, jc, 2048), gs + G_KB + kchunk(row, jc + 1, 2048), o[2]);
                 store8t<RND>(gs + G_KB + kchunk(16 + row, jc, 2048), gs + G_KB + kchunk(16 + row, jc + 1, 2048), o[3]);
                 const int mo = (j0 >> 5) * 2048 + row * 128 + ((((j0 & 31) >> 3) ^ (row & 3)) << 5);
-                store8t<RND>(gs + G_KWF + mo, gs + G_KWF + mo + 16, o[4]);
-                store8t<RND>(gs + G_BWF + mo, gs + G_BWF + mo + 16, o[5]);
-                store8t<false>(gs + G_V + mo, gs + G_V + mo + 16, v);  // bf16 values are exact in TF32
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { o[2][i] *= fwv[i]; o[3][i] *= fwv[i]; }
+                const bool flip = (row >> 2) & 1;
+                store8mn<RND>(gs + G_KWF + mo, o[2], flip);
+                store8mn<RND>(gs + G_BWF + mo, o[3], flip);
+                store8mn<false>(gs + G_V + mo, v, flip);  // bf16 values are exact in TF32
                 if (row == 15) {
                     unsigned char* df = gs + G_DF + (j0 >> 3) * 256;
 #pragma unroll
                     for (int n = 0; n < 8; ++n) *reinterpret_cast<float*>(df + (n >> 2) * 128 + n * 16 + (n & 3) * 4) = RND ? rnd(fwv[n]) : fwv[n];
                 }
             }
-            TCK(1)
             fence_async_smem();
-            TCK(8)
             group_bar(grp);
             if (c + G < nchunks) issue_raw(c + G);
-            TCK(2)
             // ---------------- the four score matrices as one product ---------------------------------
             if (wg == 0 && elect_one()) {
                 const uint64_t dA = desc_kmajor(smem_u32(gs + G_WAQ), 2048), dB = desc_kmajor(smem_u32(gs + G_KB), 2048);
@@ -415,14 +503,16 @@ __global__ void __launch_bounds__(32 * (4 * G + 1), G <= 2 ? 2 : 1) wkv7_fwd_tc_
                 tc_commit(&ctrl->score[grp]);
             }
             __syncwarp();
+            TCK(3)
+            TCK(4)
             if (wg < 2) {
                 mbar_wait<true>(&ctrl->score[grp], k & 1, ctrl, p.status);
                 tc_fence_after();
-                TCK(3)
                 uint32_t sv[32];
                 tmem_ld16(tlane + C_SCORE + 32 * grp, sv);
                 tmem_ld16(tlane + C_SCORE + 32 * grp + 16, sv + 16);
                 tmem_ld_wait();
+                TCK(5)
                 const int t = lane;
                 if (wg == 0) {
                     // lane t: row t of AK (strictly lower) and of AB (strictly lower, kept transposed for the inverse)
@@ -430,12 +520,12 @@ __global__ void __launch_bounds__(32 * (4 * G + 1), G <= 2 ? 2 : 1) wkv7_fwd_tc_
                         float* ABt = reinterpret_cast<float*>(gs + G_ABT);
 #pragma unroll
                         for (int qd = 0; qd < 4; ++qd) {
-                            float4 o;
-                            o.x = (4 * qd + 0 < t) ? rnd(__uint_as_float(sv[4 * qd + 0])) : 0.f;
-                            o.y = (4 * qd + 1 < t) ? rnd(__uint_as_float(sv[4 * qd + 1])) : 0.f;
-                            o.z = (4 * qd + 2 < t) ? rnd(__uint_as_float(sv[4 * qd + 2])) : 0.f;
-                            o.w = (4 * qd + 3 < t) ? rnd(__uint_as_float(sv[4 * qd + 3])) : 0.f;
-                            *reinterpret_cast<float4*>(gs + G_SC + kchunk(t, qd, 512)) = o;
+                            float4 x;
+                            x.x = (4 * qd + 0 < t) ? rnd(__uint_as_float(sv[4 * qd + 0])) : 0.f;
+                            x.y = (4 * qd + 1 < t) ? rnd(__uint_as_float(sv[4 * qd + 1])) : 0.f;
+                            x.z = (4 * qd + 2 < t) ? rnd(__uint_as_float(sv[4 * qd + 2])) : 0.f;
+                            x.w = (4 * qd + 3 < t) ? rnd(__uint_as_float(sv[4 * qd + 3])) : 0.f;
+                            *reinterpret_cast<float4*>(gs + G_SC + kchunk(t, qd, 512)) = x;
                         }
 #pragma unroll
                         for (int s = 0; s < 16; ++s) ABt[s * SCS + t] = (s < t) ? __uint_as_float(sv[16 + s]) : 0.f;
@@ -446,77 +536,39 @@ __global__ void __launch_bounds__(32 * (4 * G + 1), G <= 2 ? 2 : 1) wkv7_fwd_tc_
                     // lane t: row t of QK and QB (lower triangular including the diagonal)
 #pragma unroll
                     for (int qd = 0; qd < 4; ++qd) {
-                        float4 o, o2;
-                        o.x = (4 * qd + 0 <= t) ? rnd(__uint_as_float(sv[4 * qd + 0])) : 0.f;
-                        o.y = (4 * qd + 1 <= t) ? rnd(__uint_as_float(sv[4 * qd + 1])) : 0.f;
-                        o.z = (4 * qd + 2 <= t) ? rnd(__uint_as_float(sv[4 * qd + 2])) : 0.f;
-                        o.w = (4 * qd + 3 <= t) ? rnd(__uint_as_float(sv[4 * qd + 3])) : 0.f;
-                        o2.x = (4 * qd + 0 <= t) ? rnd(__uint_as_float(sv[16 + 4 * qd + 0])) : 0.f;
-                        o2.y = (4 * qd + 1 <= t) ? rnd(__uint_as_float(sv[16 + 4 * qd + 1])) : 0.f;
-                        o2.z = (4 * qd + 2 <= t) ? rnd(__uint_as_float(sv[16 + 4 * qd + 2])) : 0.f;
-                        o2.w = (4 * qd + 3 <= t) ? rnd(__uint_as_float(sv[16 + 4 * qd + 3])) : 0.f;
-                        *reinterpret_cast<float4*>(gs + G_SC + kchunk(16 + t, qd, 512)) = o;
-                        *reinterpret_cast<float4*>(gs + G_QB + kchunk(t, qd, 512)) = o2;
+                        float4 x, x2;
+                        x.x = (4 * qd + 0 <= t) ? rnd(__uint_as_float(sv[4 * qd + 0])) : 0.f;
+                        x.y = (4 * qd + 1 <= t) ? rnd(__uint_as_float(sv[4 * qd + 1])) : 0.f;
+                        x.z = (4 * qd + 2 <= t) ? rnd(__uint_as_float(sv[4 * qd + 2])) : 0.f;
+                        x.w = (4 * qd + 3 <= t) ? rnd(__uint_as_float(sv[4 * qd + 3])) : 0.f;
+                        x2.x = (4 * qd + 0 <= t) ? rnd(__uint_as_float(sv[16 + 4 * qd + 0])) : 0.f;
+                        x2.y = (4 * qd + 1 <= t) ? rnd(__uint_as_float(sv[16 + 4 * qd + 1])) : 0.f;
+                        x2.z = (4 * qd + 2 <= t) ? rnd(__uint_as_float(sv[16 + 4 * qd + 2])) : 0.f;
+                        x2.w = (4 * qd + 3 <= t) ? rnd(__uint_as_float(sv[16 + 4 * qd + 3])) : 0.f;
+                        *reinterpret_cast<float4*>(gs + G_SC + kchunk(16 + t, qd, 512)) = x;
+                        *reinterpret_cast<float4*>(gs + G_QB + kchunk(t, qd, 512)) = x2;
                     }
                 }
             }
-            TCK(4)
+            TCK(6)
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(&ctrl->full[grp]);
-            // ---------------- results of this chunk -------------------------------------------------
-            mbar_wait<true>(&ctrl->done[grp], k & 1, ctrl, p.status);
-            tc_fence_after();
-            TCK(5)
-            const bool last = c + 1 == nchunks;
-            float* sdst = last ? (p.sT ? p.sT + bh * N * N : nullptr)
-                               : (p.ckpt ? p.ckpt + (bh * nchunks + c + 1) * (long long)(N * N) : nullptr);
-#ifdef WKV7_TC_NOCKPT
-            sdst = nullptr;
-#endif
-            uint32_t yv[16], sv2[64];
-            tmem_ld16(tlane + C_XY + 16, yv);
-            if (sdst) {
-#pragma unroll
-                for (int cb = 0; cb < 64; cb += 16) tmem_ld16(tlane + C_S + 64 * ((c + 1) & 1) + cb, sv2 + cb);
-            }
-            tmem_ld_wait();
-            tc_fence_before();
-            mbar_arrive(&ctrl->rdone[grp]);
-            TCK(6)
-            // Y^T sits one value row per thread; it goes through shared memory (the [kwi;bwi] tile is dead
-            // once the score product has completed) so that each thread stores 16 contiguous bytes.
-            unsigned char* ys = gs + G_KB;
-            if (lane < 16) {
-                const int i = 16 * wg + lane;
-#pragma unroll
-                for (int t = 0; t < 16; ++t) *reinterpret_cast<IoT*>(ys + t * ROWB + i * 2) = __float2bfloat16_rn(__uint_as_float(yv[t]));
-                if (sdst) {
-                    // 32-byte stores: every lane writes whole sectors of its own 256-byte state row
-                    float* d = sdst + i * N;
-#pragma unroll
-                    for (int q8 = 0; q8 < 8; ++q8)
-                        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(d + 8 * q8), "r"(sv2[8 * q8]), "r"(sv2[8 * q8 + 1]),
-                                     "r"(sv2[8 * q8 + 2]), "r"(sv2[8 * q8 + 3]), "r"(sv2[8 * q8 + 4]), "r"(sv2[8 * q8 + 5]), "r"(sv2[8 * q8 + 6]), "r"(sv2[8 * q8 + 7]) : "memory");
-                }
-            }
-            group_bar(grp);
-            {
-                const int r = gt >> 3, seg = gt & 7;
-                *reinterpret_cast<uint4*>(gy + ((long long)c * L + r) * p.st.t + seg * 8) = *reinterpret_cast<const uint4*>(ys + r * ROWB + seg * 16);
-            }
-            TCK(7)
+            cprev = c;
+        }
+        if (cprev >= 0) {
+            read_results(cprev, k - 1);
         }
 #ifdef WKV7_TIMING
         if (blockIdx.x == 0 && lane == 0 && k > 0)
-            printf("group %d warp %d: load wait %lld | P1 %lld | bar+prefetch %lld | score issue+wait %lld | P2 %lld | wait done %lld | tmem read %lld | stores %lld | P1 fence %lld (cycles per own chunk)\n",
-                   grp, wg,  tacc[0] / k, tacc[1] / k, tacc[2] / k, tacc[3] / k, tacc[4] / k, tacc[5] / k, tacc[6] / k, tacc[7] / k, tacc[8] / k);
+            printf("group %d warp %d: load wait %lld | scan %lld | results %lld | tiles+bar+prefetch+score issue %lld | y store %lld | score wait %lld | P2 %lld (cycles per own chunk)\n",
+                   grp, wg, tacc[0] / k, tacc[1] / k, tacc[2] / k, tacc[3] / k, tacc[4] / k, tacc[5] / k, tacc[6] / k);
 #endif
     }
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 4 * G) {
+    if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(NCOLS) : "memory");
     }
 }
@@ -525,7 +577,7 @@ template <int G, bool RND> static int launch_t(const FwdParams& p, cudaStream_t 
     auto kern = wkv7_fwd_tc_kernel<G, RND>;
     const int smem = G * G_BYTES + (int)sizeof(Ctrl) + 1024;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kLaunchFailed;
-    kern<<<(unsigned)(p.B * p.H), 32 * (4 * G + 1), smem, stream>>>(p);
+    kern<<<(unsigned)(p.B * p.H), 128 * (G + 1), smem, stream>>>(p);
     return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
 
@@ -533,12 +585,12 @@ template <int G, bool RND> static int launch_t(const FwdParams& p, cudaStream_t 
 
 int launch_fwd_tc(const FwdParams& p, int groups, cudaStream_t stream) {
     switch (groups) {
-        case 2: return tc::launch_t<2, false>(p, stream);
-        case 3: return tc::launch_t<3, false>(p, stream);
-        case 4: return tc::launch_t<4, false>(p, stream);
-        case -2: return tc::launch_t<2, true>(p, stream);
-        case -3: return tc::launch_t<3, true>(p, stream);
-        case -4: return tc::launch_t<4, true>(p, stream);
+        case 2: return tc::launch_t<2, true>(p, stream);
+        case 3: return tc::launch_t<3, true>(p, stream);
+        case 4: return tc::launch_t<4, true>(p, stream);
+        case -2: return tc::launch_t<2, false>(p, stream);
+        case -3: return tc::launch_t<3, false>(p, stream);
+        case -4: return tc::launch_t<4, false>(p, stream);
         default: return kBadShape;
     }
 }

@@ -23,6 +23,8 @@ _SIGNATURES = {
     'wkv7_status_string': (ctypes.c_char_p, [_int]),
     'wkv7_checkpoint_bytes': (_i64, [_i64] * 4),
     'wkv7_device_status': (_int, []),
+    'wkv7_set_fwd_impl': (_int, [_int]),
+    'wkv7_get_fwd_impl': (_int, []),
     'wkv7_fwd': (_int, [_vp] * 10 + [_i64] * 7 + [_int, _vp]),
     'wkv7_bwd': (_int, [_vp] * 17 + [_i64] * 7 + [_int, _vp]),
     'wkv7_attn_ln_fwd': (_int, [_vp] * 12 + [_f32] + [_i64] * 7 + [_int, _vp]),
@@ -94,6 +96,14 @@ def strides4(x):
 def device_status():
     """Reads and clears the device status word (synchronises)."""
     return lib().wkv7_device_status()
+
+
+def set_fwd_impl(impl):
+    """Selects the bf16 attn forward kernel: 0 = warp-MMA, 2..4 = tcgen05 with that many preparation
+    groups (negative: operands truncated, not rounded, to TF32).  Returns the previous value."""
+    old = lib().wkv7_get_fwd_impl()
+    check(lib().wkv7_set_fwd_impl(int(impl)), 'wkv7_set_fwd_impl')
+    return old
 
 
 def opaque_op(name, fn, fake, schema_types):
