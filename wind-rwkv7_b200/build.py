@@ -24,6 +24,24 @@ def _deps():
     return [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, '..', 'include', 'wkv7_sm100.h')]
 
 
+def _check_tc_launch_registers(log):
+    """The 4-group tcgen05 forward redistributes registers between its warp groups with setmaxnreg, whose
+    blocking form waits without a bound for registers that must come out of the CTA's launch allocation.
+    The kernel's arithmetic assumes that allocation is 96 registers per thread; stop the build if ptxas
+    chose anything else for those instantiations."""
+    lines = log.splitlines()
+    seen = 0
+    for i, ln in enumerate(lines):
+        if 'Compiling entry function' in ln and 'wkv7_fwd_tc_kernelILi4E' in ln:
+            used = next((l for l in lines[i + 1:i + 6] if 'Used' in l and 'registers' in l), '')
+            seen += 1
+            if 'Used 96 registers' not in used:
+                raise RuntimeError('wkv7_fwd_tc_kernel<4,*> must be launched with 96 registers per thread '
+                                   f'(setmaxnreg arithmetic); ptxas reports: {used.strip()!r}')
+    if seen == 0:
+        raise RuntimeError('ptxas log holds no wkv7_fwd_tc_kernel<4,*> entry: cannot check its register count')
+
+
 def build(force=False, verbose=False):
     newest = max(os.path.getmtime(p) for p in _deps())
     if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= newest:
@@ -41,6 +59,8 @@ def build(force=False, verbose=False):
             raise RuntimeError(f'nvcc failed on {src}:\n{r.stdout}\n{r.stderr}')
         if verbose:
             print(r.stderr)
+        if src == 'wkv7_fwd_tc.cu':
+            _check_tc_launch_registers(r.stdout + r.stderr)
         return obj
 
     with ThreadPoolExecutor(max_workers=8) as ex:

@@ -100,40 +100,51 @@ template <int PREC> __device__ __forceinline__ FragA<PREC> fragA_from_acc(const 
     return f;
 }
 
+// Column swizzle of the operand tiles of the backward kernel.  A tile is read in two ways: along
+// the contraction index (lanes = rows g, 8-byte loads at columns 2t: wants a row stride of 8 or 24
+// mod 32 banks) and across it (lanes = columns g, rows 2t and 2t+1: with such a stride rows 2t and
+// 2t+4 fall on the same banks, a 2-way conflict on every load).  XOR-ing the column with 8 for rows
+// 4..7 of every block of 8 rows moves the second pair of rows to the other banks and leaves the
+// first access pattern conflict-free; 8-float groups stay contiguous.  X = false: plain layout.
+template <bool X> __device__ __forceinline__ int xcol(int row, int col) { return X ? (col ^ ((row & 4) << 1)) : col; }
+
 // A operand from memory laid out [m][k] (row stride ld floats), rows m0+g, m0+g+8, block k0.
-// The loaders' last template argument R says the source was stored through pre<PREC>().
-template <int PREC, bool R = false>
+// The loaders' template argument R says the source was stored through pre<PREC>(), X that the
+// tile carries the column swizzle above.
+template <int PREC, bool R = false, bool X = false>
 __device__ __forceinline__ FragA<PREC> fragA_mk(const float* p, int ld, int m0, int k0, int g, int t) {
     FragA<PREC> f;
-    float2 lo = *reinterpret_cast<const float2*>(p + (m0 + g) * ld + k0 + 2 * t);
-    float2 hi = *reinterpret_cast<const float2*>(p + (m0 + g + 8) * ld + k0 + 2 * t);
+    float2 lo = *reinterpret_cast<const float2*>(p + (m0 + g) * ld + xcol<X>(m0 + g, k0 + 2 * t));
+    float2 hi = *reinterpret_cast<const float2*>(p + (m0 + g + 8) * ld + xcol<X>(m0 + g + 8, k0 + 2 * t));
     f.x[0].template put<R>(lo.x); f.x[1].template put<R>(hi.x); f.x[2].template put<R>(lo.y); f.x[3].template put<R>(hi.y);
     return f;
 }
 
 // A operand from memory laid out [k][m] (the transpose), rows k0+2t, k0+2t+1, columns m0+g, m0+g+8.
-template <int PREC, bool R = false>
+template <int PREC, bool R = false, bool X = false>
 __device__ __forceinline__ FragA<PREC> fragA_km(const float* p, int ld, int m0, int k0, int g, int t) {
     FragA<PREC> f;
-    const float* r0 = p + (k0 + 2 * t) * ld + m0 + g;
-    f.x[0].template put<R>(r0[0]); f.x[1].template put<R>(r0[8]); f.x[2].template put<R>(r0[ld]); f.x[3].template put<R>(r0[ld + 8]);
+    // rows k0+2t and k0+2t+1 lie in the same half of their block of 8, so they share the swizzle
+    const float* r0 = p + (k0 + 2 * t) * ld;
+    const int c0 = xcol<X>(k0 + 2 * t, m0 + g), c1 = xcol<X>(k0 + 2 * t, m0 + g + 8);
+    f.x[0].template put<R>(r0[c0]); f.x[1].template put<R>(r0[c1]); f.x[2].template put<R>(r0[ld + c0]); f.x[3].template put<R>(r0[ld + c1]);
     return f;
 }
 
 // B operand from memory laid out [n][k]: row n0+g, block k0 (one 8-byte load).
-template <int PREC, bool R = false>
+template <int PREC, bool R = false, bool X = false>
 __device__ __forceinline__ FragB<PREC> fragB_nk(const float* p, int ld, int n0, int k0, int g, int t) {
     FragB<PREC> f;
-    float2 v = *reinterpret_cast<const float2*>(p + (n0 + g) * ld + k0 + 2 * t);
+    float2 v = *reinterpret_cast<const float2*>(p + (n0 + g) * ld + xcol<X>(n0 + g, k0 + 2 * t));
     f.x[0].template put<R>(v.x); f.x[1].template put<R>(v.y);
     return f;
 }
 
 // B operand from memory laid out [k][n]: rows k0+2t, k0+2t+1, column n0+g.
-template <int PREC, bool R = false>
+template <int PREC, bool R = false, bool X = false>
 __device__ __forceinline__ FragB<PREC> fragB_kn(const float* p, int ld, int n0, int k0, int g, int t) {
     FragB<PREC> f;
-    const float* r0 = p + (k0 + 2 * t) * ld + n0 + g;
+    const float* r0 = p + (k0 + 2 * t) * ld + xcol<X>(k0 + 2 * t, n0 + g);
     f.x[0].template put<R>(r0[0]); f.x[1].template put<R>(r0[ld]);
     return f;
 }
@@ -195,7 +206,7 @@ __device__ __forceinline__ void store8(float* p, const float (&f)[8]) {
 // bytes wide.  Writes wq = q*P_t, wa = a*P_{t-1}, kwi = k/P_t, bwi = b/P_t (row stride OPS), the
 // chunk decay fw = P_L, and optionally the running log-decay and the per-step log-decay.
 // tq/tw/tk/ta/tb: staging tiles with row stride `rowb` bytes.
-template <typename IoT, int PREC>
+template <typename IoT, int PREC, bool X = false>
 __device__ __forceinline__ void decay_scan(const unsigned char* tq, const unsigned char* tw, const unsigned char* tk,
                                            const unsigned char* ta, const unsigned char* tb, int rowb, float* wq, float* wa,
                                            float* kwi, float* bwi, float* fw, float* cum_out, float* lw_out, int warp, int lane) {
@@ -232,12 +243,13 @@ __device__ __forceinline__ void decay_scan(const unsigned char* tq, const unsign
         o[3][i] = pre<PREC>(b[i] * inv);
         if (row == 15) fw[j0 + i] = incl;
     }
-    store8(wq + row * OPS + j0, o[0]);
-    store8(wa + row * OPS + j0, o[1]);
-    store8(kwi + row * OPS + j0, o[2]);
-    store8(bwi + row * OPS + j0, o[3]);
-    if (cum_out) store8(cum_out + row * OPS + j0, cum);
-    if (lw_out) store8(lw_out + row * OPS + j0, lw);
+    const int at = row * OPS + xcol<X>(row, j0);
+    store8(wq + at, o[0]);
+    store8(wa + at, o[1]);
+    store8(kwi + at, o[2]);
+    store8(bwi + at, o[3]);
+    if (cum_out) store8(cum_out + at, cum);
+    if (lw_out) store8(lw_out + at, lw);
 }
 
 // Column `col` of AI = (I - AB)^-1 for a strictly lower-triangular 16x16 AB, one lane per column.
@@ -252,27 +264,27 @@ template <int S_> __device__ __forceinline__ void tri_fetch_row(float (&dst)[L],
         dst[4 * v] = x.x; dst[4 * v + 1] = x.y; dst[4 * v + 2] = x.z; dst[4 * v + 3] = x.w;
     }
 }
-template <int PREC, int S_>
+template <int PREC, int S_, bool X>
 __device__ __forceinline__ void tri_step(float (&r)[L], const float (&c)[L], float (&cn)[L], const float* ABt, float* AI, int col) {
     if (S_ + 1 < L) tri_fetch_row<(S_ + 1 < L ? S_ + 1 : 0)>(cn, ABt);  // one step ahead of its use
     const float ms = r[S_];
-    AI[S_ * SCS + col] = pre<PREC>(ms);
+    AI[S_ * SCS + xcol<X>(S_, col)] = pre<PREC>(ms);
 #pragma unroll
     for (int tq = S_ + 1; tq < L; ++tq) r[tq] = fmaf(c[tq], ms, r[tq]);
 }
-template <int PREC> __device__ __forceinline__ void tri_inverse_column(const float* ABt, float* AI, int col) {
+template <int PREC, bool X = false> __device__ __forceinline__ void tri_inverse_column(const float* ABt, float* AI, int col) {
     float r[L], ca[L], cb[L];
 #pragma unroll
     for (int tq = 0; tq < L; ++tq) r[tq] = (tq == col) ? 1.f : 0.f;
     tri_fetch_row<0>(ca, ABt);
-    tri_step<PREC, 0>(r, ca, cb, ABt, AI, col);   tri_step<PREC, 1>(r, cb, ca, ABt, AI, col);
-    tri_step<PREC, 2>(r, ca, cb, ABt, AI, col);   tri_step<PREC, 3>(r, cb, ca, ABt, AI, col);
-    tri_step<PREC, 4>(r, ca, cb, ABt, AI, col);   tri_step<PREC, 5>(r, cb, ca, ABt, AI, col);
-    tri_step<PREC, 6>(r, ca, cb, ABt, AI, col);   tri_step<PREC, 7>(r, cb, ca, ABt, AI, col);
-    tri_step<PREC, 8>(r, ca, cb, ABt, AI, col);   tri_step<PREC, 9>(r, cb, ca, ABt, AI, col);
-    tri_step<PREC, 10>(r, ca, cb, ABt, AI, col);  tri_step<PREC, 11>(r, cb, ca, ABt, AI, col);
-    tri_step<PREC, 12>(r, ca, cb, ABt, AI, col);  tri_step<PREC, 13>(r, cb, ca, ABt, AI, col);
-    tri_step<PREC, 14>(r, ca, cb, ABt, AI, col);  tri_step<PREC, 15>(r, cb, ca, ABt, AI, col);
+    tri_step<PREC, 0, X>(r, ca, cb, ABt, AI, col);   tri_step<PREC, 1, X>(r, cb, ca, ABt, AI, col);
+    tri_step<PREC, 2, X>(r, ca, cb, ABt, AI, col);   tri_step<PREC, 3, X>(r, cb, ca, ABt, AI, col);
+    tri_step<PREC, 4, X>(r, ca, cb, ABt, AI, col);   tri_step<PREC, 5, X>(r, cb, ca, ABt, AI, col);
+    tri_step<PREC, 6, X>(r, ca, cb, ABt, AI, col);   tri_step<PREC, 7, X>(r, cb, ca, ABt, AI, col);
+    tri_step<PREC, 8, X>(r, ca, cb, ABt, AI, col);   tri_step<PREC, 9, X>(r, cb, ca, ABt, AI, col);
+    tri_step<PREC, 10, X>(r, ca, cb, ABt, AI, col);  tri_step<PREC, 11, X>(r, cb, ca, ABt, AI, col);
+    tri_step<PREC, 12, X>(r, ca, cb, ABt, AI, col);  tri_step<PREC, 13, X>(r, cb, ca, ABt, AI, col);
+    tri_step<PREC, 14, X>(r, ca, cb, ABt, AI, col);  tri_step<PREC, 15, X>(r, cb, ca, ABt, AI, col);
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
