@@ -37,11 +37,20 @@ namespace wkv7 {
 
 constexpr int SS = N + 8;  // row stride (floats) of the [value][key] state buffers
 // All fp32 tiles of this kernel (operands, scores, score gradients, U, dabu, the two state buffers)
-// carry the column swizzle xcol<true>() of wkv7_common.cuh: each is read both along and across its
+// carry the column swizzle xcol<1>() of wkv7_common.cuh: each is read both along and across its
 // contraction index.  The one exception is AB, which only feeds the triangular inverse.
 
+// Staging tiles [time][channel] in the IO dtype.  bf16: 128-byte rows, the eight 16-byte segments of a
+// row XOR-ed with (row % 8) (cp.async then writes whole aligned 128-byte lines: padded rows cost it
+// 2.5 times the shared-memory wavefronts); fp32: 256-byte rows padded by 16 bytes.
 template <typename IoT> struct BwdLayout {
-    static constexpr int ROWB = N * (int)sizeof(IoT) + 16;
+    static constexpr bool SWZ = sizeof(IoT) == 2;
+    static constexpr int ROWB = N * (int)sizeof(IoT) + (SWZ ? 0 : 16);
+    // byte offset of element (row, col)
+    __device__ static __forceinline__ int at(int row, int col) {
+        const int b = col * (int)sizeof(IoT);
+        return SWZ ? row * ROWB + ((((b >> 4) ^ (row & 7)) << 4) | (b & 15)) : row * ROWB + b;
+    }
     static constexpr int TILEB = L * ROWB;
     static constexpr int YS = (sizeof(IoT) == 2) ? 24 : 20;
 };
@@ -74,15 +83,15 @@ static_assert(sizeof(BwdSmem<__nv_bfloat16, 1, false>) <= 115712, "bf16 backward
 static_assert(sizeof(BwdSmem<__nv_bfloat16, 1, true>) <= 115712, "bf16 attn_ln backward must fit two CTAs per SM");
 
 template <typename IoT> __device__ __forceinline__ float bst_elem(const unsigned char* tile, int row, int col) {
-    return to_f32<IoT>(*reinterpret_cast<const IoT*>(tile + row * BwdLayout<IoT>::ROWB + col * (int)sizeof(IoT)));
+    return to_f32<IoT>(*reinterpret_cast<const IoT*>(tile + BwdLayout<IoT>::at(row, col)));
 }
 // two adjacent elements (col even) of a staging tile
 template <typename IoT> __device__ __forceinline__ float2 bst_pair(const unsigned char* tile, int row, int col);
 template <> __device__ __forceinline__ float2 bst_pair<float>(const unsigned char* tile, int row, int col) {
-    return *reinterpret_cast<const float2*>(tile + row * BwdLayout<float>::ROWB + col * 4);
+    return *reinterpret_cast<const float2*>(tile + BwdLayout<float>::at(row, col));
 }
 template <> __device__ __forceinline__ float2 bst_pair<__nv_bfloat16>(const unsigned char* tile, int row, int col) {
-    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(tile + row * BwdLayout<__nv_bfloat16>::ROWB + col * 2));
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(tile + BwdLayout<__nv_bfloat16>::at(row, col)));
 }
 // A operand [m = time][k = value] straight from a staging tile laid out [time][value]
 template <typename IoT, int PREC>
@@ -172,7 +181,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
     auto issue_in = [&](int c) {
         for (int i = tid; i < 5 * L * CH; i += THREADS) {
             const int ten = i / (L * CH), row = (i / CH) % L, ch = i % CH;
-            cp_async16(sm.st_in[ten] + row * Lay::ROWB + ch * 16,
+            cp_async16(sm.st_in[ten] + Lay::at(row, ch * (16 / (int)sizeof(IoT))),
                        reinterpret_cast<const unsigned char*>(gin[ten] + ((long long)c * L + row) * p.st.t) + ch * 16);
         }
     };
@@ -180,14 +189,14 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
         for (int i = tid; i < (LN ? 3 : 2) * L * CH; i += THREADS) {
             const int ten = i / (L * CH), row = (i / CH) % L, ch = i % CH;
             const IoT* src = (ten == 0 ? gv : ten == 1 ? gdy : gg) + ((long long)c * L + row) * p.st.t;
-            unsigned char* dst = (ten == 0 ? sm.st_v[s] : ten == 1 ? sm.st_dy[s] : sm.st_g[LN ? s : 0]) + row * Lay::ROWB;
-            cp_async16(dst + ch * 16, reinterpret_cast<const unsigned char*>(src) + ch * 16);
+            unsigned char* dst = (ten == 0 ? sm.st_v[s] : ten == 1 ? sm.st_dy[s] : sm.st_g[LN ? s : 0]) + Lay::at(row, ch * (16 / (int)sizeof(IoT)));
+            cp_async16(dst, reinterpret_cast<const unsigned char*>(src) + ch * 16);
         }
     };
     auto issue_s0 = [&](int c) {
         for (int i = tid; i < N * (N / 4); i += THREADS) {
             const int row = i / (N / 4), ch = i % (N / 4);
-            cp_async16(sm.S0s + row * SS + xcol<true>(row, ch * 4), ckpt + (long long)c * N * N + row * N + ch * 4);
+            cp_async16(sm.S0s + row * SS + xcol<1>(row, ch * 4), ckpt + (long long)c * N * N + row * N + ch * 4);
         }
     };
     if (nchunks > 0) {
@@ -226,7 +235,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
         const int vs = it & 1;
         // ---------------- P1: decay scan and scaled operands -------------------------------------
         {
-            decay_scan<IoT, PREC, true>(sm.st_in[0], sm.st_in[1], sm.st_in[2], sm.st_in[3], sm.st_in[4], Lay::ROWB, sm.wq, sm.wa,
+            decay_scan<IoT, PREC, 1, Lay::SWZ>(sm.st_in[0], sm.st_in[1], sm.st_in[2], sm.st_in[3], sm.st_in[4], Lay::ROWB, sm.wq, sm.wa,
                                   sm.kwi, sm.bwi, sm.fw, sm.cum, PREC == 3 ? sm.lw : nullptr, warp, lane);
             if (LN) {  // bonus dot  sum_j r_j k_j bonus_j  per time step: 8 threads per row
                 const int row = tid >> 3, part = tid & 7;
@@ -260,9 +269,9 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             float d[2][4] = {};
 #pragma unroll 2
             for (int kk = 0; kk < 8; ++kk) {
-                FragA<PREC> a = fragA_mk<PREC, true, true>(Am, OPS, 0, 8 * kk, g, t4);
+                FragA<PREC> a = fragA_mk<PREC, true, 1>(Am, OPS, 0, 8 * kk, g, t4);
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) mma<PREC>(d[nt], a, fragB_nk<PREC, true, true>(Bm, OPS, 8 * nt, 8 * kk, g, t4));
+                for (int nt = 0; nt < 2; ++nt) mma<PREC>(d[nt], a, fragB_nk<PREC, true, 1>(Bm, OPS, 8 * nt, 8 * kk, g, t4));
             }
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
@@ -275,14 +284,14 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
                     dst[s * SCS + g] = lo.x; dst[(s + 1) * SCS + g] = lo.y;
                     dst[s * SCS + g + 8] = hi2.x; dst[(s + 1) * SCS + g + 8] = hi2.y;
                 } else {
-                    *reinterpret_cast<float2*>(dst + g * SCS + xcol<true>(g, s)) = lo;
-                    *reinterpret_cast<float2*>(dst + (g + 8) * SCS + xcol<true>(g, s)) = hi2;
+                    *reinterpret_cast<float2*>(dst + g * SCS + xcol<1>(g, s)) = lo;
+                    *reinterpret_cast<float2*>(dst + (g + 8) * SCS + xcol<1>(g, s)) = hi2;
                 }
             }
         }
         if (warp == 3) {  // AI = (I - AB)^-1
             __syncwarp();
-            if (lane < L) tri_inverse_column<PREC, true>(sm.sgrad, sm.AI, lane);
+            if (lane < L) tri_inverse_column<PREC, 1>(sm.sgrad, sm.AI, lane);
         }
 
         TICK(2)
@@ -304,32 +313,32 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             float X[2][4] = {}, Y[2][4] = {};
 #pragma unroll 2
             for (int kk = 0; kk < 8; ++kk) {
-                FragA<PREC> a = fragA_mk<PREC, false, true>(sm.S0s, SS, 16 * warp, 8 * kk, g, t4);
+                FragA<PREC> a = fragA_mk<PREC, false, 1>(sm.S0s, SS, 16 * warp, 8 * kk, g, t4);
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
-                    mma<PREC>(X[nt], a, fragB_nk<PREC, true, true>(sm.wa, OPS, 8 * nt, 8 * kk, g, t4));
-                    if (LN) mma<PREC>(Y[nt], a, fragB_nk<PREC, true, true>(sm.wq, OPS, 8 * nt, 8 * kk, g, t4));
+                    mma<PREC>(X[nt], a, fragB_nk<PREC, true, 1>(sm.wa, OPS, 8 * nt, 8 * kk, g, t4));
+                    if (LN) mma<PREC>(Y[nt], a, fragB_nk<PREC, true, 1>(sm.wq, OPS, 8 * nt, 8 * kk, g, t4));
                 }
             }
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                 for (int kk = 0; kk <= nt; ++kk) {
-                    mma<PREC>(X[nt], vf[kk], fragB_nk<PREC, true, true>(sm.AK, SCS, 8 * nt, 8 * kk, g, t4));
-                    if (LN) mma<PREC>(Y[nt], vf[kk], fragB_nk<PREC, true, true>(sm.QK, SCS, 8 * nt, 8 * kk, g, t4));
+                    mma<PREC>(X[nt], vf[kk], fragB_nk<PREC, true, 1>(sm.AK, SCS, 8 * nt, 8 * kk, g, t4));
+                    if (LN) mma<PREC>(Y[nt], vf[kk], fragB_nk<PREC, true, 1>(sm.QK, SCS, 8 * nt, 8 * kk, g, t4));
                 }
             FragA<PREC> xa[2] = {fragA_from_acc<PREC>(X[0]), fragA_from_acc<PREC>(X[1])};
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                for (int kk = 0; kk <= nt; ++kk) mma<PREC>(U[nt], xa[kk], fragB_nk<PREC, true, true>(sm.AI, SCS, 8 * nt, 8 * kk, g, t4));
+                for (int kk = 0; kk <= nt; ++kk) mma<PREC>(U[nt], xa[kk], fragB_nk<PREC, true, 1>(sm.AI, SCS, 8 * nt, 8 * kk, g, t4));
             if (LN) {
                 // ---- rebuild Y, then GroupNorm / bonus / gate backward in the [value][time] layout ----
                 FragA<PREC> ua0[2] = {fragA_from_acc<PREC>(U[0]), fragA_from_acc<PREC>(U[1])};
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                    for (int kk = 0; kk <= nt; ++kk) mma<PREC>(Y[nt], ua0[kk], fragB_nk<PREC, true, true>(sm.QB, SCS, 8 * nt, 8 * kk, g, t4));
+                    for (int kk = 0; kk <= nt; ++kk) mma<PREC>(Y[nt], ua0[kk], fragB_nk<PREC, true, 1>(sm.QB, SCS, 8 * nt, 8 * kk, g, t4));
                 // statistics: per-warp mean and centred sum of squares over 16 rows, merged below
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt)
@@ -440,7 +449,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
                 for (int nt = 0; nt < 2; ++nt) {
                     dyf[nt] = fragA_from_acc<PREC>(Y[nt]);
                     const int tq = 8 * nt + 2 * t4, vc = 16 * warp + g;
-                    const int c0 = xcol<true>(tq, vc), c1 = xcol<true>(tq, vc + 8);  // rows tq, tq+1 share the swizzle
+                    const int c0 = xcol<1>(tq, vc), c1 = xcol<1>(tq, vc + 8);  // rows tq, tq+1 share the swizzle
                     sm.Yt[tq * OPS + c0] = pre<PREC>(Y[nt][0]); sm.Yt[(tq + 1) * OPS + c0] = pre<PREC>(Y[nt][1]);
                     sm.Yt[tq * OPS + c1] = pre<PREC>(Y[nt][2]); sm.Yt[(tq + 1) * OPS + c1] = pre<PREC>(Y[nt][3]);
                 }
@@ -457,16 +466,16 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
         for (int sb = 0; sb < 2; ++sb)
 #pragma unroll
             for (int tb = sb; tb < 2; ++tb) {
-                mma<PREC>(du[sb], dyf[tb], fragB_kn<PREC, true, true>(sm.QB, SCS, 8 * sb, 8 * tb, g, t4));
-                mma<PREC>(dV[sb], dyf[tb], fragB_kn<PREC, true, true>(sm.QK, SCS, 8 * sb, 8 * tb, g, t4));
+                mma<PREC>(du[sb], dyf[tb], fragB_kn<PREC, true, 1>(sm.QB, SCS, 8 * sb, 8 * tb, g, t4));
+                mma<PREC>(dV[sb], dyf[tb], fragB_kn<PREC, true, 1>(sm.QK, SCS, 8 * sb, 8 * tb, g, t4));
             }
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
             FragA<PREC> a = fragA_from_acc<PREC>(dS[kk]);
 #pragma unroll
             for (int sb = 0; sb < 2; ++sb) {
-                mma<PREC>(du[sb], a, fragB_nk<PREC, true, true>(sm.bwi, OPS, 8 * sb, 8 * kk, g, t4));
-                mma<PREC>(dV[sb], a, fragB_nk<PREC, true, true>(sm.kwi, OPS, 8 * sb, 8 * kk, g, t4));
+                mma<PREC>(du[sb], a, fragB_nk<PREC, true, 1>(sm.bwi, OPS, 8 * sb, 8 * kk, g, t4));
+                mma<PREC>(dV[sb], a, fragB_nk<PREC, true, 1>(sm.kwi, OPS, 8 * sb, 8 * kk, g, t4));
             }
         }
         float dabu[2][4] = {};
@@ -475,13 +484,13 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
 #pragma unroll
             for (int nb = 0; nb < 2; ++nb)
 #pragma unroll
-                for (int kb = nb; kb < 2; ++kb) mma<PREC>(dabu[nb], da2[kb], fragB_kn<PREC, true, true>(sm.AI, SCS, 8 * nb, 8 * kb, g, t4));
+                for (int kb = nb; kb < 2; ++kb) mma<PREC>(dabu[nb], da2[kb], fragB_kn<PREC, true, 1>(sm.AI, SCS, 8 * nb, 8 * kb, g, t4));
         }
         FragA<PREC> dbf[2] = {fragA_from_acc<PREC>(dabu[0]), fragA_from_acc<PREC>(dabu[1])};
 #pragma unroll
         for (int sb = 0; sb < 2; ++sb)
 #pragma unroll
-            for (int tb = sb; tb < 2; ++tb) mma<PREC>(dV[sb], dbf[tb], fragB_kn<PREC, true, true>(sm.AK, SCS, 8 * sb, 8 * tb, g, t4));
+            for (int tb = sb; tb < 2; ++tb) mma<PREC>(dV[sb], dbf[tb], fragB_kn<PREC, true, 1>(sm.AK, SCS, 8 * sb, 8 * tb, g, t4));
 
         // dv out (transposed through a per-warp scratch tile for 16-byte stores)
         {
@@ -504,13 +513,13 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
         // dSf, U, dabu to shared memory for stage C
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
-            *reinterpret_cast<float2*>(sm.dSs + (16 * warp + g) * SS + xcol<true>(g, 8 * nt + 2 * t4)) = make_float2(pre<PREC>(dS[nt][0]), pre<PREC>(dS[nt][1]));
-            *reinterpret_cast<float2*>(sm.dSs + (16 * warp + g + 8) * SS + xcol<true>(g, 8 * nt + 2 * t4)) = make_float2(pre<PREC>(dS[nt][2]), pre<PREC>(dS[nt][3]));
+            *reinterpret_cast<float2*>(sm.dSs + (16 * warp + g) * SS + xcol<1>(g, 8 * nt + 2 * t4)) = make_float2(pre<PREC>(dS[nt][0]), pre<PREC>(dS[nt][1]));
+            *reinterpret_cast<float2*>(sm.dSs + (16 * warp + g + 8) * SS + xcol<1>(g, 8 * nt + 2 * t4)) = make_float2(pre<PREC>(dS[nt][2]), pre<PREC>(dS[nt][3]));
         }
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
             const int tq = 8 * nt + 2 * t4, vc = 16 * warp + g;
-            const int c0 = xcol<true>(tq, vc), c1 = xcol<true>(tq, vc + 8);  // rows tq, tq+1 share the swizzle
+            const int c0 = xcol<1>(tq, vc), c1 = xcol<1>(tq, vc + 8);  // rows tq, tq+1 share the swizzle
             sm.Ut[tq * OPS + c0] = pre<PREC>(U[nt][0]); sm.Ut[(tq + 1) * OPS + c0] = pre<PREC>(U[nt][1]);
             sm.Ut[tq * OPS + c1] = pre<PREC>(U[nt][2]); sm.Ut[(tq + 1) * OPS + c1] = pre<PREC>(U[nt][3]);
             sm.Dt[tq * OPS + c0] = pre<PREC>(dabu[nt][0]); sm.Dt[(tq + 1) * OPS + c0] = pre<PREC>(dabu[nt][1]);
@@ -521,11 +530,11 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
         for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
             for (int kk = 0; kk < 2; ++kk) {
-                mma<PREC>(dS[nt], dyf[kk], fragB_kn<PREC, true, true>(sm.wq, OPS, 8 * nt, 8 * kk, g, t4));
-                mma<PREC>(dS[nt], dbf[kk], fragB_kn<PREC, true, true>(sm.wa, OPS, 8 * nt, 8 * kk, g, t4));
+                mma<PREC>(dS[nt], dyf[kk], fragB_kn<PREC, true, 1>(sm.wq, OPS, 8 * nt, 8 * kk, g, t4));
+                mma<PREC>(dS[nt], dbf[kk], fragB_kn<PREC, true, 1>(sm.wa, OPS, 8 * nt, 8 * kk, g, t4));
             }
-            const float2 lo = *reinterpret_cast<const float2*>(sm.S0s + (16 * warp + g) * SS + xcol<true>(g, 8 * nt + 2 * t4));
-            const float2 hi2 = *reinterpret_cast<const float2*>(sm.S0s + (16 * warp + g + 8) * SS + xcol<true>(g, 8 * nt + 2 * t4));
+            const float2 lo = *reinterpret_cast<const float2*>(sm.S0s + (16 * warp + g) * SS + xcol<1>(g, 8 * nt + 2 * t4));
+            const float2 hi2 = *reinterpret_cast<const float2*>(sm.S0s + (16 * warp + g + 8) * SS + xcol<1>(g, 8 * nt + 2 * t4));
             float gx = dS[nt][0] * lo.x + dS[nt][2] * hi2.x, gy2 = dS[nt][1] * lo.y + dS[nt][3] * hi2.y;
 #pragma unroll
             for (int m = 4; m <= 16; m <<= 1) {
@@ -548,17 +557,17 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             float* dst = sm.sgrad + warp * (L * SCS);  // 0 dQK, 1 dAK, 2 dQB, 3 dAB
 #pragma unroll 2
             for (int kk = 0; kk < 8; ++kk) {
-                FragA<PREC> aD = fragA_mk<PREC, true, true>(sm.Dt, OPS, 0, 8 * kk, g, t4);
-                FragA<PREC> aY = LN ? fragA_mk<PREC, true, true>(sm.Yt, OPS, 0, 8 * kk, g, t4) : fragA_mk_st<IoT, PREC>(dyt, 8 * kk, g, t4);
-                FragA<PREC> aU = fragA_mk<PREC, true, true>(sm.Ut, OPS, 0, 8 * kk, g, t4);
+                FragA<PREC> aD = fragA_mk<PREC, true, 1>(sm.Dt, OPS, 0, 8 * kk, g, t4);
+                FragA<PREC> aY = LN ? fragA_mk<PREC, true, 1>(sm.Yt, OPS, 0, 8 * kk, g, t4) : fragA_mk_st<IoT, PREC>(dyt, 8 * kk, g, t4);
+                FragA<PREC> aU = fragA_mk<PREC, true, 1>(sm.Ut, OPS, 0, 8 * kk, g, t4);
                 FragA<PREC> aV = fragA_mk_st<IoT, PREC>(vt, 8 * kk, g, t4);
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
-                    FragB<PREC> bsc = (warp >> 1) ? fragB_nk<PREC, true, true>(sm.Ut, OPS, 8 * nt, 8 * kk, g, t4)
+                    FragB<PREC> bsc = (warp >> 1) ? fragB_nk<PREC, true, 1>(sm.Ut, OPS, 8 * nt, 8 * kk, g, t4)
                                                   : fragB_nk_st<IoT, PREC>(vt, 8 * nt, 8 * kk, g, t4);
                     mma<PREC>(d[nt], strict ? aD : aY, bsc);
-                    FragB<PREC> bS = fragB_kn<PREC, false, true>(sm.S0s, SS, 16 * warp + 8 * nt, 8 * kk, g, t4);
-                    FragB<PREC> bD = fragB_kn<PREC, true, true>(sm.dSs, SS, 16 * warp + 8 * nt, 8 * kk, g, t4);
+                    FragB<PREC> bS = fragB_kn<PREC, false, 1>(sm.S0s, SS, 16 * warp + 8 * nt, 8 * kk, g, t4);
+                    FragB<PREC> bD = fragB_kn<PREC, true, 1>(sm.dSs, SS, 16 * warp + 8 * nt, 8 * kk, g, t4);
                     mma<PREC>(DA[nt], aD, bS);
                     mma<PREC>(DQ[nt], aY, bS);
                     mma<PREC>(DB[nt], aU, bD);
@@ -569,9 +578,9 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             for (int nt = 0; nt < 2; ++nt) {
                 const int s = 8 * nt + 2 * t4;
                 auto keep = [&](int tq, int ss) { return strict ? ss < tq : ss <= tq; };
-                *reinterpret_cast<float2*>(dst + g * SCS + xcol<true>(g, s)) =
+                *reinterpret_cast<float2*>(dst + g * SCS + xcol<1>(g, s)) =
                     make_float2(keep(g, s) ? pre<PREC>(d[nt][0]) : 0.f, keep(g, s + 1) ? pre<PREC>(d[nt][1]) : 0.f);
-                *reinterpret_cast<float2*>(dst + (g + 8) * SCS + xcol<true>(g, s)) =
+                *reinterpret_cast<float2*>(dst + (g + 8) * SCS + xcol<1>(g, s)) =
                     make_float2(keep(g + 8, s) ? pre<PREC>(d[nt][2]) : 0.f, keep(g + 8, s + 1) ? pre<PREC>(d[nt][3]) : 0.f);
             }
         }
@@ -584,15 +593,15 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk) {
             const float *dQK = sm.sgrad, *dAK = sm.sgrad + L * SCS, *dQB = sm.sgrad + 2 * L * SCS, *dAB = sm.sgrad + 3 * L * SCS;
-            FragA<PREC> aAB = fragA_mk<PREC, true, true>(dAB, SCS, 0, 8 * kk, g, t4), aAK = fragA_mk<PREC, true, true>(dAK, SCS, 0, 8 * kk, g, t4);
-            FragA<PREC> aQB = fragA_mk<PREC, true, true>(dQB, SCS, 0, 8 * kk, g, t4), aQK = fragA_mk<PREC, true, true>(dQK, SCS, 0, 8 * kk, g, t4);
-            FragA<PREC> tAB = fragA_km<PREC, true, true>(dAB, SCS, 0, 8 * kk, g, t4), tAK = fragA_km<PREC, true, true>(dAK, SCS, 0, 8 * kk, g, t4);
-            FragA<PREC> tQB = fragA_km<PREC, true, true>(dQB, SCS, 0, 8 * kk, g, t4), tQK = fragA_km<PREC, true, true>(dQK, SCS, 0, 8 * kk, g, t4);
+            FragA<PREC> aAB = fragA_mk<PREC, true, 1>(dAB, SCS, 0, 8 * kk, g, t4), aAK = fragA_mk<PREC, true, 1>(dAK, SCS, 0, 8 * kk, g, t4);
+            FragA<PREC> aQB = fragA_mk<PREC, true, 1>(dQB, SCS, 0, 8 * kk, g, t4), aQK = fragA_mk<PREC, true, 1>(dQK, SCS, 0, 8 * kk, g, t4);
+            FragA<PREC> tAB = fragA_km<PREC, true, 1>(dAB, SCS, 0, 8 * kk, g, t4), tAK = fragA_km<PREC, true, 1>(dAK, SCS, 0, 8 * kk, g, t4);
+            FragA<PREC> tQB = fragA_km<PREC, true, 1>(dQB, SCS, 0, 8 * kk, g, t4), tQK = fragA_km<PREC, true, 1>(dQK, SCS, 0, 8 * kk, g, t4);
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 const int n0 = 16 * warp + 8 * nt;
-                FragB<PREC> bb = fragB_kn<PREC, true, true>(sm.bwi, OPS, n0, 8 * kk, g, t4), bk = fragB_kn<PREC, true, true>(sm.kwi, OPS, n0, 8 * kk, g, t4);
-                FragB<PREC> ba = fragB_kn<PREC, true, true>(sm.wa, OPS, n0, 8 * kk, g, t4), bq = fragB_kn<PREC, true, true>(sm.wq, OPS, n0, 8 * kk, g, t4);
+                FragB<PREC> bb = fragB_kn<PREC, true, 1>(sm.bwi, OPS, n0, 8 * kk, g, t4), bk = fragB_kn<PREC, true, 1>(sm.kwi, OPS, n0, 8 * kk, g, t4);
+                FragB<PREC> ba = fragB_kn<PREC, true, 1>(sm.wa, OPS, n0, 8 * kk, g, t4), bq = fragB_kn<PREC, true, 1>(sm.wq, OPS, n0, 8 * kk, g, t4);
                 mma<PREC>(DA[nt], aAB, bb); mma<PREC>(DA[nt], aAK, bk);
                 mma<PREC>(DQ[nt], aQB, bb); mma<PREC>(DQ[nt], aQK, bk);
                 mma<PREC>(DB[nt], tAB, ba); mma<PREC>(DB[nt], tQB, bq);
@@ -610,13 +619,13 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
 #pragma unroll
             for (int hrow = 0; hrow < 2; ++hrow) {
                 const int tq = g + 8 * hrow;
-                const int kx = xcol<true>(tq, key);
+                const int kx = xcol<1>(tq, key);
                 const float2 cu = *reinterpret_cast<const float2*>(sm.cum + tq * OPS + kx);
                 float2 lwp;
                 if (PREC == 3) {
                     lwp = *reinterpret_cast<const float2*>(sm.lw + tq * OPS + kx);
                 } else {  // running log-decay difference; row -1 is zero
-                    const float2 cp = tq > 0 ? *reinterpret_cast<const float2*>(sm.cum + (tq - 1) * OPS + xcol<true>(tq - 1, key)) : make_float2(0.f, 0.f);
+                    const float2 cp = tq > 0 ? *reinterpret_cast<const float2*>(sm.cum + (tq - 1) * OPS + xcol<1>(tq - 1, key)) : make_float2(0.f, 0.f);
                     lwp = make_float2(cu.x - cp.x, cu.y - cp.y);
                 }
                 const float2 oq = *reinterpret_cast<const float2*>(sm.wq + tq * OPS + kx);

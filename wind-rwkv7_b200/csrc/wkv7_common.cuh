@@ -100,18 +100,26 @@ template <int PREC> __device__ __forceinline__ FragA<PREC> fragA_from_acc(const 
     return f;
 }
 
-// Column swizzle of the operand tiles of the backward kernel.  A tile is read in two ways: along
-// the contraction index (lanes = rows g, 8-byte loads at columns 2t: wants a row stride of 8 or 24
-// mod 32 banks) and across it (lanes = columns g, rows 2t and 2t+1: with such a stride rows 2t and
-// 2t+4 fall on the same banks, a 2-way conflict on every load).  XOR-ing the column with 8 for rows
-// 4..7 of every block of 8 rows moves the second pair of rows to the other banks and leaves the
-// first access pattern conflict-free; 8-float groups stay contiguous.  X = false: plain layout.
-template <bool X> __device__ __forceinline__ int xcol(int row, int col) { return X ? (col ^ ((row & 4) << 1)) : col; }
+// Column swizzles of the fp32 tiles of the backward kernel.  A tile is read in two ways: along the
+// contraction index (lanes = rows g, 8-byte loads at columns 2t) and across it (lanes = columns g,
+// rows 2t and 2t+1).
+// X = 1, for row strides of 8 or 24 mod 32 words (the padded operand and score tiles): the first
+//   pattern is conflict-free by the padding, in the second rows 2t and 2t+4 fall on the same banks;
+//   XOR-ing the column with 8 for rows 4..7 of every block of 8 rows separates them.
+// X = 2, for unpadded 64-float rows: the column is XOR-ed with 8 * ((row ^ (row >> 2)) & 3), which gives
+//   rows g = 0..3, rows g = 4..7, rows 0,2,4,6 and rows 1,3,5,7 four different values each, so both
+//   patterns are conflict-free.  (Tried on the backward's state buffers, which cp.async fills and which
+//   it fills with fewer wavefronts when rows are 128-byte aligned; the extra address arithmetic in the
+//   inner loops cost more than that saved, so they stay padded with X = 1.)
+// Groups of 8 floats stay contiguous under both.  X = 0: plain layout.
+template <int X> __device__ __forceinline__ int xcol(int row, int col) {
+    return X == 1 ? (col ^ ((row & 4) << 1)) : X == 2 ? (col ^ (((row ^ (row >> 2)) & 3) << 3)) : col;
+}
 
 // A operand from memory laid out [m][k] (row stride ld floats), rows m0+g, m0+g+8, block k0.
 // The loaders' template argument R says the source was stored through pre<PREC>(), X that the
 // tile carries the column swizzle above.
-template <int PREC, bool R = false, bool X = false>
+template <int PREC, bool R = false, int X = 0>
 __device__ __forceinline__ FragA<PREC> fragA_mk(const float* p, int ld, int m0, int k0, int g, int t) {
     FragA<PREC> f;
     float2 lo = *reinterpret_cast<const float2*>(p + (m0 + g) * ld + xcol<X>(m0 + g, k0 + 2 * t));
@@ -121,18 +129,18 @@ __device__ __forceinline__ FragA<PREC> fragA_mk(const float* p, int ld, int m0, 
 }
 
 // A operand from memory laid out [k][m] (the transpose), rows k0+2t, k0+2t+1, columns m0+g, m0+g+8.
-template <int PREC, bool R = false, bool X = false>
+template <int PREC, bool R = false, int X = 0>
 __device__ __forceinline__ FragA<PREC> fragA_km(const float* p, int ld, int m0, int k0, int g, int t) {
     FragA<PREC> f;
-    // rows k0+2t and k0+2t+1 lie in the same half of their block of 8, so they share the swizzle
-    const float* r0 = p + (k0 + 2 * t) * ld;
-    const int c0 = xcol<X>(k0 + 2 * t, m0 + g), c1 = xcol<X>(k0 + 2 * t, m0 + g + 8);
-    f.x[0].template put<R>(r0[c0]); f.x[1].template put<R>(r0[c1]); f.x[2].template put<R>(r0[ld + c0]); f.x[3].template put<R>(r0[ld + c1]);
+    const int k = k0 + 2 * t;
+    const float *r0 = p + k * ld, *r1 = r0 + ld;
+    f.x[0].template put<R>(r0[xcol<X>(k, m0 + g)]); f.x[1].template put<R>(r0[xcol<X>(k, m0 + g + 8)]);
+    f.x[2].template put<R>(r1[xcol<X>(k + 1, m0 + g)]); f.x[3].template put<R>(r1[xcol<X>(k + 1, m0 + g + 8)]);
     return f;
 }
 
 // B operand from memory laid out [n][k]: row n0+g, block k0 (one 8-byte load).
-template <int PREC, bool R = false, bool X = false>
+template <int PREC, bool R = false, int X = 0>
 __device__ __forceinline__ FragB<PREC> fragB_nk(const float* p, int ld, int n0, int k0, int g, int t) {
     FragB<PREC> f;
     float2 v = *reinterpret_cast<const float2*>(p + (n0 + g) * ld + xcol<X>(n0 + g, k0 + 2 * t));
@@ -141,11 +149,11 @@ __device__ __forceinline__ FragB<PREC> fragB_nk(const float* p, int ld, int n0, 
 }
 
 // B operand from memory laid out [k][n]: rows k0+2t, k0+2t+1, column n0+g.
-template <int PREC, bool R = false, bool X = false>
+template <int PREC, bool R = false, int X = 0>
 __device__ __forceinline__ FragB<PREC> fragB_kn(const float* p, int ld, int n0, int k0, int g, int t) {
     FragB<PREC> f;
-    const float* r0 = p + (k0 + 2 * t) * ld + xcol<X>(k0 + 2 * t, n0 + g);
-    f.x[0].template put<R>(r0[0]); f.x[1].template put<R>(r0[ld]);
+    const int k = k0 + 2 * t;
+    f.x[0].template put<R>(p[k * ld + xcol<X>(k, n0 + g)]); f.x[1].template put<R>(p[(k + 1) * ld + xcol<X>(k + 1, n0 + g)]);
     return f;
 }
 
@@ -206,12 +214,14 @@ __device__ __forceinline__ void store8(float* p, const float (&f)[8]) {
 // bytes wide.  Writes wq = q*P_t, wa = a*P_{t-1}, kwi = k/P_t, bwi = b/P_t (row stride OPS), the
 // chunk decay fw = P_L, and optionally the running log-decay and the per-step log-decay.
 // tq/tw/tk/ta/tb: staging tiles with row stride `rowb` bytes.
-template <typename IoT, int PREC, bool X = false>
+// RAWX: the staging tiles have unpadded 128-byte rows (bf16) whose eight 16-byte segments are XOR-ed
+// with (row % 8), so that cp.async writes whole aligned lines and these 16-byte reads stay conflict-free.
+template <typename IoT, int PREC, int X = 0, bool RAWX = false>
 __device__ __forceinline__ void decay_scan(const unsigned char* tq, const unsigned char* tw, const unsigned char* tk,
                                            const unsigned char* ta, const unsigned char* tb, int rowb, float* wq, float* wa,
                                            float* kwi, float* bwi, float* fw, float* cum_out, float* lw_out, int warp, int lane) {
     const int row = lane & 15, j0 = 16 * warp + 8 * (lane >> 4);
-    const int off = row * rowb + j0 * (int)sizeof(IoT);
+    const int off = RAWX ? row * rowb + ((((j0 * (int)sizeof(IoT)) >> 4) ^ (row & 7)) << 4) : row * rowb + j0 * (int)sizeof(IoT);
     float lw[8], cum[8], q[8], k[8], a[8], b[8];
     load8<IoT>(tw + off, lw);
     load8<IoT>(tq + off, q);
@@ -264,7 +274,7 @@ template <int S_> __device__ __forceinline__ void tri_fetch_row(float (&dst)[L],
         dst[4 * v] = x.x; dst[4 * v + 1] = x.y; dst[4 * v + 2] = x.z; dst[4 * v + 3] = x.w;
     }
 }
-template <int PREC, int S_, bool X>
+template <int PREC, int S_, int X>
 __device__ __forceinline__ void tri_step(float (&r)[L], const float (&c)[L], float (&cn)[L], const float* ABt, float* AI, int col) {
     if (S_ + 1 < L) tri_fetch_row<(S_ + 1 < L ? S_ + 1 : 0)>(cn, ABt);  // one step ahead of its use
     const float ms = r[S_];
@@ -272,7 +282,7 @@ __device__ __forceinline__ void tri_step(float (&r)[L], const float (&c)[L], flo
 #pragma unroll
     for (int tq = S_ + 1; tq < L; ++tq) r[tq] = fmaf(c[tq], ms, r[tq]);
 }
-template <int PREC, bool X = false> __device__ __forceinline__ void tri_inverse_column(const float* ABt, float* AI, int col) {
+template <int PREC, int X = 0> __device__ __forceinline__ void tri_inverse_column(const float* ABt, float* AI, int col) {
     float r[L], ca[L], cb[L];
 #pragma unroll
     for (int tq = 0; tq < L; ++tq) r[tq] = (tq == col) ? 1.f : 0.f;
