@@ -639,7 +639,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
                 for (int e = 0; e < 2; ++e) {
                     const int i = e + 2 * hrow;
                     const float incl = exp_p<PREC>(fmaxf(cuv[e], -80.f));
-                    const float inv = PREC == 3 ? 1.f / incl : rcp_newton(incl);
+                    const float inv = rcp_p<PREC>(incl);
                     // P_{t-1} is P_t of the row above, which the lane four below holds (row 7 for
                     // this thread's row 8 sits in lane 28 + t4, first half); row -1 is 1.
                     const float up_same = __shfl_up_sync(0xffffffffu, incl, 4);

@@ -184,8 +184,25 @@ __device__ __forceinline__ float rcp_newton(float x) {
     y = y * fmaf(-x, y, 2.f);
     return y;
 }
-// exp() by precision class: polynomial for the single-TF32 class, libdevice expf for the fp32 class.
-template <int PREC> __device__ __forceinline__ float exp_p(float x) { return PREC == 3 ? expf(x) : exp_poly(x); }
+// The same two functions on the special-function unit (one MUFU instruction each, relative error
+// about 2^-22).  Which version is cheaper depends on what else a kernel puts on the XU pipe: the
+// polynomial versions were introduced when TF32 conversions (cvt.rna, also XU) and four to five
+// MUFU operations per element saturated it; with integer TF32 rounding the pipe is idle in the WKV7
+// kernels (ncu: 0.004 % in the backward) and three MUFU operations per element replace ~45 FMA-pipe
+// and integer instructions.  expand_loras, with seven transcendentals per element, keeps its mix.
+__device__ __forceinline__ float exp_mufu(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(fminf(fmaxf(x, -80.f), 80.f) * 1.4426950408889634f));
+    return y;
+}
+__device__ __forceinline__ float rcp_mufu(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// exp() and 1/x by precision class: MUFU for the single-TF32 class, libdevice for the fp32 class.
+template <int PREC> __device__ __forceinline__ float exp_p(float x) { return PREC == 3 ? expf(x) : exp_mufu(x); }
+template <int PREC> __device__ __forceinline__ float rcp_p(float x) { return PREC == 3 ? 1.f / x : rcp_mufu(x); }
 
 // ---- decay scan (state-independent chunk preparation, shared by forward and backward) ----------
 // 8 consecutive IO elements (16 or 32 bytes) -> floats
@@ -244,7 +261,7 @@ __device__ __forceinline__ void decay_scan(const unsigned char* tq, const unsign
     for (int i = 0; i < 8; ++i) {
         const float cc = fmaxf(cum[i], -80.f);
         const float incl = exp_p<PREC>(cc);
-        const float inv = PREC == 3 ? 1.f / incl : rcp_newton(incl);
+        const float inv = rcp_p<PREC>(incl);
         const float up = __shfl_up_sync(0xffffffffu, incl, 1, 16);
         const float non = row == 0 ? 1.f : up;
         o[0][i] = pre<PREC>(q[i] * incl);
