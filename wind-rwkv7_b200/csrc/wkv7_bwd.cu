@@ -2,7 +2,8 @@
 // walked in reverse; the gradient dS of the state stays in registers across chunks.
 //
 // Replaces the reference's backward_kernel (wind_rwkv/rwkv7/attn.cu:131-326).  The forward
-// intermediates of a chunk are rebuilt from the fp32 chunk-start state S0 the forward wrote.
+// intermediates of a chunk are rebuilt from the fp32 chunk-start state S0 the forward wrote (in the
+// single-TF32 class already rounded to TF32, so that it is loaded as an operand without conversion).
 // With the forward's notation (wq, wa, kwi, bwi, fw, QK, QB, AK, AB, AI = (I-AB)^-1, U) and
 // dSf = dS * fw[None,:]:
 //     du   = QB^T dY + bwi dSf^T          dabu = AI^T du
@@ -313,7 +314,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             float X[2][4] = {}, Y[2][4] = {};
 #pragma unroll 2
             for (int kk = 0; kk < 8; ++kk) {
-                FragA<PREC> a = fragA_mk<PREC, false, 1>(sm.S0s, SS, 16 * warp, 8 * kk, g, t4);
+                FragA<PREC> a = fragA_mk<PREC, true, 1>(sm.S0s, SS, 16 * warp, 8 * kk, g, t4);
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
                     mma<PREC>(X[nt], a, fragB_nk<PREC, true, 1>(sm.wa, OPS, 8 * nt, 8 * kk, g, t4));
@@ -566,7 +567,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
                     FragB<PREC> bsc = (warp >> 1) ? fragB_nk<PREC, true, 1>(sm.Ut, OPS, 8 * nt, 8 * kk, g, t4)
                                                   : fragB_nk_st<IoT, PREC>(vt, 8 * nt, 8 * kk, g, t4);
                     mma<PREC>(d[nt], strict ? aD : aY, bsc);
-                    FragB<PREC> bS = fragB_kn<PREC, false, 1>(sm.S0s, SS, 16 * warp + 8 * nt, 8 * kk, g, t4);
+                    FragB<PREC> bS = fragB_kn<PREC, true, 1>(sm.S0s, SS, 16 * warp + 8 * nt, 8 * kk, g, t4);
                     FragB<PREC> bD = fragB_kn<PREC, true, 1>(sm.dSs, SS, 16 * warp + 8 * nt, 8 * kk, g, t4);
                     mma<PREC>(DA[nt], aD, bS);
                     mma<PREC>(DQ[nt], aY, bS);

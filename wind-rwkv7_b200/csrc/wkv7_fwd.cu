@@ -195,8 +195,10 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
             float* ck = p.ckpt + (bh * nchunks + c) * (long long)(N * N);
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
-                *reinterpret_cast<float2*>(ck + (16 * warp + g) * N + 8 * nt + 2 * t4) = make_float2(S[nt][0], S[nt][1]);
-                *reinterpret_cast<float2*>(ck + (16 * warp + g + 8) * N + 8 * nt + 2 * t4) = make_float2(S[nt][2], S[nt][3]);
+                // in the single-TF32 class the checkpoint is stored already rounded: the backward uses it
+                // only as a tensor-core operand and skips the rounding at every load
+                *reinterpret_cast<float2*>(ck + (16 * warp + g) * N + 8 * nt + 2 * t4) = make_float2(pre<PREC>(S[nt][0]), pre<PREC>(S[nt][1]));
+                *reinterpret_cast<float2*>(ck + (16 * warp + g + 8) * N + 8 * nt + 2 * t4) = make_float2(pre<PREC>(S[nt][2]), pre<PREC>(S[nt][3]));
             }
         }
         float XY[4][4] = {};  // [0..1] X^T (time blocks 0,1), [2..3] Y^T

@@ -276,7 +276,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
             for (int q = 0; q < 4; ++q) {
                 const float4 x = s0 ? *reinterpret_cast<const float4*>(s0 + cb + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
                 v[4 * q] = __float_as_uint(x.x); v[4 * q + 1] = __float_as_uint(x.y); v[4 * q + 2] = __float_as_uint(x.z); v[4 * q + 3] = __float_as_uint(x.w);
-                if (ck) *reinterpret_cast<float4*>(ck + cb + 4 * q) = x;
+                if (ck) *reinterpret_cast<float4*>(ck + cb + 4 * q) = make_float4(rnd(x.x), rnd(x.y), rnd(x.z), rnd(x.w));  // checkpoints are TF32-rounded
             }
             tmem_st16(tmem + ((uint32_t)(32 * warp) << 16) + C_S + cb, v);
         }
@@ -405,6 +405,12 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                     if (qt == 3) {
                         tc_fence_before();
                         mbar_arrive(&ctrl->rdone[grp]);
+                    }
+                    // Checkpoints are stored rounded to TF32 (the backward uses them only as tensor-core operands
+                    // and skips the rounding at every load); the final state is stored exactly.
+                    if (!last) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) sv[i] = tf32_rna(__uint_as_float(sv[i]));
                     }
                     // 32-byte stores: every lane writes whole sectors of its own 256-byte state row
                     if (lane < 16) {
