@@ -64,13 +64,13 @@ int64_t wkv7_checkpoint_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
 int wkv7_device_status(void);
 
 /*
- * Which kernel wkv7_fwd runs for io_dtype WKV7_BF16 (no reference counterpart: the reference has one
+ * Which kernel wkv7_fwd and wkv7_attn_ln_fwd run for io_dtype WKV7_BF16 (no reference counterpart: the reference has one
  * forward kernel per dtype).  0: the warp-MMA kernel (mma.sync TF32, state in registers).  2, 3, 4: the
  * tcgen05 kernel (state in tensor memory) with that many preparation groups per CTA; negative values
  * select the same kernel without the producer-side rounding of operands to TF32 (the tensor core then
  * truncates them: 0.4 % faster, about twice the state error).  The default is 4, or the value of the environment variable WKV7_FWD_TC when the library
- * is loaded.  Returns WKV7_ERR_SHAPE for any other value.  wkv7_attn_ln_fwd and the fp32 dtypes always
- * use the warp-MMA kernel.
+ * is loaded.  Returns WKV7_ERR_SHAPE for any other value.  The fp32 dtypes always use the warp-MMA
+ * kernel.
  */
 int wkv7_set_fwd_impl(int impl);
 int wkv7_get_fwd_impl(void);

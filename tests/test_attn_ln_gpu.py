@@ -10,6 +10,15 @@ from test_attn_gpu import N, NAMES, check, maxabs_rms, rel_l2
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=[4, 0], ids=['tcgen05', 'mma'], autouse=True)
+def fwd_impl(request):
+    """Every test of this file runs with both bf16 forward kernels (the fp32 paths ignore the switch)."""
+    from wind_rwkv.rwkv7 import _lib
+    old = _lib.set_fwd_impl(request.param)
+    yield request.param
+    _lib.set_fwd_impl(old)
+
+
 def run_case(B, T, H, dtype, seed=0, upstream_params=False, s0=False):
     import c_oracle
     from wind_rwkv.rwkv7 import _lib, attn_ln, synthetic

@@ -138,9 +138,9 @@ static int fwd_common(const void* r, const void* w, const void* k, const void* v
     p.eps = eps;
     p.status = status_ptr();
     if (!p.status) return WKV7_ERR_LAUNCH;
-    if (io_dtype == WKV7_BF16 && !ln) {
+    if (io_dtype == WKV7_BF16) {
         const int groups = fwd_impl().load(std::memory_order_relaxed);
-        if (groups) return wkv7::launch_fwd_tc(p, groups, (cudaStream_t)stream);
+        if (groups) return wkv7::launch_fwd_tc(p, groups, ln, (cudaStream_t)stream);
     }
     return wkv7::launch_fwd(p, io_dtype, ln, (cudaStream_t)stream);
 }

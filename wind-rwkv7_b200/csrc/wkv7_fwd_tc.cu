@@ -1,6 +1,7 @@
 // WKV7 forward on the 5th-generation tensor cores (tcgen05, accumulators in tensor memory), bf16 IO.
 //
-// Same mathematics as wkv7_fwd.cu (the reference's forward_kernel, wind_rwkv/rwkv7/attn.cu:11-106),
+// Same mathematics as wkv7_fwd.cu (the reference's forward_kernel, wind_rwkv/rwkv7/attn.cu:11-106, and
+// with LN = true its fused GroupNorm + bonus + gate variant, wind_rwkv/rwkv7/attn_ln.cu:106-212),
 // different machine mapping.  One CTA walks one (batch, head) chain.  The 64x64 state S[value][key]
 // lives in tensor memory for the whole sequence and is never held in registers: per 16-step chunk
 // one elected thread issues 26 tcgen05.mma instructions (M = 64 value rows, TF32 operands, fp32
@@ -67,7 +68,12 @@ constexpr int G_QB = 31744;    // QB       16 x 16, K-major                  102
 constexpr int G_DF = 32768;    // eight 8x8 diagonal blocks of fw, K-major   2048
 constexpr int G_ABT = 34816;   // AB transposed, fp32 [16][SCS]              1536
 constexpr int G_RAW = 36352;   // q, w, k, a, b, v staging                   6 * 2048
-constexpr int G_BYTES = 49152; // 48 KB (36352 + 12288 = 48640, rounded up to 1 KB)
+constexpr int G_GRAW = 48640;  // attn_ln only: the gate tile, double buffered (read one iteration later)  2 * 2048
+constexpr int G_BYTES_PLAIN = 49152;  // 48 KB (48640 rounded up to 1 KB)
+constexpr int G_BYTES_LN = 53248;     // 52 KB
+// attn_ln epilogue scratch inside the [kwi;bwi] tile, which is dead once the score product has completed
+constexpr int LN_YS = 68;                  // row stride (floats) of the fp32 [time][value] staging of Y
+constexpr int LN_PART = L * LN_YS * 4;     // byte offset of the per-warp partial sums [4][16][2] behind it
 
 // tensor-memory columns (32-bit each, 128 lanes; the M = 64 products use lanes 0-15 of each 32-lane quarter)
 constexpr int C_S = 0;      // two 64-column state buffers
@@ -81,6 +87,8 @@ struct Ctrl {
     uint64_t full[4], done[4], rdone[4], score[4], hop;
     uint32_t tmem_base;
     volatile int abort;
+    float lnp[3 * N];          // attn_ln: GroupNorm weight, bias, bonus of this head
+    float bdot[4][2][4][L];    // attn_ln: per-warp partial bonus dots [group][iteration parity][warp][time]
 };
 
 __device__ __forceinline__ uint32_t elect_one() {
@@ -212,15 +220,20 @@ template <bool R> __device__ __forceinline__ void store8mn(unsigned char* p, con
     *reinterpret_cast<float4*>(p + off) = make_float4(x[0], x[1], x[2], x[3]);
     *reinterpret_cast<float4*>(p + (16 - off)) = make_float4(y[0], y[1], y[2], y[3]);
 }
+__device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
 
-template <int G, bool RND>
+template <int G, bool RND, bool LN>
 __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams p) {
     using IoT = __nv_bfloat16;
+    constexpr int G_BYTES = LN ? G_BYTES_LN : G_BYTES_PLAIN;
     constexpr int NCOLS = 512;
     static_assert(C_SCORE + 32 * G <= NCOLS, "tensor memory columns");
     // Register reallocation (G == 4 only).  setmaxnreg.inc blocks, without a bound, until the CTA's
@@ -250,6 +263,9 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
         mbar_init(&ctrl->hop, 1);
         ctrl->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (LN) {
+        for (int i = tid; i < 3 * N; i += blockDim.x) ctrl->lnp[i] = p.params[(long long)(i / N) * p.H * N + hi * N + (i % N)];
     }
     // the off-diagonal zeros of the decay blocks are written once
     for (int i = tid; i < G * (2048 / 16); i += blockDim.x)
@@ -359,12 +375,15 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
         const IoT* gin[6] = {(const IoT*)p.r + base, (const IoT*)p.w + base, (const IoT*)p.k + base,
                              (const IoT*)p.a + base, (const IoT*)p.b + base, (const IoT*)p.v + base};
         IoT* gy = (IoT*)p.y + base;
-        auto issue_raw = [&](int c) {
+        const IoT* gg = LN ? (const IoT*)p.g + base : nullptr;
+        auto issue_raw = [&](int c, int gbuf) {  // gbuf: parity of the iteration that will process chunk c
             const int r = gt >> 3, seg = gt & 7;
             const long long goff = ((long long)c * L + r) * p.st.t;
+            const int at = r * ROWB + ((seg ^ (r & 7)) << 4);
 #pragma unroll
             for (int ten = 0; ten < 6; ++ten)
-                cp_async16(gs + G_RAW + ten * RAW_TILE + r * ROWB + ((seg ^ (r & 7)) << 4), reinterpret_cast<const unsigned char*>(gin[ten] + goff) + seg * 16);
+                cp_async16(gs + G_RAW + ten * RAW_TILE + at, reinterpret_cast<const unsigned char*>(gin[ten] + goff) + seg * 16);
+            if (LN) cp_async16(gs + G_GRAW + gbuf * RAW_TILE + at, reinterpret_cast<const unsigned char*>(gg + goff) + seg * 16);
             cp_async_commit();
         };
         // Results of own chunk number kk (chunk cc): Y^T into registers, the chunk-end state straight to the
@@ -378,7 +397,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
 #ifdef WKV7_TC_NOCKPT
             sdst = nullptr;
 #endif
-            {
+            if (!LN) {
                 // Y^T sits one value row per thread.  Lanes i and i^1 swap half of their 16 time steps, so that
                 // every lane holds (row i&~1, row i|1) pairs for 8 time steps and stores them as bf16x2.
                 uint32_t yv[16];
@@ -394,6 +413,64 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                     const __nv_bfloat162 pr = odd ? __floats2bfloat162_rn(got, mine) : __floats2bfloat162_rn(mine, got);
                     if (lane < 16) *reinterpret_cast<__nv_bfloat162*>(yo + (long long)(2 * m) * p.st.t) = pr;
                 }
+            } else {
+                // attn_ln epilogue (reference: wind_rwkv/rwkv7/attn_ln.cu:176-205): GroupNorm over the head's 64
+                // value channels of each time step, + bonus dot * v, * gate.  Y^T goes to shared memory as
+                // fp32 [time][value]; then one thread = one time step x 8 value channels, the mapping of the scan.
+                float* ysf = reinterpret_cast<float*>(gs + G_KB);
+                float* part = reinterpret_cast<float*>(gs + G_KB + LN_PART);
+                {
+                    uint32_t yv[16];
+                    tmem_ld16(tlane + C_XY + 32 * (cc & 1) + 16, yv);
+                    tmem_ld_wait();
+                    if (lane < 16) {
+#pragma unroll
+                        for (int t = 0; t < 16; ++t) ysf[t * LN_YS + 16 * wg + lane] = __uint_as_float(yv[t]);
+                    }
+                }
+                group_bar(grp);
+                const int t = lane & 15, i0 = 16 * wg + 8 * (lane >> 4);
+                float yv8[8];
+                {
+                    const float4 a4 = *reinterpret_cast<const float4*>(ysf + t * LN_YS + i0), b4 = *reinterpret_cast<const float4*>(ysf + t * LN_YS + i0 + 4);
+                    yv8[0] = a4.x; yv8[1] = a4.y; yv8[2] = a4.z; yv8[3] = a4.w; yv8[4] = b4.x; yv8[5] = b4.y; yv8[6] = b4.z; yv8[7] = b4.w;
+                }
+                // sums about a pivot (the row's first element) keep the one-pass variance well conditioned
+                const float pivot = ysf[t * LN_YS];
+                float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { const float dd = yv8[i] - pivot; s1 += dd; s2 = fmaf(dd, dd, s2); }
+                s1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+                s2 += __shfl_xor_sync(0xffffffffu, s2, 16);
+                if (lane < 16) *reinterpret_cast<float2*>(part + (wg * L + t) * 2) = make_float2(s1, s2);
+                group_bar(grp);
+                {
+                    float a1 = 0.f, a2 = 0.f, bd = 0.f;
+#pragma unroll
+                    for (int w2 = 0; w2 < 4; ++w2) {
+                        const float2 pp = *reinterpret_cast<const float2*>(part + (w2 * L + t) * 2);
+                        a1 += pp.x; a2 += pp.y;
+                        bd += ctrl->bdot[grp][kk & 1][w2][t];
+                    }
+                    const float md = a1 * (1.f / N);
+                    const float mu = pivot + md;
+                    const float rstd = rsqrtf(fmaxf(a2 * (1.f / N) - md * md, 0.f) + p.eps);
+                    // v of this chunk is still in the fp32 MN-major tile, the gate in its own double buffer
+                    const int mo = (i0 >> 5) * 2048 + t * 128 + ((((i0 & 31) >> 3) ^ (t & 3)) << 5);
+                    const float4 v0 = *reinterpret_cast<const float4*>(gs + G_V + mo), v1 = *reinterpret_cast<const float4*>(gs + G_V + mo + 16);
+                    const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                    float gv[8];
+                    load8<IoT>(gs + G_GRAW + (kk & 1) * RAW_TILE + t * ROWB + (((i0 >> 3) ^ (t & 7)) << 4), gv);
+                    float o8[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        o8[i] = ((yv8[i] - mu) * rstd * ctrl->lnp[i0 + i] + ctrl->lnp[N + i0 + i] + bd * vv[i]) * gv[i];
+                    uint4 pk;
+                    pk.x = pack_bf16x2_rn(o8[0], o8[1]); pk.y = pack_bf16x2_rn(o8[2], o8[3]);
+                    pk.z = pack_bf16x2_rn(o8[4], o8[5]); pk.w = pack_bf16x2_rn(o8[6], o8[7]);
+                    *reinterpret_cast<uint4*>(gy + ((long long)cc * L + t) * p.st.t + i0) = pk;
+                }
+                group_bar(grp);  // the scratch lies in an operand tile that is rewritten next
             }
             if (sdst) {
                 float* d = sdst + (16 * wg + (lane & 15)) * N;
@@ -426,7 +503,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
             }
         };
         const int row = lane & 15, j0 = 16 * wg + 8 * (lane >> 4);
-        if (grp < nchunks) issue_raw(grp);
+        if (grp < nchunks) issue_raw(grp, 0);
         int k = 0, cprev = -1;
 #ifdef WKV7_TIMING
         long long tacc[10] = {}, tprev = clock64();
@@ -449,6 +526,13 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                 load8<IoT>(raw + 3 * RAW_TILE, a);
                 load8<IoT>(raw + 4 * RAW_TILE, b);
                 load8<IoT>(raw + 5 * RAW_TILE, v);
+                if (LN) {  // bonus dot sum_j r_j k_j bonus_j of this time step: 8 channels here, the rest by shuffle and in the epilogue
+                    float acc = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc = fmaf(q[i] * kk[i], ctrl->lnp[2 * N + j0 + i], acc);
+                    acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+                    if (lane < 16) ctrl->bdot[grp][k & 1][wg][row] = acc;
+                }
                 // log2 of the per-step decay: -exp(w) * log2(e); running sum along the 16 time rows
 #pragma unroll
                 for (int i = 0; i < 8; ++i) cum[i] = ex2_approx(cum[i] * 1.4426950408889634f) * -1.4426950408889634f;
@@ -500,7 +584,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
             }
             fence_async_smem();
             group_bar(grp);
-            if (c + G < nchunks) issue_raw(c + G);
+            if (c + G < nchunks) issue_raw(c + G, (k + 1) & 1);
             // ---------------- the four score matrices as one product ---------------------------------
             if (wg == 0 && elect_one()) {
                 const uint64_t dA = desc_kmajor(smem_u32(gs + G_WAQ), 2048), dB = desc_kmajor(smem_u32(gs + G_KB), 2048);
@@ -579,9 +663,9 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
     }
 }
 
-template <int G, bool RND> static int launch_t(const FwdParams& p, cudaStream_t stream) {
-    auto kern = wkv7_fwd_tc_kernel<G, RND>;
-    const int smem = G * G_BYTES + (int)sizeof(Ctrl) + 1024;
+template <int G, bool RND, bool LN> static int launch_t(const FwdParams& p, cudaStream_t stream) {
+    auto kern = wkv7_fwd_tc_kernel<G, RND, LN>;
+    const int smem = G * (LN ? G_BYTES_LN : G_BYTES_PLAIN) + (int)sizeof(Ctrl) + 1024;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kLaunchFailed;
     kern<<<(unsigned)(p.B * p.H), 128 * (G + 1), smem, stream>>>(p);
     return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
@@ -589,16 +673,20 @@ template <int G, bool RND> static int launch_t(const FwdParams& p, cudaStream_t 
 
 }  // namespace tc
 
-int launch_fwd_tc(const FwdParams& p, int groups, cudaStream_t stream) {
+template <bool LN> static int launch_ln(const FwdParams& p, int groups, cudaStream_t stream) {
     switch (groups) {
-        case 2: return tc::launch_t<2, true>(p, stream);
-        case 3: return tc::launch_t<3, true>(p, stream);
-        case 4: return tc::launch_t<4, true>(p, stream);
-        case -2: return tc::launch_t<2, false>(p, stream);
-        case -3: return tc::launch_t<3, false>(p, stream);
-        case -4: return tc::launch_t<4, false>(p, stream);
+        case 2: return tc::launch_t<2, true, LN>(p, stream);
+        case 3: return tc::launch_t<3, true, LN>(p, stream);
+        case 4: return tc::launch_t<4, true, LN>(p, stream);
+        case -2: return tc::launch_t<2, false, LN>(p, stream);
+        case -3: return tc::launch_t<3, false, LN>(p, stream);
+        case -4: return tc::launch_t<4, false, LN>(p, stream);
         default: return kBadShape;
     }
+}
+
+int launch_fwd_tc(const FwdParams& p, int groups, bool ln, cudaStream_t stream) {
+    return ln ? launch_ln<true>(p, groups, stream) : launch_ln<false>(p, groups, stream);
 }
 
 }  // namespace wkv7

@@ -38,8 +38,8 @@ struct BwdParams {
 
 int launch_fwd(const FwdParams& p, int io_dtype, bool ln, cudaStream_t stream);
 int launch_bwd(const BwdParams& p, int io_dtype, bool ln, cudaStream_t stream);
-// tcgen05 forward (bf16 IO, plain attn); |groups| = preparation groups per CTA (2..4); negative: operands are
+// tcgen05 forward (bf16 IO; attn, or attn_ln with ln = true); |groups| = preparation groups per CTA (2..4); negative: operands are
 // not rounded to TF32 by their producer (the tensor core truncates them)
-int launch_fwd_tc(const FwdParams& p, int groups, cudaStream_t stream);
+int launch_fwd_tc(const FwdParams& p, int groups, bool ln, cudaStream_t stream);
 
 }  // namespace wkv7
