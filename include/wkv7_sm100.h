@@ -64,6 +64,17 @@ int64_t wkv7_checkpoint_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
 int wkv7_device_status(void);
 
 /*
+ * Self-test of the bounded device-side wait (no reference counterpart).  Launches one 128-thread CTA in
+ * which two warps wait, with a limit of `limit_cycles` SM cycles, on mbarriers that nothing arrives on
+ * (one polling, one hardware-suspended: the two forms the tcgen05 forward uses), and two more warps then
+ * wait with the kernel's full limit and must return at once because the CTA has aborted.  Synchronises
+ * the stream.  cycles_out (host, 4 values, may be null) receives the cycles each warp's wait took.
+ * Returns the device status word, read and cleared: WKV7_ERR_DEVICE_TIMEOUT when the path works.  The
+ * kernel touches no tensor memory and cannot fault or hang; the context stays usable.
+ */
+int wkv7_selftest_bounded_wait(int64_t limit_cycles, int64_t* cycles_out, void* stream);
+
+/*
  * Which kernel wkv7_fwd and wkv7_attn_ln_fwd run for io_dtype WKV7_BF16 (no reference counterpart: the reference has one
  * forward kernel per dtype).  0: the warp-MMA kernel (mma.sync TF32, state in registers).  2, 3, 4: the
  * tcgen05 kernel (state in tensor memory) with that many preparation groups per CTA; negative values

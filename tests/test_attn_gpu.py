@@ -174,6 +174,26 @@ def test_bf16_arithmetic_on_fp32_outputs():
         assert v <= (4e-2 if k in ('da', 'db', 'dw') else 2e-2), f'{k}: {v:.2e}'
 
 
+def test_bounded_wait_gives_up_and_reports(fwd_impl):
+    """A device-side wait that can never be satisfied runs out after its limit, raises the CTA's abort
+    flag (later waits return at once), leaves WKV7_ERR_DEVICE_TIMEOUT in the status word and the
+    context usable: the next forward runs and reports no error."""
+    if fwd_impl == 0:
+        pytest.skip('one run is enough')
+    _, _lib, attn, synthetic, _ = _mods()
+    limit = 400_000  # cycles, about 0.2 ms
+    cyc = (ctypes.c_int64 * 4)()
+    rc = _lib.lib().wkv7_selftest_bounded_wait(limit, cyc, None)
+    assert rc == -9, rc                                # WKV7_ERR_DEVICE_TIMEOUT
+    assert limit <= cyc[0] < 100 * limit and limit <= cyc[1] < 100 * limit, list(cyc)
+    assert cyc[2] < limit and cyc[3] < limit, list(cyc)  # aborted CTA: no second wait
+    assert _lib.device_status() == 0                   # the status word was cleared by the read
+    d = synthetic.wkv7_inputs(1, 64, 2, N, seed=2, dtype=th.bfloat16, device='cuda')
+    with th.no_grad():
+        y = attn(*[d[n] for n in NAMES], N)
+    assert th.isfinite(y.float()).all() and _lib.device_status() == 0
+
+
 def test_split_sequence_is_bit_identical():
     """State carry: two calls over the halves of T reproduce one call bit for bit (same chunking)."""
     _, _, attn, synthetic, _ = _mods()

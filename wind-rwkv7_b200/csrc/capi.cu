@@ -95,6 +95,24 @@ int64_t wkv7_checkpoint_bytes(int64_t B, int64_t T, int64_t H, int64_t N) {
     return B * H * (T / wkv7::L) * N * N * (int64_t)sizeof(float);
 }
 
+__device__ long long g_selftest_cycles[4];
+
+int wkv7_selftest_bounded_wait(int64_t limit_cycles, int64_t* cycles_out, void* stream) {
+    if (limit_cycles <= 0 || limit_cycles > (1LL << 28)) return WKV7_ERR_SHAPE;
+    int* status = status_ptr();
+    long long* cyc = nullptr;
+    if (!status || cudaGetSymbolAddress((void**)&cyc, g_selftest_cycles) != cudaSuccess) return WKV7_ERR_LAUNCH;
+    int rc = wkv7::launch_bounded_wait_selftest(limit_cycles, status, cyc, (cudaStream_t)stream);
+    if (rc) return rc;
+    if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) return WKV7_ERR_LAUNCH;
+    if (cycles_out) {
+        long long h[4];
+        if (cudaMemcpy(h, cyc, sizeof(h), cudaMemcpyDeviceToHost) != cudaSuccess) return WKV7_ERR_LAUNCH;
+        for (int i = 0; i < 4; ++i) cycles_out[i] = h[i];
+    }
+    return wkv7_device_status();
+}
+
 int wkv7_set_fwd_impl(int impl) {
     if (!valid_fwd_impl(impl)) return WKV7_ERR_SHAPE;
     fwd_impl().store(impl, std::memory_order_relaxed);

@@ -107,7 +107,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // that the many warps that wait for the chain do not take issue slots from the warps that work; the
 // chain's own short waits poll.
 template <bool SLEEP>
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, Ctrl* ctrl, int* status) {
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, Ctrl* ctrl, int* status, long long limit = WAIT_LIMIT) {
     const uint32_t addr = smem_u32(bar);
     long long start = 0;
     for (int spin = 0;; ++spin) {
@@ -121,7 +121,7 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, Ctrl* 
         if (ok) return;
         if (ctrl->abort) return;
         if (spin == 0) start = clock64();
-        else if ((SLEEP || (spin & 63) == 0) && clock64() - start > WAIT_LIMIT) {
+        else if ((SLEEP || (spin & 63) == 0) && clock64() - start > limit) {
             ctrl->abort = 1;
             atomicExch(status, (int)kDeviceTimeout);
             return;
@@ -671,7 +671,37 @@ template <int G, bool RND, bool LN> static int launch_t(const FwdParams& p, cuda
     return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
 
+// Exercises the bounded wait and the abort path with the kernel's own mbar_wait: one CTA of four warps;
+// warp 0 waits (polling) and warp 1 waits (suspended) on mbarriers that nothing ever arrives on, with a
+// short limit; warps 2 and 3 then wait on a third barrier with the full limit and must fall through at
+// once because the CTA has aborted.  Leaves kDeviceTimeout in the status word and writes, per warp, the
+// cycles its wait took.  No tensor memory, no tcgen05: nothing here can fault or hang.
+__global__ void __launch_bounds__(128) bounded_wait_selftest_kernel(long long limit, int* status, long long* cycles) {
+    __shared__ Ctrl ctrl;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    if (tid == 0) {
+        for (int g = 0; g < 3; ++g) mbar_init(&ctrl.full[g], 1);
+        ctrl.abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    // clock reads that cannot be scheduled across the barrier / the wait: they take a value produced there as input
+    auto clock_after = [](int dep) { long long t; asm volatile("mov.u64 %0, %%clock64;" : "=l"(t) : "r"(dep) : "memory"); return t; };
+    const long long t0 = clock_after(__syncthreads_or(0));
+    if (warp == 0) mbar_wait<false>(&ctrl.full[0], 0, &ctrl, status, limit);
+    else if (warp == 1) mbar_wait<true>(&ctrl.full[1], 0, &ctrl, status, limit);
+    const long long t1 = clock_after(__syncthreads_or(0));
+    if (warp >= 2) mbar_wait<true>(&ctrl.full[2], 0, &ctrl, status);  // full limit, but the abort flag is up
+    const long long t2 = clock_after(ctrl.abort);
+    if ((tid & 31) == 0) cycles[warp] = warp < 2 ? t1 - t0 : t2 - t1;
+}
+
 }  // namespace tc
+
+int launch_bounded_wait_selftest(long long limit_cycles, int* status, long long* cycles, cudaStream_t stream) {
+    tc::bounded_wait_selftest_kernel<<<1, 128, 0, stream>>>(limit_cycles, status, cycles);
+    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
 
 template <bool LN> static int launch_ln(const FwdParams& p, int groups, cudaStream_t stream) {
     switch (groups) {

@@ -23,6 +23,7 @@ _SIGNATURES = {
     'wkv7_status_string': (ctypes.c_char_p, [_int]),
     'wkv7_checkpoint_bytes': (_i64, [_i64] * 4),
     'wkv7_device_status': (_int, []),
+    'wkv7_selftest_bounded_wait': (_int, [_i64, ctypes.POINTER(ctypes.c_int64), _vp]),
     'wkv7_set_fwd_impl': (_int, [_int]),
     'wkv7_get_fwd_impl': (_int, []),
     'wkv7_fwd': (_int, [_vp] * 10 + [_i64] * 7 + [_int, _vp]),
