@@ -268,7 +268,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             float* dst = warp == 0 ? sm.QK : warp == 1 ? sm.AK : warp == 2 ? sm.QB : sm.sgrad;
             const bool strict = warp & 1;
             float d[2][4] = {};
-#pragma unroll 2
+#pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
                 FragA<PREC> a = fragA_mk<PREC, true, 1>(Am, OPS, 0, 8 * kk, g, t4);
 #pragma unroll
@@ -312,7 +312,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
         float dvx[2][4] = {};  // LN: bonus-term contribution to dv
         {
             float X[2][4] = {}, Y[2][4] = {};
-#pragma unroll 2
+#pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
                 FragA<PREC> a = fragA_mk<PREC, true, 1>(sm.S0s, SS, 16 * warp, 8 * kk, g, t4);
 #pragma unroll
@@ -556,7 +556,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             float d[2][4] = {};
             const bool strict = warp & 1;
             float* dst = sm.sgrad + warp * (L * SCS);  // 0 dQK, 1 dAK, 2 dQB, 3 dAB
-#pragma unroll 2
+#pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
                 FragA<PREC> aD = fragA_mk<PREC, true, 1>(sm.Dt, OPS, 0, 8 * kk, g, t4);
                 FragA<PREC> aY = LN ? fragA_mk<PREC, true, 1>(sm.Yt, OPS, 0, 8 * kk, g, t4) : fragA_mk_st<IoT, PREC>(dyt, 8 * kk, g, t4);
