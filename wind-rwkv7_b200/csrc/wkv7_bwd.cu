@@ -133,6 +133,26 @@ template <> __device__ __forceinline__ void store_pair<__nv_bfloat16>(__nv_bfloa
     *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(x, y);
 }
 
+// Epilogue stores.  A thread holds columns (2*t4, 2*t4+1) of two adjacent 8-column tiles; stored as they
+// are, a warp-wide store writes 16 bytes per row (half a 32-byte sector).  Lanes t4 and t4^1 swap one
+// pair, after which the even lane holds columns 4m..4m+3 of the first tile and the odd lane the same
+// columns of the second tile (m = t4 / 2): 8-byte stores (bf16), whole sectors per row.
+// `row` points at column 16*warp of the output row.
+__device__ __forceinline__ void store_quad(__nv_bfloat16* row, float a0, float a1, float b0, float b1, int t4) {
+    const __nv_bfloat162 p0 = __floats2bfloat162_rn(a0, a1), p1 = __floats2bfloat162_rn(b0, b1);  // tile 0, tile 1
+    const uint32_t u0 = *reinterpret_cast<const uint32_t*>(&p0), u1 = *reinterpret_cast<const uint32_t*>(&p1);
+    const bool odd = t4 & 1;
+    const uint32_t got = __shfl_xor_sync(0xffffffffu, odd ? u0 : u1, 1);
+    const uint2 v = odd ? make_uint2(got, u1) : make_uint2(u0, got);
+    *reinterpret_cast<uint2*>(row + 8 * (t4 & 1) + 4 * (t4 >> 1)) = v;
+}
+__device__ __forceinline__ void store_quad(float* row, float a0, float a1, float b0, float b1, int t4) {
+    const bool odd = t4 & 1;
+    const float g0 = __shfl_xor_sync(0xffffffffu, odd ? a0 : b0, 1), g1 = __shfl_xor_sync(0xffffffffu, odd ? a1 : b1, 1);
+    const float4 v = odd ? make_float4(g0, g1, b0, b1) : make_float4(a0, a1, g0, g1);
+    *reinterpret_cast<float4*>(row + 8 * (t4 & 1) + 4 * (t4 >> 1)) = v;
+}
+
 template <typename IoT, int PREC, bool LN>
 __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
     using Lay = BwdLayout<IoT>;
@@ -612,6 +632,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
 
         TICK(8)
         // ---------------- epilogue: thread holds rows g, g+8 x key columns n0+2*t4, +1 ---------
+        float outv[5][2][2][2];  // [dq, dw, dk, da, db][tile][row half][column]
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
             const int key = 16 * warp + 8 * nt + 2 * t4;
@@ -663,11 +684,11 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
                     x[hrow][e] = wqv[e] * DQ[nt][i] - kwv[e] * DK[nt][i] - bwv[e] * DB[nt][i] + e2[hrow][e];
                     lwv[hrow][e] = lwa[e];
                 }
-                const long long off = ((long long)c * L + tq) * p.st.t + key;
-                store_pair<IoT>(gout[0] + off, o_q[0], o_q[1]);
-                store_pair<IoT>(gout[2] + off, o_k[0], o_k[1]);
-                store_pair<IoT>(gout[3] + off, o_a[0], o_a[1]);
-                store_pair<IoT>(gout[4] + off, o_b[0], o_b[1]);
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    outv[0][nt][hrow][e] = o_q[e]; outv[2][nt][hrow][e] = o_k[e];
+                    outv[3][nt][hrow][e] = o_a[e]; outv[4][nt][hrow][e] = o_b[e];
+                }
             }
             // inclusive suffix sum over the 16 time rows (rows live in lanes g = 0..7, two halves)
 #pragma unroll
@@ -689,8 +710,15 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
                 const int tq = g + 8 * hrow;
                 const float d0 = (x[hrow][0] - e2[hrow][0] + Gc.x) * lwv[hrow][0];
                 const float d1 = (x[hrow][1] - e2[hrow][1] + Gc.y) * lwv[hrow][1];
-                store_pair<IoT>(gout[1] + ((long long)c * L + tq) * p.st.t + key, d0, d1);
+                outv[1][nt][hrow][0] = d0; outv[1][nt][hrow][1] = d1;
             }
+        }
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            const long long off = ((long long)c * L + g + 8 * hrow) * p.st.t + 16 * warp;
+#pragma unroll
+            for (int ten = 0; ten < 5; ++ten)
+                store_quad(gout[ten] + off, outv[ten][0][hrow][0], outv[ten][0][hrow][1], outv[ten][1][hrow][0], outv[ten][1][hrow][1], t4);
         }
         cp_async_wait<0>();
         __syncthreads();  // (E)
