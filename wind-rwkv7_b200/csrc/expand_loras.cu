@@ -180,7 +180,11 @@ __global__ void __launch_bounds__(128) loras_bwd_kernel(LorasParams p) {
     float dWacc[4][NT][4] = {};
     float dwb[4] = {};
 
-    for (int t0 = 0; t0 < T; t0 += 64) {
+    // gridDim.z CTAs share a sequence: each walks a contiguous range of 64-token tiles (more resident
+    // CTAs per SM; the price is one more flush of the weight-gradient accumulators per extra CTA)
+    const int tiles = (T + 63) / 64, per = (tiles + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int tbeg = (int)blockIdx.z * per * 64, tend = min(T, tbeg + per * 64);
+    for (int t0 = tbeg; t0 < tend; t0 += 64) {
         const long long r0 = b0 + t0 + 16 * warp;
         const bool valid = t0 + 16 * warp < T;
         // ---- stage this tile's LoRA inputs (tanh applied to z_in) ---------------------------------------
@@ -418,7 +422,12 @@ template <int D> static int launch_loras_bwd_t(const LorasParams& p, cudaStream_
     auto kern = loras_bwd_kernel<D>;
     const int smem = (int)sizeof(LorasBwdSmem<D>);
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kLaunchFailed;
-    kern<<<dim3((unsigned)H, (unsigned)(p.rows / p.T)), 128, smem, stream>>>(p);
+    // enough CTAs for about eight per SM (three are resident at a time), at most one per 64-token tile
+    const long long seqs = (long long)H * (p.rows / p.T), tiles = (p.T + 63) / 64;
+    long long nseg = (8 * 148 + seqs - 1) / seqs;
+    if (nseg > tiles) nseg = tiles;
+    if (nseg < 1) nseg = 1;
+    kern<<<dim3((unsigned)H, (unsigned)(p.rows / p.T), (unsigned)nseg), 128, smem, stream>>>(p);
     if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
     const long long n = 4 * p.rows * D;
     loras_reduce_heads_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p, H, D);
