@@ -134,7 +134,16 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void group_bar(int grp) { asm volatile("bar.sync %0, 128;" ::"r"(grp + 1) : "memory"); }
+// named barrier of one preparation group; immediate ids, so that ptxas counts G + 1 barriers for the CTA
+// and not all sixteen
+__device__ __forceinline__ void group_bar(int grp) {
+    switch (grp) {
+        case 0: asm volatile("bar.sync 1, 128;" ::: "memory"); break;
+        case 1: asm volatile("bar.sync 2, 128;" ::: "memory"); break;
+        case 2: asm volatile("bar.sync 3, 128;" ::: "memory"); break;
+        default: asm volatile("bar.sync 4, 128;" ::: "memory"); break;
+    }
+}
 
 // shared-memory matrix descriptor (sm_100 version field set); byte offsets are added to the low word
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr, uint32_t sbo) {
