@@ -53,9 +53,12 @@ extern "C" {
 /* Human-readable text for a status code (host pointer, static storage). */
 const char* wkv7_status_string(int status);
 
-/* Bytes of checkpoint buffer the forward writes for the backward: B*H*(T/16)*N*N*4.  The contents are
- * private to the library (chunk-start states, rounded to TF32 in the bf16 and F32_TF32 classes): only a
- * buffer written by wkv7_fwd / wkv7_attn_ln_fwd with the same io_dtype may be given to the backward. */
+/* Bytes of checkpoint buffer the forward writes for the backward: B*H*(T/16) records of
+ * WKV7_CHECKPOINT_FLOATS floats (the N*N chunk-start state and the chunk's four 16x16 score / inverse
+ * matrices, which the backward loads instead of rebuilding).  The contents are private to the library
+ * (in the bf16 and F32_TF32 classes they are rounded to TF32): only a buffer written by wkv7_fwd /
+ * wkv7_attn_ln_fwd with the same io_dtype may be given to the backward.  0 for N != 64. */
+#define WKV7_CHECKPOINT_FLOATS (64 * 64 + 4 * 16 * 16)
 int64_t wkv7_checkpoint_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
 
 /* Reads and clears the device-side status word of the current device (synchronises the

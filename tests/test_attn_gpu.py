@@ -153,8 +153,8 @@ def test_bf16_arithmetic_on_fp32_outputs():
     dev = {n: d[n].float().cuda().view(B, T, H, N).contiguous() for n in list(NAMES) + ['dy']}
     y = th.empty_like(dev['r'])
     sT = th.empty(B, H, N, N, device='cuda')
-    ck = th.empty(B, H, T // 16, N, N, device='cuda')
     L = _lib.lib()
+    ck = th.empty(L.wkv7_checkpoint_bytes(B, T, H, N) // 4, device='cuda')
     st = (T * H * N, H * N, N)
     rc = L.wkv7_fwd(*[dev[n].data_ptr() for n in NAMES], None, y.data_ptr(), sT.data_ptr(), ck.data_ptr(),
                     B, T, H, N, *st, 2, None)

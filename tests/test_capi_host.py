@@ -40,7 +40,8 @@ def test_status_strings(lib):
 
 
 def test_checkpoint_bytes(lib):
-    assert lib.wkv7_checkpoint_bytes(64, 1024, 12, 64) == 64 * 12 * 64 * 64 * 64 * 4
+    assert lib.wkv7_checkpoint_bytes(64, 1024, 12, 64) == 64 * 12 * 64 * (64 * 64 + 4 * 16 * 16) * 4
+    assert lib.wkv7_checkpoint_bytes(1, 64, 1, 32) == 0  # only N == 64 is built
     assert lib.wkv7_checkpoint_bytes(1, 0, 1, 64) == 0
 
 

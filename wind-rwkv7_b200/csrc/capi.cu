@@ -92,7 +92,8 @@ const char* wkv7_status_string(int status) {
 
 int64_t wkv7_checkpoint_bytes(int64_t B, int64_t T, int64_t H, int64_t N) {
     if (B < 0 || T < 0 || H < 0 || N < 0) return 0;
-    return B * H * (T / wkv7::L) * N * N * (int64_t)sizeof(float);
+    if (N != wkv7::N) return 0;
+    return B * H * (T / wkv7::L) * (int64_t)wkv7::CK_FLOATS * (int64_t)sizeof(float);
 }
 
 __device__ long long g_selftest_cycles[4];

@@ -39,7 +39,7 @@ namespace wkv7 {
 constexpr int SS = N + 8;  // row stride (floats) of the [value][key] state buffers
 // All fp32 tiles of this kernel (operands, scores, score gradients, U, dabu, the two state buffers)
 // carry the column swizzle xcol<1>() of wkv7_common.cuh: each is read both along and across its
-// contraction index.  The one exception is AB, which only feeds the triangular inverse.
+// contraction index.
 
 // Staging tiles [time][channel] in the IO dtype.  bf16: 128-byte rows, the eight 16-byte segments of a
 // row XOR-ed with (row % 8) (cp.async then writes whole aligned 128-byte lines: padded rows cost it
@@ -65,10 +65,9 @@ template <typename IoT, int PREC, bool LN> struct BwdSmem {
     alignas(16) float wq[L * OPS], wa[L * OPS], kwi[L * OPS], bwi[L * OPS];
     alignas(16) float cum[L * OPS];
     alignas(16) float lw[PREC == 3 ? L * OPS : 4];   // single-TF32 path derives it from cum
-    alignas(16) float QK[L * SCS], QB[L * SCS], AK[L * SCS], AI[L * SCS];  // AB (input of the inverse only) lives in sgrad
+    alignas(16) float QK[L * SCS], QB[L * SCS], AK[L * SCS], AI[L * SCS];  // from the checkpoint record, by cp.async
     // Score gradients (stage C).  While stage B runs they are dead, and the same bytes serve as
-    // the per-warp transposition scratch for dv / dg and as the GroupNorm reduction buffers; before
-    // that, while the scores are formed, the first 16 x SCS floats hold AB for the triangular inverse.
+    // the per-warp transposition scratch for dv / dg and as the GroupNorm reduction buffers.
     static constexpr int SCRATCH_FLOATS = WARPS * L * Lay::YS * (int)sizeof(IoT) / 4 + WARPS * L * 5;
     static constexpr int SGRAD_FLOATS = 4 * L * SCS > SCRATCH_FLOATS ? 4 * L * SCS : SCRATCH_FLOATS;
     alignas(16) float sgrad[SGRAD_FLOATS];  // score gradient i at sgrad + i * L * SCS
@@ -173,7 +172,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
     IoT* gdv = (IoT*)p.dv + base;
     const IoT* gg = LN ? (const IoT*)p.g + base : nullptr;
     IoT* gdg = LN ? (IoT*)p.dg + base : nullptr;
-    const float* ckpt = p.ckpt + bh * nchunks * (long long)(N * N);
+    const float* ckpt = p.ckpt + bh * nchunks * (long long)CK_FLOATS;
     constexpr uint32_t ROW_BYTES = N * sizeof(IoT);
 
     if (LN) {
@@ -214,10 +213,18 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             cp_async16(dst, reinterpret_cast<const unsigned char*>(src) + ch * 16);
         }
     };
+    // the checkpoint record of chunk c: its start state and its four 16x16 matrices (QK, QB, AK, AI), which the
+    // forward left there so that the scores and the triangular inverse are not rebuilt here
     auto issue_s0 = [&](int c) {
+        const float* rec = ckpt + (long long)c * CK_FLOATS;
         for (int i = tid; i < N * (N / 4); i += THREADS) {
             const int row = i / (N / 4), ch = i % (N / 4);
-            cp_async16(sm.S0s + row * SS + xcol<1>(row, ch * 4), ckpt + (long long)c * N * N + row * N + ch * 4);
+            cp_async16(sm.S0s + row * SS + xcol<1>(row, ch * 4), rec + CK_STATE + row * N + ch * 4);
+        }
+        for (int i = tid; i < 4 * L * (L / 4); i += THREADS) {
+            const int m = i / (L * (L / 4)), row = (i / (L / 4)) % L, ch = i % (L / 4);
+            float* dst = m == 0 ? sm.QK : m == 1 ? sm.QB : m == 2 ? sm.AK : sm.AI;
+            cp_async16(dst + row * SCS + xcol<1>(row, ch * 4), rec + CK_QK + m * (L * L) + row * L + ch * 4);
         }
     };
     if (nchunks > 0) {
@@ -280,44 +287,6 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             issue_in(c - 1);
             issue_vdy(c - 1, vs ^ 1);
         }
-
-        // ---------------- P2: masked score matrices, one per warp ------------------------------
-        {
-            const float* Am = (warp & 1) ? sm.wa : sm.wq;
-            const float* Bm = (warp >> 1) ? sm.bwi : sm.kwi;
-            float* dst = warp == 0 ? sm.QK : warp == 1 ? sm.AK : warp == 2 ? sm.QB : sm.sgrad;
-            const bool strict = warp & 1;
-            float d[2][4] = {};
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {
-                FragA<PREC> a = fragA_mk<PREC, true, 1>(Am, OPS, 0, 8 * kk, g, t4);
-#pragma unroll
-                for (int nt = 0; nt < 2; ++nt) mma<PREC>(d[nt], a, fragB_nk<PREC, true, 1>(Bm, OPS, 8 * nt, 8 * kk, g, t4));
-            }
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                const int s = 8 * nt + 2 * t4;
-                auto keep = [&](int tq, int ss) { return strict ? ss < tq : ss <= tq; };
-                auto val = [&](float x) { return warp == 3 ? x : pre<PREC>(x); };  // AB only feeds the inverse
-                const float2 lo = make_float2(keep(g, s) ? val(d[nt][0]) : 0.f, keep(g, s + 1) ? val(d[nt][1]) : 0.f);
-                const float2 hi2 = make_float2(keep(g + 8, s) ? val(d[nt][2]) : 0.f, keep(g + 8, s + 1) ? val(d[nt][3]) : 0.f);
-                if (warp == 3) {  // AB is kept transposed for the inverse
-                    dst[s * SCS + g] = lo.x; dst[(s + 1) * SCS + g] = lo.y;
-                    dst[s * SCS + g + 8] = hi2.x; dst[(s + 1) * SCS + g + 8] = hi2.y;
-                } else {
-                    *reinterpret_cast<float2*>(dst + g * SCS + xcol<1>(g, s)) = lo;
-                    *reinterpret_cast<float2*>(dst + (g + 8) * SCS + xcol<1>(g, s)) = hi2;
-                }
-            }
-        }
-        if (warp == 3) {  // AI = (I - AB)^-1
-            __syncwarp();
-            if (lane < L) tri_inverse_column<PREC, 1>(sm.sgrad, sm.AI, lane);
-        }
-
-        TICK(2)
-        __syncthreads();  // (B)
-        TICK(3)
 
         // ---------------- stage B: rows = value index -----------------------------------------
         const unsigned char* vt = sm.st_v[vs];

@@ -14,6 +14,12 @@ constexpr int WARPS = 4;     // one warp per 16 value rows of the state
 constexpr int THREADS = 32 * WARPS;
 constexpr int OPS = N + 8;   // row stride (floats) of the [time][key] operand buffers
 constexpr int SCS = L + 8;   // row stride (floats) of the [time][time] score buffers
+// One checkpoint record per 16-step chunk, written by the forward for the backward: the fp32 state at
+// the start of the chunk [N][N], then the chunk's four state-independent 16x16 matrices as plain
+// row-major fp32 [L][L]: QK, QB (lower triangular), AK (strictly lower), AI = (I - AB)^-1.  The backward
+// loads them instead of rebuilding them (two score products per warp and the 16-step inverse).
+constexpr int CK_STATE = 0, CK_QK = N * N, CK_QB = CK_QK + L * L, CK_AK = CK_QB + L * L, CK_AI = CK_AK + L * L;
+constexpr int CK_FLOATS = CK_AI + L * L;  // 5120 floats = 20 KB
 
 // ---- status codes (mirrored in include/wkv7_sm100.h) -------------------------------------
 enum Status : int {

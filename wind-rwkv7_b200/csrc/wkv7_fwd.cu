@@ -192,7 +192,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
         TICK(3)
         // ---------------- chain, part 1: needs only S and the scaled operands ------------------
         if (p.ckpt) {
-            float* ck = p.ckpt + (bh * nchunks + c) * (long long)(N * N);
+            float* ck = p.ckpt + (bh * nchunks + c) * (long long)CK_FLOATS;
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
                 // in the single-TF32 class the checkpoint is stored already rounded: the backward uses it
@@ -213,6 +213,14 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
         TICK(4)
         __syncthreads();  // (B) scores and AI visible
         TICK(5)
+        if (p.ckpt) {  // the chunk's four 16x16 matrices go into the checkpoint record: 8 floats per thread
+            float* ck = p.ckpt + (bh * nchunks + c) * (long long)CK_FLOATS + CK_QK;
+            const int m = tid >> 5, r = (tid & 31) >> 1, hf = tid & 1;
+            const float* src = (m == 0 ? sm.QK : m == 1 ? sm.QB : m == 2 ? sm.AK : sm.AI) + r * SCS + 8 * hf;
+            float4* dst = reinterpret_cast<float4*>(ck + m * (L * L) + r * L + 8 * hf);
+            dst[0] = *reinterpret_cast<const float4*>(src);
+            dst[1] = *reinterpret_cast<const float4*>(src + 4);
+        }
 
         // ---------------- chain, part 2 ----------------------------------------------------------
         const unsigned char* vt = sm.st_v[c & 1];

@@ -176,6 +176,8 @@ __device__ __forceinline__ void tmem_st16(uint32_t ta, const uint32_t* v) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+__device__ __forceinline__ float rnd(float x) { return __uint_as_float(tf32_rna(x)); }
+
 // byte offset of the 16-byte chunk holding (row, k..k+3) in a K-major tile; sbo = bytes per 8-row group
 __device__ __forceinline__ int kchunk(int row, int kc, int sbo) { return (row >> 3) * sbo + kc * 128 + (row & 7) * 16; }
 
@@ -183,8 +185,8 @@ __device__ __forceinline__ int kchunk(int row, int kc, int sbo) { return (row >>
 // as element (row S_, k = col).  Right-looking substitution as in tri_inverse_column().
 template <int S_> __device__ __forceinline__ void tri_step_tc(float (&r)[L], const float (&c)[L], float (&cn)[L], const float* ABt, unsigned char* AI, int col) {
     if (S_ + 1 < L) tri_fetch_row<(S_ + 1 < L ? S_ + 1 : 0)>(cn, ABt);
-    const float ms = r[S_];
-    *reinterpret_cast<float*>(AI + kchunk(S_, col >> 2, 512) + (col & 3) * 4) = ms;
+    const float ms = r[S_], msr = rnd(ms);
+    *reinterpret_cast<float*>(AI + kchunk(S_, col >> 2, 512) + (col & 3) * 4) = msr;
 #pragma unroll
     for (int tq = S_ + 1; tq < L; ++tq) r[tq] = fmaf(c[tq], ms, r[tq]);
 }
@@ -203,7 +205,6 @@ __device__ __forceinline__ void tri_inverse_tc(const float* ABt, unsigned char* 
     tri_step_tc<14>(r, ca, cb, ABt, AI, col);  tri_step_tc<15>(r, cb, ca, ABt, AI, col);
 }
 
-__device__ __forceinline__ float rnd(float x) { return __uint_as_float(tf32_rna(x)); }
 // two 16-byte chunks of an operand tile; R: round to TF32 (nearest) first, otherwise the tensor core
 // truncates the low 13 mantissa bits when it reads the operand
 template <bool R> __device__ __forceinline__ void store8t(unsigned char* p0, unsigned char* p1, const float (&f)[8]) {
@@ -293,7 +294,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
     if (warp < 4) {
         const int i = 16 * warp + (lane & 15);
         const float* s0 = p.s0 ? p.s0 + bh * N * N + i * N : nullptr;
-        float* ck = (p.ckpt && lane < 16) ? p.ckpt + bh * nchunks * (long long)(N * N) + i * N : nullptr;
+        float* ck = (p.ckpt && lane < 16) ? p.ckpt + bh * nchunks * (long long)CK_FLOATS + i * N : nullptr;
 #pragma unroll
         for (int cb = 0; cb < N; cb += 16) {
             uint32_t v[16];
@@ -402,7 +403,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
             tc_fence_after();
             const bool last = cc + 1 == nchunks;
             float* sdst = last ? (p.sT ? p.sT + bh * N * N : nullptr)
-                               : (p.ckpt ? p.ckpt + (bh * nchunks + cc + 1) * (long long)(N * N) : nullptr);
+                               : (p.ckpt ? p.ckpt + (bh * nchunks + cc + 1) * (long long)CK_FLOATS : nullptr);
 #ifdef WKV7_TC_NOCKPT
             sdst = nullptr;
 #endif
@@ -653,6 +654,22 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(&ctrl->full[grp]);
+            // The chunk's four 16x16 matrices go into its checkpoint record (row-major, one row per lane), copied
+            // from the operand tiles after the chain has been given the go-ahead: off the critical path.
+            if (p.ckpt && wg < 2 && lane < 16) {
+#ifndef WKV7_TC_NOCKPT
+                float* ckm = p.ckpt + (bh * nchunks + c) * (long long)CK_FLOATS;
+                const unsigned char* t0 = gs + (wg == 0 ? G_SC : G_SC) + kchunk(wg == 0 ? lane : 16 + lane, 0, 512);  // AK | QK row
+                const unsigned char* t1 = gs + (wg == 0 ? G_AI : G_QB) + kchunk(lane, 0, 512);                      // AI | QB row
+                float* d0 = ckm + (wg == 0 ? CK_AK : CK_QK) + lane * L;
+                float* d1 = ckm + (wg == 0 ? CK_AI : CK_QB) + lane * L;
+#pragma unroll
+                for (int qd = 0; qd < 4; ++qd) {
+                    *reinterpret_cast<float4*>(d0 + 4 * qd) = *reinterpret_cast<const float4*>(t0 + qd * 128);
+                    *reinterpret_cast<float4*>(d1 + 4 * qd) = *reinterpret_cast<const float4*>(t1 + qd * 128);
+                }
+#endif
+            }
             cprev = c;
         }
         if (cprev >= 0) {

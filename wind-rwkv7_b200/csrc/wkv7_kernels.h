@@ -11,7 +11,7 @@ struct FwdParams {
     const float* s0;                    // [B,H,N,N] or null (zeros)
     void* y;                            // [B,T,H,N]
     float* sT;                          // [B,H,N,N] or null
-    float* ckpt;                        // [B,H,T/16,N,N] chunk-start states, or null
+    float* ckpt;                        // [B,H,T/16,CK_FLOATS] checkpoint records (chunk-start state + 4 matrices), or null
     long long B, T, H;
     Strides st;
     float eps;

@@ -14,6 +14,9 @@ LIB_PATH = os.path.join(_PKG_ROOT, 'lib', 'libwkv7_sm100.so')
 WKV7_BF16, WKV7_F32 = 0, 1
 HEAD_SIZE = 64
 CHUNK = 16
+# floats per checkpoint record (WKV7_CHECKPOINT_FLOATS of the header): the 64x64 chunk-start state and the
+# chunk's four 16x16 matrices; the checkpoint tensor is [B, H, T/16, CKPT_FLOATS] fp32
+CKPT_FLOATS = 64 * 64 + 4 * 16 * 16
 
 _lib = None
 
