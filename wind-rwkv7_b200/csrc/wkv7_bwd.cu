@@ -221,10 +221,15 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             const int row = i / (N / 4), ch = i % (N / 4);
             cp_async16(sm.S0s + row * SS + xcol<1>(row, ch * 4), rec + CK_STATE + row * N + ch * 4);
         }
+        // the matrices are read in the order they are stored (the forward's tile layout: consecutive 16-byte pieces
+        // walk 8 rows of one 4-column chunk), so that a warp reads whole 128-byte lines
         for (int i = tid; i < 4 * L * (L / 4); i += THREADS) {
-            const int m = i / (L * (L / 4)), row = (i / (L / 4)) % L, ch = i % (L / 4);
-            float* dst = m == 0 ? sm.QK : m == 1 ? sm.QB : m == 2 ? sm.AK : sm.AI;
-            cp_async16(dst + row * SCS + xcol<1>(row, ch * 4), rec + CK_QK + m * (L * L) + row * L + ch * 4);
+            const int tile = i < 128 ? 0 : i < 192 ? 1 : 2;           // [AK;QK] (128 pieces), AI (64), QB (64)
+            const int pc = i - (tile == 0 ? 0 : tile == 1 ? 128 : 192);
+            const int r = (pc >> 5) * 8 + (pc & 7), ch = (pc >> 3) & 3;  // row within the tile, 4-column chunk
+            float* dst = tile == 1 ? sm.AI : tile == 2 ? sm.QB : (r < L ? sm.AK : sm.QK);
+            const int row = r & (L - 1);
+            cp_async16(dst + row * SCS + xcol<1>(row, ch * 4), rec + CK_MATS + i * 4);
         }
     };
     if (nchunks > 0) {

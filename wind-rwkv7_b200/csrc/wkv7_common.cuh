@@ -15,11 +15,16 @@ constexpr int THREADS = 32 * WARPS;
 constexpr int OPS = N + 8;   // row stride (floats) of the [time][key] operand buffers
 constexpr int SCS = L + 8;   // row stride (floats) of the [time][time] score buffers
 // One checkpoint record per 16-step chunk, written by the forward for the backward: the fp32 state at
-// the start of the chunk [N][N], then the chunk's four state-independent 16x16 matrices as plain
-// row-major fp32 [L][L]: QK, QB (lower triangular), AK (strictly lower), AI = (I - AB)^-1.  The backward
-// loads them instead of rebuilding them (two score products per warp and the 16-step inverse).
-constexpr int CK_STATE = 0, CK_QK = N * N, CK_QB = CK_QK + L * L, CK_AK = CK_QB + L * L, CK_AI = CK_AK + L * L;
-constexpr int CK_FLOATS = CK_AI + L * L;  // 5120 floats = 20 KB
+// the start of the chunk [N][N], then the chunk's four state-independent 16x16 matrices QK, QB (lower
+// triangular), AK (strictly lower), AI = (I - AB)^-1.  The backward loads them instead of rebuilding
+// them (two score products per warp and the 16-step inverse).  The matrices are kept in the layout of
+// the tcgen05 forward's operand tiles, so that that kernel can copy them out with one bulk copy:
+// three K-major tiles of 16-byte chunks, element (row, col) at float (row/8)*128 + (col/4)*32 + (row%8)*4
+// + col%4; the first tile has 32 rows (AK in rows 0-15, QK in rows 16-31), then AI, then QB.
+constexpr int CK_STATE = 0, CK_MATS = N * N;
+constexpr int CK_SC = CK_MATS, CK_AI = CK_SC + 2 * L * L, CK_QB = CK_AI + L * L;
+__host__ __device__ constexpr int ck_tile_at(int row, int chunk) { return (row >> 3) * 128 + chunk * 32 + (row & 7) * 4; }
+constexpr int CK_FLOATS = CK_QB + L * L;  // 5120 floats = 20 KB
 
 // ---- status codes (mirrored in include/wkv7_sm100.h) -------------------------------------
 enum Status : int {

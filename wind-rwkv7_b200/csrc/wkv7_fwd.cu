@@ -214,12 +214,13 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
         __syncthreads();  // (B) scores and AI visible
         TICK(5)
         if (p.ckpt) {  // the chunk's four 16x16 matrices go into the checkpoint record: 8 floats per thread
-            float* ck = p.ckpt + (bh * nchunks + c) * (long long)CK_FLOATS + CK_QK;
+            float* ck = p.ckpt + (bh * nchunks + c) * (long long)CK_FLOATS;
             const int m = tid >> 5, r = (tid & 31) >> 1, hf = tid & 1;
             const float* src = (m == 0 ? sm.QK : m == 1 ? sm.QB : m == 2 ? sm.AK : sm.AI) + r * SCS + 8 * hf;
-            float4* dst = reinterpret_cast<float4*>(ck + m * (L * L) + r * L + 8 * hf);
-            dst[0] = *reinterpret_cast<const float4*>(src);
-            dst[1] = *reinterpret_cast<const float4*>(src + 4);
+            float* dst = ck + (m == 0 ? CK_SC + ck_tile_at(16 + r, 2 * hf) : m == 1 ? CK_QB + ck_tile_at(r, 2 * hf)
+                                                                            : m == 2 ? CK_SC + ck_tile_at(r, 2 * hf) : CK_AI + ck_tile_at(r, 2 * hf));
+            *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+            *reinterpret_cast<float4*>(dst + 32) = *reinterpret_cast<const float4*>(src + 4);
         }
 
         // ---------------- chain, part 2 ----------------------------------------------------------

@@ -65,6 +65,7 @@ constexpr int G_BWF = 24576;   // bwf [time][key]    MN-major                409
 constexpr int G_SC = 28672;    // [AK;QK]  32 rows x 16, K-major             2048
 constexpr int G_AI = 30720;    // AI       16 x 16, K-major                  1024
 constexpr int G_QB = 31744;    // QB       16 x 16, K-major                  1024
+static_assert(G_AI == G_SC + 2048 && G_QB == G_AI + 1024, "[AK;QK], AI, QB must be contiguous: they leave as one bulk copy");
 constexpr int G_DF = 32768;    // eight 8x8 diagonal blocks of fw, K-major   2048
 constexpr int G_ABT = 34816;   // AB transposed, fp32 [16][SCS]              1536
 constexpr int G_RAW = 36352;   // q, w, k, a, b, v staging                   6 * 2048
@@ -520,6 +521,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
 #endif
         for (int c = grp; c < nchunks; c += G, ++k) {
             cp_async_wait<0>();
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the matrix copy of the previous own chunk (its issuer only)
             group_bar(grp);
             TCK(0)
             // ---------------- decay scan, into registers ---------------------------------------------
@@ -654,24 +656,25 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(&ctrl->full[grp]);
-            // The chunk's four 16x16 matrices go into its checkpoint record (row-major, one row per lane), copied
-            // from the operand tiles after the chain has been given the go-ahead: off the critical path.
-            if (p.ckpt && wg < 2 && lane < 16) {
+            // The chunk's four 16x16 matrices go into its checkpoint record: the three tiles [AK;QK], AI, QB are
+            // contiguous in shared memory and are stored as they are, by one bulk copy issued after the chain
+            // has been given the go-ahead.  The issuing thread waits on the same barrier as the chain (all 128
+            // threads have written and fenced their part of the tiles by then).
 #ifndef WKV7_TC_NOCKPT
-                float* ckm = p.ckpt + (bh * nchunks + c) * (long long)CK_FLOATS;
-                const unsigned char* t0 = gs + (wg == 0 ? G_SC : G_SC) + kchunk(wg == 0 ? lane : 16 + lane, 0, 512);  // AK | QK row
-                const unsigned char* t1 = gs + (wg == 0 ? G_AI : G_QB) + kchunk(lane, 0, 512);                      // AI | QB row
-                float* d0 = ckm + (wg == 0 ? CK_AK : CK_QK) + lane * L;
-                float* d1 = ckm + (wg == 0 ? CK_AI : CK_QB) + lane * L;
-#pragma unroll
-                for (int qd = 0; qd < 4; ++qd) {
-                    *reinterpret_cast<float4*>(d0 + 4 * qd) = *reinterpret_cast<const float4*>(t0 + qd * 128);
-                    *reinterpret_cast<float4*>(d1 + 4 * qd) = *reinterpret_cast<const float4*>(t1 + qd * 128);
+            if (p.ckpt && wg == 0) {
+                if (elect_one()) {
+                    mbar_wait<true>(&ctrl->full[grp], k & 1, ctrl, p.status);
+                    float* ckm = p.ckpt + (bh * nchunks + c) * (long long)CK_FLOATS + CK_MATS;
+                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                 ::"l"(__cvta_generic_to_global(ckm)), "r"(smem_u32(gs + G_SC)), "n"(4 * L * L * 4) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
-#endif
+                __syncwarp();
             }
+#endif
             cprev = c;
         }
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory must outlive the last matrix copy
         if (cprev >= 0) {
             read_results(cprev, k - 1);
         }
