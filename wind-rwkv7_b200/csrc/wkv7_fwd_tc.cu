@@ -38,9 +38,18 @@
 //     base exists for 32-bit MN-major operands: rows of 32 channels (128 B) per time step, the
 //     32-byte unit index XOR-ed with (t % 4); LBO = stride between the two 32-channel halves,
 //     SBO = 512 B (four time steps).
+// Checkpoint states leave through shared memory: tensor memory holds one state row per lane, so a warp-wide
+// store from registers can write one 32-byte sector per lane at best (512 wavefronts of the SM's L1 data
+// pipe per 16 KB state).  Instead each thread writes its row into a 128-byte-swizzled staging tile (two
+// [64 rows][32 floats] halves in the dead [wa;wq] / [kwi;bwi] tiles, conflict-free 16-byte stores) and one
+// thread issues two tensor-map bulk stores (cp.async.bulk.tensor.2d, shared -> global), which undo the
+// swizzle: the record in global memory stays plain row-major.
 // Every wait on an mbarrier is bounded; a wait that runs out raises an abort flag that makes all
 // later waits of the CTA return at once, records kDeviceTimeout and lets the CTA finish (tensor
 // memory is still released).
+#include <cuda.h>
+#include <cstring>
+
 #include "wkv7_kernels.h"
 #ifdef WKV7_TIMING
 #include <cstdio>
@@ -72,7 +81,7 @@ constexpr int G_RAW = 36352;   // q, w, k, a, b, v staging                   6 *
 constexpr int G_GRAW = 48640;  // attn_ln only: the gate tile, double buffered (read one iteration later)  2 * 2048
 constexpr int G_BYTES_PLAIN = 49152;  // 48 KB (48640 rounded up to 1 KB)
 constexpr int G_BYTES_LN = 53248;     // 52 KB
-// attn_ln epilogue scratch inside the [kwi;bwi] tile, which is dead once the score product has completed
+// attn_ln epilogue scratch inside the kwf / bwf tiles, which are dead once the chain step has completed
 constexpr int LN_YS = 68;                  // row stride (floats) of the fp32 [time][value] staging of Y
 constexpr int LN_PART = L * LN_YS * 4;     // byte offset of the per-warp partial sums [4][16][2] behind it
 
@@ -242,7 +251,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 template <int G, bool RND, bool LN>
-__global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams p) {
+__global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams p, const __grid_constant__ CUtensorMap ckmap) {
     using IoT = __nv_bfloat16;
     constexpr int G_BYTES = LN ? G_BYTES_LN : G_BYTES_PLAIN;
     constexpr int NCOLS = 512;
@@ -427,9 +436,9 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
             } else {
                 // attn_ln epilogue (reference: wind_rwkv/rwkv7/attn_ln.cu:176-205): GroupNorm over the head's 64
                 // value channels of each time step, + bonus dot * v, * gate.  Y^T goes to shared memory as
-                // fp32 [time][value]; then one thread = one time step x 8 value channels, the mapping of the scan.
-                float* ysf = reinterpret_cast<float*>(gs + G_KB);
-                float* part = reinterpret_cast<float*>(gs + G_KB + LN_PART);
+                // fp32 [time][value] (in the dead kwf / bwf tiles); then one thread = one time step x 8 value channels, the mapping of the scan.
+                float* ysf = reinterpret_cast<float*>(gs + G_KWF);
+                float* part = reinterpret_cast<float*>(gs + G_KWF + LN_PART);
                 {
                     uint32_t yv[16];
                     tmem_ld16(tlane + C_XY + 32 * (cc & 1) + 16, yv);
@@ -483,7 +492,44 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                 }
                 group_bar(grp);  // the scratch lies in an operand tile that is rewritten next
             }
-            if (sdst) {
+            if (sdst && !last) {
+                // checkpoint state: rounded to TF32 (the backward uses it only as a tensor-core operand), staged in
+                // the 128-byte-swizzled layout the tensor-map store expects: half h = columns 32h..32h+31,
+                // row i at i*128 bytes, its 16-byte unit u at (u ^ (i & 7))
+                unsigned char* stage = gs + G_WAQ;
+                const int i = 16 * wg + (lane & 15);
+#pragma unroll
+                for (int qt = 0; qt < 4; ++qt) {
+                    uint32_t sv[16];
+                    tmem_ld16(tlane + C_S + 64 * ((cc + 1) & 1) + 16 * qt, sv);
+                    tmem_ld_wait();
+                    if (qt == 3) {
+                        tc_fence_before();
+                        mbar_arrive(&ctrl->rdone[grp]);
+                    }
+                    if (lane < 16) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int u = 4 * qt + j;
+                            *reinterpret_cast<uint4*>(stage + (u >> 3) * 8192 + i * 128 + (((u & 7) ^ (i & 7)) << 4)) =
+                                make_uint4(tf32_rna(__uint_as_float(sv[4 * j])), tf32_rna(__uint_as_float(sv[4 * j + 1])),
+                                           tf32_rna(__uint_as_float(sv[4 * j + 2])), tf32_rna(__uint_as_float(sv[4 * j + 3])));
+                        }
+                    }
+                }
+                fence_async_smem();
+                group_bar(grp);
+                if (wg == 0 && elect_one()) {
+                    const int rec_row = (int)((bh * nchunks + cc + 1) * (CK_FLOATS / N));  // a record is 80 rows of 64 floats
+                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                                 ::"l"(&ckmap), "r"(0), "r"(rec_row), "r"(smem_u32(stage)) : "memory");
+                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                                 ::"l"(&ckmap), "r"(32), "r"(rec_row), "r"(smem_u32(stage + 8192)) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+                __syncwarp();
+            } else if (sdst) {
+                // final state: exact, straight from registers (32-byte stores: whole sectors of the lane's 256-byte row)
                 float* d = sdst + (16 * wg + (lane & 15)) * N;
 #pragma unroll
                 for (int qt = 0; qt < 4; ++qt) {
@@ -494,13 +540,6 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                         tc_fence_before();
                         mbar_arrive(&ctrl->rdone[grp]);
                     }
-                    // Checkpoints are stored rounded to TF32 (the backward uses them only as tensor-core operands
-                    // and skips the rounding at every load); the final state is stored exactly.
-                    if (!last) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) sv[i] = tf32_rna(__uint_as_float(sv[i]));
-                    }
-                    // 32-byte stores: every lane writes whole sectors of its own 256-byte state row
                     if (lane < 16) {
 #pragma unroll
                         for (int q8 = 0; q8 < 2; ++q8)
@@ -572,7 +611,13 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
             }
             TCK(1)
             // ---------------- results of the previous own chunk (its operand tiles are free afterwards) --
-            if (cprev >= 0) read_results(cprev, k - 1);
+            if (cprev >= 0) {
+                read_results(cprev, k - 1);
+                if (p.ckpt) {  // the staging tiles are operand tiles: wait until the bulk stores have read them
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    group_bar(grp);
+                }
+            }
             TCK(2)
             // ---------------- operand tiles -----------------------------------------------------------
             {
@@ -677,6 +722,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory must outlive the last matrix copy
         if (cprev >= 0) {
             read_results(cprev, k - 1);
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // ... and the last state copy
         }
 #ifdef WKV7_TIMING
         if (blockIdx.x == 0 && lane == 0 && k > 0)
@@ -692,11 +738,36 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
     }
 }
 
+// Tensor map over the checkpoint buffer seen as an fp32 matrix [records * 80 rows][64 floats]; box = 64 rows x
+// 32 floats (128 bytes) with the 128-byte swizzle.  Encoded through the runtime's driver-entry-point query
+// (the library does not link against libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static bool encode_checkpoint_map(CUtensorMap* m, float* base, long long records) {
+    static EncodeTiledFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) f = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(f);
+    }();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)(records * (CK_FLOATS / N))};
+    const cuuint64_t strides[1] = {(cuuint64_t)(N * sizeof(float))};
+    const cuuint32_t box[2] = {32, (cuuint32_t)N};
+    const cuuint32_t es[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int G, bool RND, bool LN> static int launch_t(const FwdParams& p, cudaStream_t stream) {
     auto kern = wkv7_fwd_tc_kernel<G, RND, LN>;
     const int smem = G * (LN ? G_BYTES_LN : G_BYTES_PLAIN) + (int)sizeof(Ctrl) + 1024;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kLaunchFailed;
-    kern<<<(unsigned)(p.B * p.H), 128 * (G + 1), smem, stream>>>(p);
+    alignas(64) CUtensorMap ckmap;
+    memset(&ckmap, 0, sizeof(ckmap));
+    if (p.ckpt && !encode_checkpoint_map(&ckmap, p.ckpt, p.B * p.H * (p.T / L))) return kLaunchFailed;
+    kern<<<(unsigned)(p.B * p.H), 128 * (G + 1), smem, stream>>>(p, ckmap);
     return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
 
