@@ -29,12 +29,18 @@
 // Stage B (rows = value index, per warp, no cross-warp traffic): U^T, du^T, dabu^T, dV^T, dS0.
 // Stage C (contractions over the value index, warp owns 16 key columns): the four score
 // gradients and DA, DQ, DB, DK with S0 and dSf read from shared memory.
+#include <cuda.h>
+#include <cstring>
+
 #include "wkv7_kernels.h"
 #ifdef WKV7_TIMING
 #include <cstdio>
 #endif
 
 namespace wkv7 {
+
+// Tensor maps of the five [time x key] outputs (dq, dw, dk, da, db) for the bulk-store epilogue.
+struct alignas(64) OutMaps { CUtensorMap m[5]; };
 
 constexpr int SS = N + 8;  // row stride (floats) of the [value][key] state buffers
 // All fp32 tiles of this kernel (operands, scores, score gradients, U, dabu, the two state buffers)
@@ -76,6 +82,10 @@ template <typename IoT, int PREC, bool LN> struct BwdSmem {
     alignas(16) float S0s[N * SS], dSs[N * SS];  // chunk-start state and dSf as [value][key]
     alignas(16) float fw[N];
     alignas(16) float Gp[2][WARPS][N];
+    // bf16 attn: the five [16 x 64] output tiles of a chunk, 128-byte rows with the 16-byte unit index XOR-ed
+    // with (row % 8) (what a 128-byte-swizzle tensor map expects), stored by five bulk tensor copies per chunk
+    static constexpr bool TMA_OUT = sizeof(IoT) == 2 && !LN;
+    alignas(1024) unsigned char ostage[TMA_OUT ? 5 * 2048 : 16];
     alignas(16) float lnp[LN ? 3 * N : 4];
     float bdot[L], sbon[L];
 };
@@ -153,11 +163,12 @@ __device__ __forceinline__ void store_quad(float* row, float a0, float a1, float
 }
 
 template <typename IoT, int PREC, bool LN>
-__global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
+__global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __grid_constant__ OutMaps omaps) {
     using Lay = BwdLayout<IoT>;
     using Smem = BwdSmem<IoT, PREC, LN>;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
+    constexpr bool TMA_OUT = Smem::TMA_OUT;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const long long bh = blockIdx.x;
@@ -580,6 +591,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
             }
         }
         TICK(6)
+        if (TMA_OUT) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // previous chunk's output tiles have been read
         __syncthreads();  // (C2) score gradients visible; S0s free
         TICK(7)
         if (c > 0) issue_s0(c - 1);
@@ -687,17 +699,41 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p) {
                 outv[1][nt][hrow][0] = d0; outv[1][nt][hrow][1] = d1;
             }
         }
-#pragma unroll
-        for (int hrow = 0; hrow < 2; ++hrow) {
-            const long long off = ((long long)c * L + g + 8 * hrow) * p.st.t + 16 * warp;
+        if (TMA_OUT) {
+            // into the swizzled staging tiles: 4-byte stores, a warp-wide store covers 8 rows x 16 bytes in 8 different
+            // 16-byte units (conflict-free); the tiles leave by bulk tensor stores after the barrier below
 #pragma unroll
             for (int ten = 0; ten < 5; ++ten)
-                store_quad(gout[ten] + off, outv[ten][0][hrow][0], outv[ten][0][hrow][1], outv[ten][1][hrow][0], outv[ten][1][hrow][1], t4);
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int hrow = 0; hrow < 2; ++hrow) {
+                        const int tq = g + 8 * hrow;
+                        const __nv_bfloat162 v2 = __floats2bfloat162_rn(outv[ten][nt][hrow][0], outv[ten][nt][hrow][1]);
+                        *reinterpret_cast<__nv_bfloat162*>(sm.ostage + ten * 2048 + tq * 128 + ((((2 * warp + nt) ^ (tq & 7))) << 4) + 4 * t4) = v2;
+                    }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        } else {
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                const long long off = ((long long)c * L + g + 8 * hrow) * p.st.t + 16 * warp;
+#pragma unroll
+                for (int ten = 0; ten < 5; ++ten)
+                    store_quad(gout[ten] + off, outv[ten][0][hrow][0], outv[ten][0][hrow][1], outv[ten][1][hrow][0], outv[ten][1][hrow][1], t4);
+            }
         }
         cp_async_wait<0>();
         __syncthreads();  // (E)
+        if (TMA_OUT && tid == 0) {
+#pragma unroll
+            for (int ten = 0; ten < 5; ++ten)
+                asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];"
+                             ::"l"(&omaps.m[ten]), "r"(0), "r"((int)hi), "r"(c * L), "r"((int)bi), "r"(smem_u32(sm.ostage + ten * 2048)) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
         TICK(9)
     }
+    if (TMA_OUT) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory must outlive the last stores
 #ifdef WKV7_TIMING
     if (blockIdx.x == 0 && lane == 0)
         printf("bwd warp %d: P1 %lld | syncA %lld | P2P3 %lld | syncB %lld | stageB %lld | syncC1 %lld | Ca %lld | syncC2 %lld | Cb %lld | epi+syncE %lld\n", warp,
@@ -746,13 +782,43 @@ __global__ void reduce_dparams_kernel(const float* __restrict__ ws, float* __res
     out[i] = acc;
 }
 
+// Tensor map of a bf16 [B,T,H,N] tensor with element strides st; box = one head, 16 time steps, 64 channels,
+// 128-byte swizzle.  Encoded through the runtime's driver-entry-point query (no link against libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static bool encode_bthn_map(CUtensorMap* m, void* base, long long B, long long T, long long H, const Strides& st) {
+    static EncodeTiledFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) f = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(f);
+    }();
+    if (!fn) return false;
+    const cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
+    // a dimension of extent 1 may carry any stride; give it a valid (16-byte multiple, non-zero) one
+    auto sb = [&](long long s, long long fallback) { return (cuuint64_t)((s > 0 ? s : fallback) * 2); };
+    const cuuint64_t strides[3] = {sb(st.h, N), sb(st.t, H * N), sb(st.b, T * H * N)};
+    const cuuint32_t box[4] = {(cuuint32_t)N, 1, (cuuint32_t)L, 1};
+    const cuuint32_t es[4] = {1, 1, 1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <typename IoT, int PREC, bool LN> static int launch_bwd_t(const BwdParams& p, cudaStream_t stream) {
     using Smem = BwdSmem<IoT, PREC, LN>;
     auto kern = wkv7_bwd_kernel<IoT, PREC, LN>;
     const int smem = (int)sizeof(Smem);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return kLaunchFailed;
-    kern<<<(unsigned)(p.B * p.H), THREADS, smem, stream>>>(p);
+    OutMaps omaps;
+    memset(&omaps, 0, sizeof(omaps));
+    if (Smem::TMA_OUT) {
+        void* outs[5] = {p.dr, p.dw, p.dk, p.da, p.db};
+        for (int i = 0; i < 5; ++i)
+            if (!encode_bthn_map(&omaps.m[i], outs[i], p.B, p.T, p.H, p.st)) return kLaunchFailed;
+    }
+    kern<<<(unsigned)(p.B * p.H), THREADS, smem, stream>>>(p, omaps);
     if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
     if (LN) {
         const long long n3 = 3 * p.H * N;
