@@ -30,6 +30,7 @@
 // Stage C (contractions over the value index, warp owns 16 key columns): the four score
 // gradients and DA, DQ, DB, DK with S0 and dSf read from shared memory.
 #include <cuda.h>
+#include <cstddef>
 #include <cstring>
 
 #include "wkv7_kernels.h"
@@ -77,20 +78,27 @@ template <typename IoT, int PREC, bool LN> struct BwdSmem {
     static constexpr int SCRATCH_FLOATS = WARPS * L * Lay::YS * (int)sizeof(IoT) / 4 + WARPS * L * 5;
     static constexpr int SGRAD_FLOATS = 4 * L * SCS > SCRATCH_FLOATS ? 4 * L * SCS : SCRATCH_FLOATS;
     alignas(16) float sgrad[SGRAD_FLOATS];  // score gradient i at sgrad + i * L * SCS
-    alignas(16) float Ut[L * OPS], Dt[L * OPS];  // U and dabu as [time][value]
+    // attn_ln: Ut, Dt, Yt are dead between stage C and the next chunk's stage B and double as the output staging tiles
+    alignas(LN ? 1024 : 16) float Ut[L * OPS];  // U and dabu as [time][value]
+    alignas(16) float Dt[L * OPS];
     alignas(16) float Yt[LN ? L * OPS : 4];      // recurrence-output gradient as [time][value]
     alignas(16) float S0s[N * SS], dSs[N * SS];  // chunk-start state and dSf as [value][key]
     alignas(16) float fw[N];
     alignas(16) float Gp[2][WARPS][N];
-    // bf16 attn: the five [16 x 64] output tiles of a chunk, 128-byte rows with the 16-byte unit index XOR-ed
+    // bf16: the five [16 x 64] output tiles of a chunk, 128-byte rows with the 16-byte unit index XOR-ed
     // with (row % 8) (what a 128-byte-swizzle tensor map expects), stored by five bulk tensor copies per chunk
-    static constexpr bool TMA_OUT = sizeof(IoT) == 2 && !LN;
-    alignas(1024) unsigned char ostage[TMA_OUT ? 5 * 2048 : 16];
+    static constexpr bool TMA_OUT = sizeof(IoT) == 2;
+    alignas(TMA_OUT && !LN ? 1024 : 16) unsigned char ostage[TMA_OUT && !LN ? 5 * 2048 : 16];
+    __device__ __forceinline__ unsigned char* out_tiles() { return LN ? reinterpret_cast<unsigned char*>(Ut) : ostage; }
     alignas(16) float lnp[LN ? 3 * N : 4];
     float bdot[L], sbon[L];
 };
 static_assert(sizeof(BwdSmem<__nv_bfloat16, 1, false>) <= 115712, "bf16 backward must fit two CTAs per SM");
 static_assert(sizeof(BwdSmem<__nv_bfloat16, 1, true>) <= 115712, "bf16 attn_ln backward must fit two CTAs per SM");
+using BwdSmemLnBf16 = BwdSmem<__nv_bfloat16, 1, true>;
+static_assert(offsetof(BwdSmemLnBf16, Yt) - offsetof(BwdSmemLnBf16, Ut) == 2 * L * OPS * 4 && 3 * L * OPS * 4 >= 5 * 2048 &&
+                  offsetof(BwdSmemLnBf16, Ut) % 1024 == 0,
+              "attn_ln output staging tiles alias Ut, Dt, Yt");
 
 template <typename IoT> __device__ __forceinline__ float bst_elem(const unsigned char* tile, int row, int col) {
     return to_f32<IoT>(*reinterpret_cast<const IoT*>(tile + BwdLayout<IoT>::at(row, col)));
@@ -432,6 +440,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                     if (sizeof(IoT) == 4) dst[1] = src[1];
                     __syncwarp();
                 }
+                if (TMA_OUT) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // previous chunk's output tiles (in Ut, Dt, Yt) have been read
                 __syncthreads();  // (D2)
 #pragma unroll
                 for (int i4 = 0; i4 < 4; ++i4) {
@@ -591,7 +600,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
             }
         }
         TICK(6)
-        if (TMA_OUT) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // previous chunk's output tiles have been read
+        if (TMA_OUT && !LN) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // previous chunk's output tiles have been read
         __syncthreads();  // (C2) score gradients visible; S0s free
         TICK(7)
         if (c > 0) issue_s0(c - 1);
@@ -693,7 +702,6 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                 sm.Gp[(it & 1) ^ 1][0][key + 1] + sm.Gp[(it & 1) ^ 1][1][key + 1] + sm.Gp[(it & 1) ^ 1][2][key + 1] + sm.Gp[(it & 1) ^ 1][3][key + 1]);
 #pragma unroll
             for (int hrow = 0; hrow < 2; ++hrow) {
-                const int tq = g + 8 * hrow;
                 const float d0 = (x[hrow][0] - e2[hrow][0] + Gc.x) * lwv[hrow][0];
                 const float d1 = (x[hrow][1] - e2[hrow][1] + Gc.y) * lwv[hrow][1];
                 outv[1][nt][hrow][0] = d0; outv[1][nt][hrow][1] = d1;
@@ -710,7 +718,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                     for (int hrow = 0; hrow < 2; ++hrow) {
                         const int tq = g + 8 * hrow;
                         const __nv_bfloat162 v2 = __floats2bfloat162_rn(outv[ten][nt][hrow][0], outv[ten][nt][hrow][1]);
-                        *reinterpret_cast<__nv_bfloat162*>(sm.ostage + ten * 2048 + tq * 128 + ((((2 * warp + nt) ^ (tq & 7))) << 4) + 4 * t4) = v2;
+                        *reinterpret_cast<__nv_bfloat162*>(sm.out_tiles() + ten * 2048 + tq * 128 + ((((2 * warp + nt) ^ (tq & 7))) << 4) + 4 * t4) = v2;
                     }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         } else {
@@ -728,7 +736,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
 #pragma unroll
             for (int ten = 0; ten < 5; ++ten)
                 asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];"
-                             ::"l"(&omaps.m[ten]), "r"(0), "r"((int)hi), "r"(c * L), "r"((int)bi), "r"(smem_u32(sm.ostage + ten * 2048)) : "memory");
+                             ::"l"(&omaps.m[ten]), "r"(0), "r"((int)hi), "r"(c * L), "r"((int)bi), "r"(smem_u32(sm.out_tiles() + ten * 2048)) : "memory");
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
         TICK(9)
