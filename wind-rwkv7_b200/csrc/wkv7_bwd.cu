@@ -41,7 +41,8 @@
 namespace wkv7 {
 
 // Tensor maps of the five [time x key] outputs (dq, dw, dk, da, db) for the bulk-store epilogue.
-struct alignas(64) OutMaps { CUtensorMap m[5]; };
+// ck: the checkpoint states, for the bulk tensor loads of the chunk-start state.
+struct alignas(64) OutMaps { CUtensorMap m[5]; CUtensorMap ck; };
 
 constexpr int SS = N + 8;  // row stride (floats) of the [value][key] state buffers
 // All fp32 tiles of this kernel (operands, scores, score gradients, U, dabu, the two state buffers)
@@ -82,7 +83,13 @@ template <typename IoT, int PREC, bool LN> struct BwdSmem {
     alignas(LN ? 1024 : 16) float Ut[L * OPS];  // U and dabu as [time][value]
     alignas(16) float Dt[L * OPS];
     alignas(16) float Yt[LN ? L * OPS : 4];      // recurrence-output gradient as [time][value]
-    alignas(16) float S0s[N * SS], dSs[N * SS];  // chunk-start state and dSf as [value][key]
+    // Chunk-start state [value][key], filled by two bulk tensor loads per chunk: rows with (row & 4) == 0 form a dense
+    // block of 32 rows x 72 floats (64 values, 8 floats of fill), the other rows a second block whose rows start with
+    // the 8 floats of fill (the load starts at column -8).  See s0_at().
+    alignas(128) float S0s[N * SS];
+    alignas(16) float dSs[N * SS];  // dSf as [value][key], column swizzle 1
+    alignas(8) uint64_t s0_bar;     // completion of the state loads
+    volatile int abort;             // set when a bounded wait gave up
     alignas(16) float fw[N];
     alignas(16) float Gp[2][WARPS][N];
     // bf16: the five [16 x 64] output tiles of a chunk, 128-byte rows with the 16-byte unit index XOR-ed
@@ -170,6 +177,36 @@ __device__ __forceinline__ void store_quad(float* row, float a0, float a1, float
     *reinterpret_cast<float4*>(row + 8 * (t4 & 1) + 4 * (t4 >> 1)) = v;
 }
 
+// Offset of element (row = value, col = key) of the chunk-start state in shared memory.  With the 72-float row pitch
+// (8 banks) both access patterns of the tensor-core fragments are free of bank conflicts: lanes over rows g = 0..3 or
+// 4..7 of one block with 8-byte loads, and lanes over rows 0,2,4,6 (or 1,3,5,7) x 8 columns, where the second block's
+// shift by 8 floats separates rows r and r + 4.
+constexpr int S0_BLK = 32 * SS;
+__device__ __forceinline__ int s0_at(int row, int col) {
+    return ((row >> 2) & 1) * (S0_BLK + 8) + (((row >> 3) << 2) | (row & 3)) * SS + col;
+}
+static_assert(SS == N + 8, "the state loads copy boxes of N + 8 floats per row");
+
+// Waits for a phase of the state-load barrier; gives up after about 2^28 clocks (sets the abort flag and the device
+// status, after which every later wait returns at once) so that a lost copy cannot hang the GPU.
+__device__ __forceinline__ void s0_wait(uint64_t* bar, uint32_t parity, volatile int* abort, int* status) {
+    const uint32_t addr = smem_u32(bar);
+    long long start = 0;
+    for (int spin = 0;; ++spin) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred P;\nmbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\nselp.u32 %0, 1, 0, P;\n}\n"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return;
+        if (*abort) return;
+        if (spin == 0) start = clock64();
+        else if ((spin & 63) == 0 && clock64() - start > (1LL << 28)) {
+            *abort = 1;
+            if (status) atomicExch(status, (int)kDeviceTimeout);
+            return;
+        }
+    }
+}
+
 template <typename IoT, int PREC, bool LN>
 __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __grid_constant__ OutMaps omaps) {
     using Lay = BwdLayout<IoT>;
@@ -204,6 +241,11 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
     float dlnw_acc[2] = {0.f, 0.f}, dlnb_acc[2] = {0.f, 0.f}, dbon_acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
     // Carried decay term for the last chunk: sum_i dsT[i,:] * sT[i,:] (zero without dsT).
     for (int i = tid; i < WARPS * N; i += THREADS) sm.Gp[1][i / N][i % N] = 0.f;
+    if (tid == 0) {
+        sm.abort = 0;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&sm.s0_bar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     __syncthreads();
     if (p.dsT && p.sT && tid < N) {
         const float* d = p.dsT + bh * N * N;
@@ -236,9 +278,16 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
     // forward left there so that the scores and the triangular inverse are not rebuilt here
     auto issue_s0 = [&](int c) {
         const float* rec = ckpt + (long long)c * CK_FLOATS;
-        for (int i = tid; i < N * (N / 4); i += THREADS) {
-            const int row = i / (N / 4), ch = i % (N / 4);
-            cp_async16(sm.S0s + row * SS + xcol<1>(row, ch * 4), rec + CK_STATE + row * N + ch * 4);
+        if (tid == 0) {
+            // two boxes of [8][4 rows][72 floats]: rows 8a + b and rows 8a + 4 + b (a < 8, b < 4); the second starts at
+            // column -8, so that its fill comes first in each row
+            const uint32_t bar = smem_u32(&sm.s0_bar);
+            const int record = (int)(bh * nchunks + c);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(N * SS * 4)) : "memory");
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk)
+                asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+                             ::"r"(smem_u32(sm.S0s + blk * S0_BLK)), "l"(&omaps.ck), "r"(bar), "r"(-8 * blk), "r"(0), "r"(blk), "r"(0), "r"(record) : "memory");
         }
         // the matrices are read in the order they are stored (the forward's tile layout: consecutive 16-byte pieces
         // walk 8 rows of one 4-column chunk), so that a warp reads whole 128-byte lines
@@ -282,6 +331,10 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
 #else
 #define TICK(i)
 #endif
+    // this thread's offsets into the chunk-start state: rows 16*warp + g (and + 8) at columns 2*t4 + 8*block, and
+    // rows 2*t4 (and + 1) + 8*block at column 16*warp + g
+    const float* const s0_mk = sm.S0s + s0_at(16 * warp + g, 2 * t4);
+    const float* const s0_kn = sm.S0s + s0_at(2 * t4, 16 * warp + g);
     for (int it = 0; it < nchunks; ++it) {
         const int c = nchunks - 1 - it;
         const int vs = it & 1;
@@ -306,6 +359,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
         TICK(0)
         __syncthreads();  // (A)
         TICK(1)
+        s0_wait(&sm.s0_bar, it & 1, &sm.abort, p.status);  // this chunk's start state has landed
 
         if (c > 0) {
             issue_in(c - 1);
@@ -327,7 +381,11 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
             float X[2][4] = {}, Y[2][4] = {};
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
-                FragA<PREC> a = fragA_mk<PREC, true, 1>(sm.S0s, SS, 16 * warp, 8 * kk, g, t4);
+                FragA<PREC> a;
+                {
+                    const float2 lo = *reinterpret_cast<const float2*>(s0_mk + 8 * kk), hi2 = *reinterpret_cast<const float2*>(s0_mk + 4 * SS + 8 * kk);
+                    a.x[0].setr(lo.x); a.x[1].setr(hi2.x); a.x[2].setr(lo.y); a.x[3].setr(hi2.y);
+                }
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
                     mma<PREC>(X[nt], a, fragB_nk<PREC, true, 1>(sm.wa, OPS, 8 * nt, 8 * kk, g, t4));
@@ -548,8 +606,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                 mma<PREC>(dS[nt], dyf[kk], fragB_kn<PREC, true, 1>(sm.wq, OPS, 8 * nt, 8 * kk, g, t4));
                 mma<PREC>(dS[nt], dbf[kk], fragB_kn<PREC, true, 1>(sm.wa, OPS, 8 * nt, 8 * kk, g, t4));
             }
-            const float2 lo = *reinterpret_cast<const float2*>(sm.S0s + (16 * warp + g) * SS + xcol<1>(g, 8 * nt + 2 * t4));
-            const float2 hi2 = *reinterpret_cast<const float2*>(sm.S0s + (16 * warp + g + 8) * SS + xcol<1>(g, 8 * nt + 2 * t4));
+            const float2 lo = *reinterpret_cast<const float2*>(s0_mk + 8 * nt);
+            const float2 hi2 = *reinterpret_cast<const float2*>(s0_mk + 4 * SS + 8 * nt);
             float gx = dS[nt][0] * lo.x + dS[nt][2] * hi2.x, gy2 = dS[nt][1] * lo.y + dS[nt][3] * hi2.y;
 #pragma unroll
             for (int m = 4; m <= 16; m <<= 1) {
@@ -581,7 +639,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                     FragB<PREC> bsc = (warp >> 1) ? fragB_nk<PREC, true, 1>(sm.Ut, OPS, 8 * nt, 8 * kk, g, t4)
                                                   : fragB_nk_st<IoT, PREC>(vt, 8 * nt, 8 * kk, g, t4);
                     mma<PREC>(d[nt], strict ? aD : aY, bsc);
-                    FragB<PREC> bS = fragB_kn<PREC, true, 1>(sm.S0s, SS, 16 * warp + 8 * nt, 8 * kk, g, t4);
+                    FragB<PREC> bS;
+                    bS.x[0].setr(s0_kn[4 * kk * SS + 8 * nt]); bS.x[1].setr(s0_kn[(4 * kk + 1) * SS + 8 * nt]);
                     FragB<PREC> bD = fragB_kn<PREC, true, 1>(sm.dSs, SS, 16 * warp + 8 * nt, 8 * kk, g, t4);
                     mma<PREC>(DA[nt], aD, bS);
                     mma<PREC>(DQ[nt], aY, bS);
@@ -795,13 +854,30 @@ __global__ void reduce_dparams_kernel(const float* __restrict__ ws, float* __res
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static bool encode_bthn_map(CUtensorMap* m, void* base, long long B, long long T, long long H, const Strides& st) {
+static EncodeTiledFn encode_tiled_fn() {
     static EncodeTiledFn fn = [] {
         void* f = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) f = nullptr;
         return reinterpret_cast<EncodeTiledFn>(f);
     }();
+    return fn;
+}
+// Tensor map over the states of `records` checkpoint records (fp32 [64][64] at the start of each record of CK_FLOATS
+// floats), seen as [record][a = row / 8][row bit 2][b = row % 4][column]; a box is the 32 rows of one value of bit 2,
+// N + 8 floats wide (the part outside the 64 columns reads as zero).
+static bool encode_ckpt_state_map(CUtensorMap* m, const float* ckpt, long long records) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[5] = {(cuuint64_t)N, 4, 2, 8, (cuuint64_t)records};
+    const cuuint64_t strides[4] = {N * 4, 4 * N * 4, 8 * N * 4, (cuuint64_t)CK_FLOATS * 4};
+    const cuuint32_t box[5] = {(cuuint32_t)SS, 4, 1, 8, 1};
+    const cuuint32_t es[5] = {1, 1, 1, 1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float*>(ckpt + CK_STATE), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+static bool encode_bthn_map(CUtensorMap* m, void* base, long long B, long long T, long long H, const Strides& st) {
+    EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     const cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
     // a dimension of extent 1 may carry any stride; give it a valid (16-byte multiple, non-zero) one
@@ -826,6 +902,7 @@ template <typename IoT, int PREC, bool LN> static int launch_bwd_t(const BwdPara
         for (int i = 0; i < 5; ++i)
             if (!encode_bthn_map(&omaps.m[i], outs[i], p.B, p.T, p.H, p.st)) return kLaunchFailed;
     }
+    if (p.T >= L && !encode_ckpt_state_map(&omaps.ck, p.ckpt, p.B * p.H * (p.T / L))) return kLaunchFailed;
     kern<<<(unsigned)(p.B * p.H), THREADS, smem, stream>>>(p, omaps);
     if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
     if (LN) {
