@@ -359,7 +359,6 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
         TICK(0)
         __syncthreads();  // (A)
         TICK(1)
-        s0_wait(&sm.s0_bar, it & 1, &sm.abort, p.status);  // this chunk's start state has landed
 
         if (c > 0) {
             issue_in(c - 1);
@@ -375,6 +374,36 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
             vf[kk] = fragA_km_st<IoT, PREC>(vt, 16 * warp, 8 * kk, g, t4);
             if (!LN) dyf[kk] = fragA_km_st<IoT, PREC>(dyt, 16 * warp, 8 * kk, g, t4);
         }
+        // dS <- dSf = dS * fw, then du and the first part of dV.  None of this needs the chunk-start state, so the
+        // attn kernel does it before it waits for the state's copy; attn_ln needs the state first (for dy).
+        float du[2][4] = {}, dV[2][4] = {};
+        auto du_dv = [&]() {
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                const float2 f = *reinterpret_cast<const float2*>(sm.fw + 8 * nt + 2 * t4);
+                dS[nt][0] *= f.x; dS[nt][1] *= f.y; dS[nt][2] *= f.x; dS[nt][3] *= f.y;
+            }
+#pragma unroll
+            for (int sb = 0; sb < 2; ++sb)
+#pragma unroll
+                for (int tb = sb; tb < 2; ++tb) {
+                    mma<PREC>(du[sb], dyf[tb], fragB_kn<PREC, true, 1>(sm.QB, SCS, 8 * sb, 8 * tb, g, t4));
+                    mma<PREC>(dV[sb], dyf[tb], fragB_kn<PREC, true, 1>(sm.QK, SCS, 8 * sb, 8 * tb, g, t4));
+                }
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+                FragA<PREC> a = fragA_from_acc<PREC>(dS[kk]);
+#pragma unroll
+                for (int sb = 0; sb < 2; ++sb) {
+                    mma<PREC>(du[sb], a, fragB_nk<PREC, true, 1>(sm.bwi, OPS, 8 * sb, 8 * kk, g, t4));
+                    mma<PREC>(dV[sb], a, fragB_nk<PREC, true, 1>(sm.kwi, OPS, 8 * sb, 8 * kk, g, t4));
+                }
+            }
+        };
+        if (!LN) du_dv();
+        TICK(2)
+        s0_wait(&sm.s0_bar, it & 1, &sm.abort, p.status);  // this chunk's start state has landed
+        TICK(3)
         float U[2][4] = {};
         float dvx[2][4] = {};  // LN: bonus-term contribution to dv
         {
@@ -528,29 +557,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                 }
             }
         }
-        // dS <- dSf = dS * fw
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-            const float2 f = *reinterpret_cast<const float2*>(sm.fw + 8 * nt + 2 * t4);
-            dS[nt][0] *= f.x; dS[nt][1] *= f.y; dS[nt][2] *= f.x; dS[nt][3] *= f.y;
-        }
-        float du[2][4] = {}, dV[2][4] = {};
-#pragma unroll
-        for (int sb = 0; sb < 2; ++sb)
-#pragma unroll
-            for (int tb = sb; tb < 2; ++tb) {
-                mma<PREC>(du[sb], dyf[tb], fragB_kn<PREC, true, 1>(sm.QB, SCS, 8 * sb, 8 * tb, g, t4));
-                mma<PREC>(dV[sb], dyf[tb], fragB_kn<PREC, true, 1>(sm.QK, SCS, 8 * sb, 8 * tb, g, t4));
-            }
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-            FragA<PREC> a = fragA_from_acc<PREC>(dS[kk]);
-#pragma unroll
-            for (int sb = 0; sb < 2; ++sb) {
-                mma<PREC>(du[sb], a, fragB_nk<PREC, true, 1>(sm.bwi, OPS, 8 * sb, 8 * kk, g, t4));
-                mma<PREC>(dV[sb], a, fragB_nk<PREC, true, 1>(sm.kwi, OPS, 8 * sb, 8 * kk, g, t4));
-            }
-        }
+        if (LN) du_dv();
         float dabu[2][4] = {};
         {
             FragA<PREC> da2[2] = {fragA_from_acc<PREC>(du[0]), fragA_from_acc<PREC>(du[1])};
@@ -803,7 +810,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
     if (TMA_OUT) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory must outlive the last stores
 #ifdef WKV7_TIMING
     if (blockIdx.x == 0 && lane == 0)
-        printf("bwd warp %d: P1 %lld | syncA %lld | P2P3 %lld | syncB %lld | stageB %lld | syncC1 %lld | Ca %lld | syncC2 %lld | Cb %lld | epi+syncE %lld\n", warp,
+        printf("bwd warp %d: P1 %lld | syncA %lld | du/dV %lld | s0 wait %lld | stageB %lld | syncC1 %lld | Ca %lld | syncC2 %lld | Cb %lld | epi+syncE %lld\n", warp,
                tacc[0] / nchunks, tacc[1] / nchunks, tacc[2] / nchunks, tacc[3] / nchunks, tacc[4] / nchunks, tacc[5] / nchunks, tacc[6] / nchunks,
                tacc[7] / nchunks, tacc[8] / nchunks, tacc[9] / nchunks);
 #endif
