@@ -24,8 +24,8 @@
 // chunk is computed into registers while the chain works on its previous chunk, and the read-back of
 // that chunk's results happens just before the operand tiles are overwritten.
 //
-// Warp roles (128 (G+1) threads): warps 0..4G-1 are the preparation groups, warp 4G issues the chain,
-// the remaining three warps of its warp group only exist so that setmaxnreg can be used: the chain
+// Warp roles (128 (G+1) threads): warps 0..4G-1 are the preparation groups, warp 4G+3 issues the chain,
+// the other three warps of its warp group only exist so that setmaxnreg can be used: the chain
 // warp group shrinks to 32 registers per thread and the preparation warps grow to 112 (a kernel-wide
 // 96, which is all that 20 warps leave, makes the decay scan spill, and the spills cost more than
 // the whole scan).  The chain thread waits for "operands of chunk c ready" and "results of chunk c-2
@@ -325,7 +325,10 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
     if (warp >= 4 * G) {
         // ------------------------------ chain warp group -----------------------------------------
         if (G == 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(CHAIN_REGS));
-        if (warp == 4 * G && elect_one()) {
+        // The chain is issued by the LAST warp of its warp group: warp 4G + 3 shares its scheduler (warp index mod 4) with
+        // warp 3 of every preparation group, which has the least to do (no score read-back, no inverse); on the
+        // scheduler of the groups' warps 0 the chain's instructions waited longer for issue slots (forward +5 %).
+        if (warp == 4 * G + 3 && elect_one()) {
             const uint32_t sb = smem_u32(sm);
             uint32_t hop_phase = 0;
 #ifdef WKV7_TIMING
