@@ -606,22 +606,40 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
             sm.Dt[tq * OPS + c1] = pre<PREC>(dabu[nt][2]); sm.Dt[(tq + 1) * OPS + c1] = pre<PREC>(dabu[nt][3]);
         }
         // dS0 = dSf + dY^T wq + dabu^T wa ; carried decay term sum_i dS0[i,:] S0[i,:]
+        {
+            float gp[16];  // this thread's two rows: [2 * nt + e] for key column 8 * nt + 2 * t4 + e
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
+            for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
-            for (int kk = 0; kk < 2; ++kk) {
-                mma<PREC>(dS[nt], dyf[kk], fragB_kn<PREC, true, 1>(sm.wq, OPS, 8 * nt, 8 * kk, g, t4));
-                mma<PREC>(dS[nt], dbf[kk], fragB_kn<PREC, true, 1>(sm.wa, OPS, 8 * nt, 8 * kk, g, t4));
+                for (int kk = 0; kk < 2; ++kk) {
+                    mma<PREC>(dS[nt], dyf[kk], fragB_kn<PREC, true, 1>(sm.wq, OPS, 8 * nt, 8 * kk, g, t4));
+                    mma<PREC>(dS[nt], dbf[kk], fragB_kn<PREC, true, 1>(sm.wa, OPS, 8 * nt, 8 * kk, g, t4));
+                }
+                const float2 lo = *reinterpret_cast<const float2*>(s0_mk + 8 * nt);
+                const float2 hi2 = *reinterpret_cast<const float2*>(s0_mk + 4 * SS + 8 * nt);
+                gp[2 * nt] = dS[nt][0] * lo.x + dS[nt][2] * hi2.x;
+                gp[2 * nt + 1] = dS[nt][1] * lo.y + dS[nt][3] * hi2.y;
             }
-            const float2 lo = *reinterpret_cast<const float2*>(s0_mk + 8 * nt);
-            const float2 hi2 = *reinterpret_cast<const float2*>(s0_mk + 4 * SS + 8 * nt);
-            float gx = dS[nt][0] * lo.x + dS[nt][2] * hi2.x, gy2 = dS[nt][1] * lo.y + dS[nt][3] * hi2.y;
+            // Sum over the eight row lanes g as a reduce-scatter: every step halves the values a lane carries (8 + 4 + 2
+            // shuffles instead of 3 per value), and lane g ends with the two sums of tile nt = bit-reversed g.
+            const bool b0 = g & 1, b1 = g & 2, b2 = g & 4;
 #pragma unroll
-            for (int m = 4; m <= 16; m <<= 1) {
-                gx += __shfl_xor_sync(0xffffffffu, gx, m);
-                gy2 += __shfl_xor_sync(0xffffffffu, gy2, m);
+            for (int i = 0; i < 8; ++i) {
+                const float send = b0 ? gp[i] : gp[i + 8], keep = b0 ? gp[i + 8] : gp[i];
+                gp[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
             }
-            if (g == 0) *reinterpret_cast<float2*>(&sm.Gp[it & 1][warp][8 * nt + 2 * t4]) = make_float2(gx, gy2);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float send = b1 ? gp[i] : gp[i + 4], keep = b1 ? gp[i + 4] : gp[i];
+                gp[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float send = b2 ? gp[i] : gp[i + 2], keep = b2 ? gp[i + 2] : gp[i];
+                gp[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+            }
+            const int nt_own = (b2 ? 1 : 0) + (b1 ? 2 : 0) + (b0 ? 4 : 0);
+            *reinterpret_cast<float2*>(&sm.Gp[it & 1][warp][8 * nt_own + 2 * t4]) = make_float2(gp[0], gp[1]);
         }
         TICK(4)
         __syncthreads();  // (C1)
