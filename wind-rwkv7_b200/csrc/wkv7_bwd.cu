@@ -716,7 +716,6 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
         for (int nt = 0; nt < 2; ++nt) {
             const int key = 16 * warp + 8 * nt + 2 * t4;
             float x[2][2], e2[2][2], lwv[2][2];  // [row half][column]
-            float incl_lo[2] = {1.f, 1.f};  // P_t of this thread's first-half row, per column
 #pragma unroll
             for (int hrow = 0; hrow < 2; ++hrow) {
                 const int tq = g + 8 * hrow;
@@ -741,13 +740,9 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                     const int i = e + 2 * hrow;
                     const float incl = exp_p<PREC>(fmaxf(cuv[e], -80.f));
                     const float inv = rcp_p<PREC>(incl);
-                    // P_{t-1} is P_t of the row above, which the lane four below holds (row 7 for
-                    // this thread's row 8 sits in lane 28 + t4, first half); row -1 is 1.
-                    const float up_same = __shfl_up_sync(0xffffffffu, incl, 4);
-                    const float up_lo7 = __shfl_sync(0xffffffffu, incl_lo[e], 28 + t4);
-                    const float non = PREC == 3 ? exp_p<PREC>(cuv[e] - lwa[e])
-                                                : (g > 0 ? up_same : (hrow == 0 ? 1.f : up_lo7));
-                    if (hrow == 0) incl_lo[e] = incl;
+                    // P_{t-1} = exp(cum_{t-1}) with cum_{t-1} = cum_t - lw_t (0 for the first row): an exponential on the idle
+                    // special-function unit instead of two shuffles for the row above
+                    const float non = exp_p<PREC>(fmaxf(cuv[e] - lwa[e], -80.f));
                     o_a[e] = non * DA[nt][i];
                     o_q[e] = incl * DQ[nt][i];
                     o_b[e] = inv * DB[nt][i];

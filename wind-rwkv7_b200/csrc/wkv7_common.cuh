@@ -265,16 +265,16 @@ __device__ __forceinline__ void decay_scan(const unsigned char* tq, const unsign
             const float up = __shfl_up_sync(0xffffffffu, cum[i], d, 16);
             if (row >= d) cum[i] += up;
         }
-    // P_t from one exp (argument clamped so that P_t and 1/P_t stay finite), 1/P_t from a
-    // Newton reciprocal, P_{t-1} from the row above.
+    // P_t from one exp (argument clamped so that P_t and 1/P_t stay finite), 1/P_t from a reciprocal.
     float o[4][8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const float cc = fmaxf(cum[i], -80.f);
         const float incl = exp_p<PREC>(cc);
         const float inv = rcp_p<PREC>(incl);
-        const float up = __shfl_up_sync(0xffffffffu, incl, 1, 16);
-        const float non = row == 0 ? 1.f : up;
+        // P_{t-1} = exp(cum_t - lw_t) (row 0: exp(0) = 1): one more exponential on the idle special-function unit is
+        // cheaper here than fetching the row above with a shuffle
+        const float non = exp_p<PREC>(fmaxf(cum[i] - lw[i], -80.f));
         o[0][i] = pre<PREC>(q[i] * incl);
         o[1][i] = pre<PREC>(a[i] * non);
         o[2][i] = pre<PREC>(k[i] * inv);

@@ -590,6 +590,9 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                 // log2 of the per-step decay: -exp(w) * log2(e); running sum along the 16 time rows
 #pragma unroll
                 for (int i = 0; i < 8; ++i) cum[i] = ex2_approx(cum[i] * 1.4426950408889634f) * -1.4426950408889634f;
+                float step[8];  // this row's own log2 decay: P_{t-1} = 2^(cum_t - step_t), cheaper than a shuffle for the row above
+#pragma unroll
+                for (int i = 0; i < 8; ++i) step[i] = cum[i];
 #pragma unroll
                 for (int d = 1; d < 16; d <<= 1)
 #pragma unroll
@@ -602,8 +605,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                     const float cc = fmaxf(cum[i], -115.f);  // keeps P_t and 1/P_t finite (2^-115 ~ e^-80)
                     const float incl = ex2_approx(cc);
                     const float inv = ex2_approx(-cc);
-                    const float up = __shfl_up_sync(0xffffffffu, incl, 1, 16);
-                    const float non = row == 0 ? 1.f : up;
+                    const float non = ex2_approx(fmaxf(cum[i] - step[i], -115.f));
                     const float fw = __shfl_sync(0xffffffffu, incl, 15, 16);
                     o[0][i] = q[i] * incl;   // wq
                     o[1][i] = a[i] * non;    // wa
