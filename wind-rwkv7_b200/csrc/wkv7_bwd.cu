@@ -377,6 +377,9 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
         // dS <- dSf = dS * fw, then du and the first part of dV.  None of this needs the chunk-start state, so the
         // attn kernel does it before it waits for the state's copy; attn_ln needs the state first (for dy).
         float du[2][4] = {}, dV[2][4] = {};
+        float X[2][4] = {};
+        if (!LN) s0_wait(&sm.s0_bar, it & 1, &sm.abort, p.status);  // this chunk's start state has landed
+        // attn: the X = S0 wa^T products ride in the same loop, six independent accumulator chains instead of four, then two
         auto du_dv = [&]() {
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
@@ -398,18 +401,25 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                     mma<PREC>(du[sb], a, fragB_nk<PREC, true, 1>(sm.bwi, OPS, 8 * sb, 8 * kk, g, t4));
                     mma<PREC>(dV[sb], a, fragB_nk<PREC, true, 1>(sm.kwi, OPS, 8 * sb, 8 * kk, g, t4));
                 }
+                if (!LN) {
+                    FragA<PREC> a0;
+                    const float2 lo = *reinterpret_cast<const float2*>(s0_mk + 8 * kk), hi2 = *reinterpret_cast<const float2*>(s0_mk + 4 * SS + 8 * kk);
+                    a0.x[0].setr(lo.x); a0.x[1].setr(hi2.x); a0.x[2].setr(lo.y); a0.x[3].setr(hi2.y);
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt) mma<PREC>(X[nt], a0, fragB_nk<PREC, true, 1>(sm.wa, OPS, 8 * nt, 8 * kk, g, t4));
+                }
             }
         };
         if (!LN) du_dv();
         TICK(2)
-        s0_wait(&sm.s0_bar, it & 1, &sm.abort, p.status);  // this chunk's start state has landed
+        if (LN) s0_wait(&sm.s0_bar, it & 1, &sm.abort, p.status);
         TICK(3)
         float U[2][4] = {};
         float dvx[2][4] = {};  // LN: bonus-term contribution to dv
         {
-            float X[2][4] = {}, Y[2][4] = {};
+            float Y[2][4] = {};
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {
+            for (int kk = 0; kk < (LN ? 8 : 0); ++kk) {
                 FragA<PREC> a;
                 {
                     const float2 lo = *reinterpret_cast<const float2*>(s0_mk + 8 * kk), hi2 = *reinterpret_cast<const float2*>(s0_mk + 4 * SS + 8 * kk);
