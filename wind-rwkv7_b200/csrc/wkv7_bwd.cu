@@ -451,29 +451,45 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
 #pragma unroll
                     for (int kk = 0; kk <= nt; ++kk) mma<PREC>(Y[nt], ua0[kk], fragB_nk<PREC, true, 1>(sm.QB, SCS, 8 * nt, 8 * kk, g, t4));
                 // statistics: per-warp mean and centred sum of squares over 16 rows, merged below
+                // (a thread's four time steps i4 = 2 * nt + e go through every shuffle level together; sums that only one
+                // lane has to store are formed as a reduce-scatter over the row lanes, which halves the values per level)
+                const bool b0 = g & 1, b1 = g & 2, b2 = g & 4;
+                {
+                    float sy[4], q2[4];
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
+                    for (int i4 = 0; i4 < 4; ++i4) sy[i4] = Y[i4 >> 1][i4 & 1] + Y[i4 >> 1][(i4 & 1) + 2];
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        float sy = Y[nt][e] + Y[nt][e + 2];
-                        sy += __shfl_xor_sync(0xffffffffu, sy, 4);
-                        sy += __shfl_xor_sync(0xffffffffu, sy, 8);
-                        sy += __shfl_xor_sync(0xffffffffu, sy, 16);
-                        const float mu = sy * (1.f / 16.f);
-                        const float d0 = Y[nt][e] - mu, d1 = Y[nt][e + 2] - mu;
-                        float q2 = d0 * d0 + d1 * d1;
-                        q2 += __shfl_xor_sync(0xffffffffu, q2, 4);
-                        q2 += __shfl_xor_sync(0xffffffffu, q2, 8);
-                        q2 += __shfl_xor_sync(0xffffffffu, q2, 16);
-                        if (g == 0) {
-                            const int tq = 8 * nt + 2 * t4 + e;
-                            red[(warp * L + tq) * 2 + 0] = mu;
-                            red[(warp * L + tq) * 2 + 1] = q2;
-                        }
+                    for (int m = 4; m <= 16; m <<= 1)
+#pragma unroll
+                        for (int i4 = 0; i4 < 4; ++i4) sy[i4] += __shfl_xor_sync(0xffffffffu, sy[i4], m);
+#pragma unroll
+                    for (int i4 = 0; i4 < 4; ++i4) {
+                        sy[i4] *= (1.f / 16.f);  // the warp's mean
+                        const float d0 = Y[i4 >> 1][i4 & 1] - sy[i4], d1 = Y[i4 >> 1][(i4 & 1) + 2] - sy[i4];
+                        q2[i4] = d0 * d0 + d1 * d1;
                     }
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const float send = b0 ? q2[i] : q2[i + 2], keep = b0 ? q2[i + 2] : q2[i];
+                        q2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+                    }
+                    {
+                        const float send = b1 ? q2[0] : q2[1], keep = b1 ? q2[1] : q2[0];
+                        q2[0] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+                    }
+                    q2[0] += __shfl_xor_sync(0xffffffffu, q2[0], 16);
+                    if (!b2) {  // this lane holds time step i4 = 2 * b0 + b1
+                        const int tq = 8 * (b0 ? 1 : 0) + 2 * t4 + (b1 ? 1 : 0);
+                        red[(warp * L + tq) * 2 + 0] = b0 ? (b1 ? sy[3] : sy[2]) : (b1 ? sy[1] : sy[0]);
+                        red[(warp * L + tq) * 2 + 1] = q2[0];
+                    }
+                }
                 __syncthreads();  // (D1)
                 const unsigned char* gt = sm.st_g[LN ? vs : 0];
                 float xh[2][4], dxh[2][4], rstd_t[4];
+                float asum[16];  // [a1 | a2 | a3 | unused][i4]
+#pragma unroll
+                for (int i4 = 0; i4 < 4; ++i4) asum[12 + i4] = 0.f;
 #pragma unroll
                 for (int i4 = 0; i4 < 4; ++i4) {
                     const int nt = i4 >> 1, e = i4 & 1, tq = 8 * nt + 2 * t4 + e;
@@ -506,16 +522,30 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                         dxh[nt][i] = dx;
                         a1 += dx; a2 += dx * x; a3 += dz * ve;
                     }
+                    asum[i4] = a1; asum[4 + i4] = a2; asum[8 + i4] = a3;
+                }
+                {
 #pragma unroll
-                    for (int m = 4; m <= 16; m <<= 1) {
-                        a1 += __shfl_xor_sync(0xffffffffu, a1, m);
-                        a2 += __shfl_xor_sync(0xffffffffu, a2, m);
-                        a3 += __shfl_xor_sync(0xffffffffu, a3, m);
+                    for (int i = 0; i < 8; ++i) {
+                        const float send = b0 ? asum[i] : asum[i + 8], keep = b0 ? asum[i + 8] : asum[i];
+                        asum[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
                     }
-                    if (g == 0) {
-                        red2[(warp * L + tq) * 3 + 0] = a1;
-                        red2[(warp * L + tq) * 3 + 1] = a2;
-                        red2[(warp * L + tq) * 3 + 2] = a3;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float send = b1 ? asum[i] : asum[i + 4], keep = b1 ? asum[i + 4] : asum[i];
+                        asum[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const float send = b2 ? asum[i] : asum[i + 2], keep = b2 ? asum[i + 2] : asum[i];
+                        asum[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+                    }
+                    // the lane now holds entries 8 * b0 + 4 * b1 + 2 * b2 + {0, 1}: sum number 2 * b0 + b1 of time steps i4 = 2 * b2 + {0, 1}
+                    const int which = (b0 ? 2 : 0) + (b1 ? 1 : 0);
+                    if (which < 3) {
+                        const int tq = 8 * (b2 ? 1 : 0) + 2 * t4;
+                        red2[(warp * L + tq) * 3 + which] = asum[0];
+                        red2[(warp * L + tq + 1) * 3 + which] = asum[1];
                     }
                 }
                 // dg out through the per-warp scratch tile
