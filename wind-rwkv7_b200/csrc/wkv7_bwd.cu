@@ -42,7 +42,7 @@ namespace wkv7 {
 
 // Tensor maps of the five [time x key] outputs (dq, dw, dk, da, db) for the bulk-store epilogue.
 // ck: the checkpoint states, for the bulk tensor loads of the chunk-start state.
-struct alignas(64) OutMaps { CUtensorMap m[5]; CUtensorMap ck; };
+struct alignas(64) OutMaps { CUtensorMap m[6]; CUtensorMap ck; };  // m[5]: dv (attn only)
 
 constexpr int SS = N + 8;  // row stride (floats) of the [value][key] state buffers
 // All fp32 tiles of this kernel (operands, scores, score gradients, U, dabu, the two state buffers)
@@ -95,7 +95,8 @@ template <typename IoT, int PREC, bool LN> struct BwdSmem {
     // bf16: the five [16 x 64] output tiles of a chunk, 128-byte rows with the 16-byte unit index XOR-ed
     // with (row % 8) (what a 128-byte-swizzle tensor map expects), stored by five bulk tensor copies per chunk
     static constexpr bool TMA_OUT = sizeof(IoT) == 2;
-    alignas(TMA_OUT && !LN ? 1024 : 16) unsigned char ostage[TMA_OUT && !LN ? 5 * 2048 : 16];
+    // (attn: a sixth tile carries dv, which is formed one stage earlier)
+    alignas(TMA_OUT && !LN ? 1024 : 16) unsigned char ostage[TMA_OUT && !LN ? 6 * 2048 : 16];
     __device__ __forceinline__ unsigned char* out_tiles() { return LN ? reinterpret_cast<unsigned char*>(Ut) : ostage; }
     alignas(16) float lnp[LN ? 3 * N : 4];
     float bdot[L], sbon[L];
@@ -357,6 +358,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
             }
         }
         TICK(0)
+        if (TMA_OUT && !LN) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // previous chunk's output tiles have been read
         __syncthreads();  // (A)
         TICK(1)
 
@@ -612,8 +614,17 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
 #pragma unroll
             for (int tb = sb; tb < 2; ++tb) mma<PREC>(dV[sb], dbf[tb], fragB_kn<PREC, true, 1>(sm.AK, SCS, 8 * sb, 8 * tb, g, t4));
 
-        // dv out (transposed through a per-warp scratch tile for 16-byte stores)
-        {
+        // dv out: attn (bf16) writes it into the sixth staging tile; otherwise transposed through a per-warp scratch tile
+        // for 16-byte stores
+        if constexpr (TMA_OUT && !LN) {
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int tq = 8 * nt + 2 * t4 + (i & 1), vc = 16 * warp + g + 8 * (i >> 1);
+                    *reinterpret_cast<__nv_bfloat16*>(sm.ostage + 5 * 2048 + tq * 128 + (((vc >> 3) ^ (tq & 7)) << 4) + (vc & 7) * 2) = __float2bfloat16_rn(dV[nt][i]);
+                }
+        } else {
             IoT* sc = dvsc;
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
@@ -724,7 +735,6 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
             }
         }
         TICK(6)
-        if (TMA_OUT && !LN) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // previous chunk's output tiles have been read
         __syncthreads();  // (C2) score gradients visible; S0s free
         TICK(7)
         if (c > 0) issue_s0(c - 1);
@@ -853,7 +863,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
         __syncthreads();  // (E)
         if (TMA_OUT && tid == 0) {
 #pragma unroll
-            for (int ten = 0; ten < 5; ++ten)
+            for (int ten = 0; ten < (LN ? 5 : 6); ++ten)
                 asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];"
                              ::"l"(&omaps.m[ten]), "r"(0), "r"((int)hi), "r"(c * L), "r"((int)bi), "r"(smem_u32(sm.out_tiles() + ten * 2048)) : "memory");
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -958,8 +968,8 @@ template <typename IoT, int PREC, bool LN> static int launch_bwd_t(const BwdPara
     OutMaps omaps;
     memset(&omaps, 0, sizeof(omaps));
     if (Smem::TMA_OUT) {
-        void* outs[5] = {p.dr, p.dw, p.dk, p.da, p.db};
-        for (int i = 0; i < 5; ++i)
+        void* outs[6] = {p.dr, p.dw, p.dk, p.da, p.db, p.dv};
+        for (int i = 0; i < (LN ? 5 : 6); ++i)
             if (!encode_bthn_map(&omaps.m[i], outs[i], p.B, p.T, p.H, p.st)) return kLaunchFailed;
     }
     if (p.T >= L && !encode_ckpt_state_map(&omaps.ck, p.ckpt, p.B * p.H * (p.T / L))) return kLaunchFailed;
