@@ -42,9 +42,11 @@ namespace wkv7 {
 
 // Tensor maps of the five [time x key] outputs (dq, dw, dk, da, db) for the bulk-store epilogue.
 // ck: the checkpoint states, for the bulk tensor loads of the chunk-start state.
-struct alignas(64) OutMaps { CUtensorMap m[6]; CUtensorMap ck; };  // m[5]: dv (attn only)
+struct alignas(64) OutMaps { CUtensorMap m[6]; CUtensorMap ck, ckm; };  // m[5]: dv (attn only); ck, ckm: checkpoint states, matrices
 
 constexpr int SS = N + 8;  // row stride (floats) of the [value][key] state buffers
+constexpr int MAT_BLK = 8 * 4 * SCS;  // floats per block of the matrices buffer
+static_assert(SCS == L + 8, "the matrix loads copy boxes of L + 8 floats per row");
 // All fp32 tiles of this kernel (operands, scores, score gradients, U, dabu, the two state buffers)
 // carry the column swizzle xcol<1>() of wkv7_common.cuh: each is read both along and across its
 // contraction index.
@@ -73,7 +75,10 @@ template <typename IoT, int PREC, bool LN> struct BwdSmem {
     alignas(16) float wq[L * OPS], wa[L * OPS], kwi[L * OPS], bwi[L * OPS];
     alignas(16) float cum[L * OPS];
     alignas(16) float lw[PREC == 3 ? L * OPS : 4];   // single-TF32 path derives it from cum
-    alignas(16) float QK[L * SCS], QB[L * SCS], AK[L * SCS], AI[L * SCS];  // from the checkpoint record, by cp.async
+    // The chunk's four 16x16 matrices AK, QK, AI, QB (matrix m, row r: row group 2m + r/8 of the record's 64-row operand
+    // tile), filled by two bulk tensor loads: rows with (r & 4) == 0 form a dense block of [8 row groups][4 rows][24 floats]
+    // (16 values, 8 floats of fill), the other rows a second block whose rows start with the fill.  See mat_at().
+    alignas(128) float mats[2 * MAT_BLK];
     // Score gradients (stage C).  While stage B runs they are dead, and the same bytes serve as
     // the per-warp transposition scratch for dv / dg and as the GroupNorm reduction buffers.
     static constexpr int SCRATCH_FLOATS = WARPS * L * Lay::YS * (int)sizeof(IoT) / 4 + WARPS * L * 5;
@@ -92,14 +97,14 @@ template <typename IoT, int PREC, bool LN> struct BwdSmem {
     volatile int abort;             // set when a bounded wait gave up
     alignas(16) float fw[N];
     alignas(16) float Gp[2][WARPS][N];
+    alignas(16) float lnp[LN ? 3 * N : 4];
+    float bdot[L], sbon[L];
     // bf16: the five [16 x 64] output tiles of a chunk, 128-byte rows with the 16-byte unit index XOR-ed
     // with (row % 8) (what a 128-byte-swizzle tensor map expects), stored by five bulk tensor copies per chunk
     static constexpr bool TMA_OUT = sizeof(IoT) == 2;
     // (attn: a sixth tile carries dv, which is formed one stage earlier)
     alignas(TMA_OUT && !LN ? 1024 : 16) unsigned char ostage[TMA_OUT && !LN ? 6 * 2048 : 16];
     __device__ __forceinline__ unsigned char* out_tiles() { return LN ? reinterpret_cast<unsigned char*>(Ut) : ostage; }
-    alignas(16) float lnp[LN ? 3 * N : 4];
-    float bdot[L], sbon[L];
 };
 static_assert(sizeof(BwdSmem<__nv_bfloat16, 1, false>) <= 115712, "bf16 backward must fit two CTAs per SM");
 static_assert(sizeof(BwdSmem<__nv_bfloat16, 1, true>) <= 115712, "bf16 attn_ln backward must fit two CTAs per SM");
@@ -183,6 +188,11 @@ __device__ __forceinline__ void store_quad(float* row, float a0, float a1, float
 // 4..7 of one block with 8-byte loads, and lanes over rows 0,2,4,6 (or 1,3,5,7) x 8 columns, where the second block's
 // shift by 8 floats separates rows r and r + 4.
 constexpr int S0_BLK = 32 * SS;
+// Offset of element (row, col) of matrix m (0 AK, 1 QK, 2 AI, 3 QB) in the matrices buffer; the same split by row bit 2
+// and the same shift of the second block by 8 floats as for the state, here with the 24-float row pitch.
+__device__ __forceinline__ int mat_at(int m, int row, int col) {
+    return ((row >> 2) & 1) * (MAT_BLK + 8) + ((2 * m + (row >> 3)) * 4 + (row & 3)) * SCS + col;
+}
 __device__ __forceinline__ int s0_at(int row, int col) {
     return ((row >> 2) & 1) * (S0_BLK + 8) + (((row >> 3) << 2) | (row & 3)) * SS + col;
 }
@@ -278,27 +288,23 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
     // the checkpoint record of chunk c: its start state and its four 16x16 matrices (QK, QB, AK, AI), which the
     // forward left there so that the scores and the triangular inverse are not rebuilt here
     auto issue_s0 = [&](int c) {
-        const float* rec = ckpt + (long long)c * CK_FLOATS;
         if (tid == 0) {
             // two boxes of [8][4 rows][72 floats]: rows 8a + b and rows 8a + 4 + b (a < 8, b < 4); the second starts at
             // column -8, so that its fill comes first in each row
             const uint32_t bar = smem_u32(&sm.s0_bar);
             const int record = (int)(bh * nchunks + c);
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(N * SS * 4)) : "memory");
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)((N * SS + 2 * MAT_BLK) * 4)) : "memory");
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk)
                 asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
                              ::"r"(smem_u32(sm.S0s + blk * S0_BLK)), "l"(&omaps.ck), "r"(bar), "r"(-8 * blk), "r"(0), "r"(blk), "r"(0), "r"(record) : "memory");
-        }
-        // the matrices are read in the order they are stored (the forward's tile layout: consecutive 16-byte pieces
-        // walk 8 rows of one 4-column chunk), so that a warp reads whole 128-byte lines
-        for (int i = tid; i < 4 * L * (L / 4); i += THREADS) {
-            const int tile = i < 128 ? 0 : i < 192 ? 1 : 2;           // [AK;QK] (128 pieces), AI (64), QB (64)
-            const int pc = i - (tile == 0 ? 0 : tile == 1 ? 128 : 192);
-            const int r = (pc >> 5) * 8 + (pc & 7), ch = (pc >> 3) & 3;  // row within the tile, 4-column chunk
-            float* dst = tile == 1 ? sm.AI : tile == 2 ? sm.QB : (r < L ? sm.AK : sm.QK);
-            const int row = r & (L - 1);
-            cp_async16(dst + row * SCS + xcol<1>(row, ch * 4), rec + CK_MATS + i * 4);
+            // the matrices: the record keeps them as the forward's operand tiles, 16-byte pieces [row / 8][column / 4][row % 8];
+            // seen as [row group][row bit 2][row % 4][piece][4 floats], a box of 6 pieces per row (2 of them beyond the
+            // row: zero fill) lands as rows of 24 floats; the second block starts at piece -2
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk)
+                asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+                             ::"r"(smem_u32(sm.mats + blk * MAT_BLK)), "l"(&omaps.ckm), "r"(bar), "r"(0), "r"(-2 * blk), "r"(0), "r"(blk), "r"(record * (CK_FLOATS / 128) + CK_MATS / 128) : "memory");
         }
     };
     if (nchunks > 0) {
@@ -336,6 +342,21 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
     // rows 2*t4 (and + 1) + 8*block at column 16*warp + g
     const float* const s0_mk = sm.S0s + s0_at(16 * warp + g, 2 * t4);
     const float* const s0_kn = sm.S0s + s0_at(2 * t4, 16 * warp + g);
+    // matrix m as a B operand: [n][k] (row 8*nt + g, columns 8*kk + 2*t4, +1) and [k][n] (rows 8*tb + 2*t4, +1, column 8*sb + g)
+    const float* const mat_g = sm.mats + mat_at(0, g, 2 * t4);
+    const float* const mat_t = sm.mats + mat_at(0, 2 * t4, g);
+    auto mat_nk = [&](int m, int nt, int kk) {
+        FragB<PREC> f;
+        const float2 v = *reinterpret_cast<const float2*>(mat_g + (2 * m + nt) * (4 * SCS) + 8 * kk);
+        f.x[0].setr(v.x); f.x[1].setr(v.y);
+        return f;
+    };
+    auto mat_kn = [&](int m, int sb, int tb) {
+        FragB<PREC> f;
+        const float* q = mat_t + (2 * m + tb) * (4 * SCS) + 8 * sb;
+        f.x[0].setr(q[0]); f.x[1].setr(q[SCS]);
+        return f;
+    };
     for (int it = 0; it < nchunks; ++it) {
         const int c = nchunks - 1 - it;
         const int vs = it & 1;
@@ -392,8 +413,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
             for (int sb = 0; sb < 2; ++sb)
 #pragma unroll
                 for (int tb = sb; tb < 2; ++tb) {
-                    mma<PREC>(du[sb], dyf[tb], fragB_kn<PREC, true, 1>(sm.QB, SCS, 8 * sb, 8 * tb, g, t4));
-                    mma<PREC>(dV[sb], dyf[tb], fragB_kn<PREC, true, 1>(sm.QK, SCS, 8 * sb, 8 * tb, g, t4));
+                    mma<PREC>(du[sb], dyf[tb], mat_kn(3, sb, tb));
+                    mma<PREC>(dV[sb], dyf[tb], mat_kn(1, sb, tb));
                 }
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
@@ -437,21 +458,21 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                 for (int kk = 0; kk <= nt; ++kk) {
-                    mma<PREC>(X[nt], vf[kk], fragB_nk<PREC, true, 1>(sm.AK, SCS, 8 * nt, 8 * kk, g, t4));
-                    if (LN) mma<PREC>(Y[nt], vf[kk], fragB_nk<PREC, true, 1>(sm.QK, SCS, 8 * nt, 8 * kk, g, t4));
+                    mma<PREC>(X[nt], vf[kk], mat_nk(0, nt, kk));
+                    if (LN) mma<PREC>(Y[nt], vf[kk], mat_nk(1, nt, kk));
                 }
             FragA<PREC> xa[2] = {fragA_from_acc<PREC>(X[0]), fragA_from_acc<PREC>(X[1])};
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                for (int kk = 0; kk <= nt; ++kk) mma<PREC>(U[nt], xa[kk], fragB_nk<PREC, true, 1>(sm.AI, SCS, 8 * nt, 8 * kk, g, t4));
+                for (int kk = 0; kk <= nt; ++kk) mma<PREC>(U[nt], xa[kk], mat_nk(2, nt, kk));
             if (LN) {
                 // ---- rebuild Y, then GroupNorm / bonus / gate backward in the [value][time] layout ----
                 FragA<PREC> ua0[2] = {fragA_from_acc<PREC>(U[0]), fragA_from_acc<PREC>(U[1])};
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                    for (int kk = 0; kk <= nt; ++kk) mma<PREC>(Y[nt], ua0[kk], fragB_nk<PREC, true, 1>(sm.QB, SCS, 8 * nt, 8 * kk, g, t4));
+                    for (int kk = 0; kk <= nt; ++kk) mma<PREC>(Y[nt], ua0[kk], mat_nk(3, nt, kk));
                 // statistics: per-warp mean and centred sum of squares over 16 rows, merged below
                 // (a thread's four time steps i4 = 2 * nt + e go through every shuffle level together; sums that only one
                 // lane has to store are formed as a reduce-scatter over the row lanes, which halves the values per level)
@@ -606,13 +627,13 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
 #pragma unroll
             for (int nb = 0; nb < 2; ++nb)
 #pragma unroll
-                for (int kb = nb; kb < 2; ++kb) mma<PREC>(dabu[nb], da2[kb], fragB_kn<PREC, true, 1>(sm.AI, SCS, 8 * nb, 8 * kb, g, t4));
+                for (int kb = nb; kb < 2; ++kb) mma<PREC>(dabu[nb], da2[kb], mat_kn(2, nb, kb));
         }
         FragA<PREC> dbf[2] = {fragA_from_acc<PREC>(dabu[0]), fragA_from_acc<PREC>(dabu[1])};
 #pragma unroll
         for (int sb = 0; sb < 2; ++sb)
 #pragma unroll
-            for (int tb = sb; tb < 2; ++tb) mma<PREC>(dV[sb], dbf[tb], fragB_kn<PREC, true, 1>(sm.AK, SCS, 8 * sb, 8 * tb, g, t4));
+            for (int tb = sb; tb < 2; ++tb) mma<PREC>(dV[sb], dbf[tb], mat_kn(0, sb, tb));
 
         // dv out: attn (bf16) writes it into the sixth staging tile; otherwise transposed through a per-warp scratch tile
         // for 16-byte stores
@@ -946,6 +967,21 @@ static bool encode_ckpt_state_map(CUtensorMap* m, const float* ckpt, long long r
     return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float*>(ckpt + CK_STATE), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+// Tensor map over the matrices part of the checkpoint records.  A record is 40 row groups of 128 floats (32 of state, then
+// 8 of matrices: [AK;QK], AI, QB as operand tiles, a row group = [4 pieces][8 rows][4 floats]); the map sees the whole
+// buffer as [row group][row bit 2][row % 4][piece][4 floats]; a box is the rows of one value of bit 2 in 8 row groups,
+// 6 pieces wide (pieces 4, 5 do not exist and read as zero).
+static bool encode_ckpt_mats_map(CUtensorMap* m, const float* ckpt, long long records) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    static_assert(CK_FLOATS % 128 == 0 && CK_MATS % 128 == 0, "records and their matrices part are whole row groups");
+    const cuuint64_t dims[5] = {4, 4, 4, 2, (cuuint64_t)(records * (CK_FLOATS / 128))};
+    const cuuint64_t strides[4] = {32 * 4, 4 * 4, 16 * 4, 128 * 4};
+    const cuuint32_t box[5] = {4, (cuuint32_t)(SCS / 4), 4, 1, 8};
+    const cuuint32_t es[5] = {1, 1, 1, 1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float*>(ckpt), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 static bool encode_bthn_map(CUtensorMap* m, void* base, long long B, long long T, long long H, const Strides& st) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
@@ -972,7 +1008,8 @@ template <typename IoT, int PREC, bool LN> static int launch_bwd_t(const BwdPara
         for (int i = 0; i < (LN ? 5 : 6); ++i)
             if (!encode_bthn_map(&omaps.m[i], outs[i], p.B, p.T, p.H, p.st)) return kLaunchFailed;
     }
-    if (p.T >= L && !encode_ckpt_state_map(&omaps.ck, p.ckpt, p.B * p.H * (p.T / L))) return kLaunchFailed;
+    if (p.T >= L && !(encode_ckpt_state_map(&omaps.ck, p.ckpt, p.B * p.H * (p.T / L)) && encode_ckpt_mats_map(&omaps.ckm, p.ckpt, p.B * p.H * (p.T / L))))
+        return kLaunchFailed;
     kern<<<(unsigned)(p.B * p.H), THREADS, smem, stream>>>(p, omaps);
     if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
     if (LN) {
