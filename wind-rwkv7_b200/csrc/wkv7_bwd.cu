@@ -103,8 +103,10 @@ template <typename IoT, int PREC, bool LN> struct BwdSmem {
     // with (row % 8) (what a 128-byte-swizzle tensor map expects), stored by five bulk tensor copies per chunk
     static constexpr bool TMA_OUT = sizeof(IoT) == 2;
     // (attn: a sixth tile carries dv, which is formed one stage earlier)
-    alignas(TMA_OUT && !LN ? 1024 : 16) unsigned char ostage[TMA_OUT && !LN ? 6 * 2048 : 16];
+    // (attn_ln: the five tiles alias Ut, Dt, Yt; only dv's tile lives here)
+    alignas(TMA_OUT ? 1024 : 16) unsigned char ostage[TMA_OUT ? (LN ? 1 : 6) * 2048 : 16];
     __device__ __forceinline__ unsigned char* out_tiles() { return LN ? reinterpret_cast<unsigned char*>(Ut) : ostage; }
+    __device__ __forceinline__ unsigned char* dv_tile() { return ostage + (TMA_OUT && !LN ? 5 * 2048 : 0); }
 };
 static_assert(sizeof(BwdSmem<__nv_bfloat16, 1, false>) <= 115712, "bf16 backward must fit two CTAs per SM");
 static_assert(sizeof(BwdSmem<__nv_bfloat16, 1, true>) <= 115712, "bf16 attn_ln backward must fit two CTAs per SM");
@@ -239,7 +241,6 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
     IoT* gdv = (IoT*)p.dv + base;
     const IoT* gg = LN ? (const IoT*)p.g + base : nullptr;
     IoT* gdg = LN ? (IoT*)p.dg + base : nullptr;
-    const float* ckpt = p.ckpt + bh * nchunks * (long long)CK_FLOATS;
     constexpr uint32_t ROW_BYTES = N * sizeof(IoT);
 
     if (LN) {
@@ -635,15 +636,15 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
 #pragma unroll
             for (int tb = sb; tb < 2; ++tb) mma<PREC>(dV[sb], dbf[tb], mat_kn(0, sb, tb));
 
-        // dv out: attn (bf16) writes it into the sixth staging tile; otherwise transposed through a per-warp scratch tile
+        // dv out: the bf16 kernels write it into its staging tile; otherwise transposed through a per-warp scratch tile
         // for 16-byte stores
-        if constexpr (TMA_OUT && !LN) {
+        if constexpr (TMA_OUT) {
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int tq = 8 * nt + 2 * t4 + (i & 1), vc = 16 * warp + g + 8 * (i >> 1);
-                    *reinterpret_cast<__nv_bfloat16*>(sm.ostage + 5 * 2048 + tq * 128 + (((vc >> 3) ^ (tq & 7)) << 4) + (vc & 7) * 2) = __float2bfloat16_rn(dV[nt][i]);
+                    *reinterpret_cast<__nv_bfloat16*>(sm.dv_tile() + tq * 128 + (((vc >> 3) ^ (tq & 7)) << 4) + (vc & 7) * 2) = __float2bfloat16_rn(dV[nt][i] + dvx[nt][i]);
                 }
         } else {
             IoT* sc = dvsc;
@@ -884,9 +885,9 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
         __syncthreads();  // (E)
         if (TMA_OUT && tid == 0) {
 #pragma unroll
-            for (int ten = 0; ten < (LN ? 5 : 6); ++ten)
+            for (int ten = 0; ten < 6; ++ten)
                 asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];"
-                             ::"l"(&omaps.m[ten]), "r"(0), "r"((int)hi), "r"(c * L), "r"((int)bi), "r"(smem_u32(sm.out_tiles() + ten * 2048)) : "memory");
+                             ::"l"(&omaps.m[ten]), "r"(0), "r"((int)hi), "r"(c * L), "r"((int)bi), "r"(smem_u32(ten < 5 ? sm.out_tiles() + ten * 2048 : sm.dv_tile())) : "memory");
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
         TICK(9)
@@ -1005,7 +1006,7 @@ template <typename IoT, int PREC, bool LN> static int launch_bwd_t(const BwdPara
     memset(&omaps, 0, sizeof(omaps));
     if (Smem::TMA_OUT) {
         void* outs[6] = {p.dr, p.dw, p.dk, p.da, p.db, p.dv};
-        for (int i = 0; i < (LN ? 5 : 6); ++i)
+        for (int i = 0; i < 6; ++i)
             if (!encode_bthn_map(&omaps.m[i], outs[i], p.B, p.T, p.H, p.st)) return kLaunchFailed;
     }
     if (p.T >= L && !(encode_ckpt_state_map(&omaps.ck, p.ckpt, p.B * p.H * (p.T / L)) && encode_ckpt_mats_map(&omaps.ckm, p.ckpt, p.B * p.H * (p.T / L))))
