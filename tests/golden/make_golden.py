@@ -1,10 +1,10 @@
 """Generates the golden vectors under tests/golden/ by running the UPSTREAM reference code.
 
-Run in a container where the upstream checkout is available (default
-/root/reference, override with WIND_RWKV_REFERENCE); the produced .npz files are
+Run where a checkout of upstream (johanwind/wind-rwkv7) is available and name it in
+WIND_RWKV_REFERENCE or as the first argument; the produced .npz files are
 committed, so the tests themselves never need the checkout:
 
-    python tests/golden/make_golden.py
+    WIND_RWKV_REFERENCE=<path to the upstream checkout> python tests/golden/make_golden.py
 
 Every fixture stores the seeded inputs and what upstream's own fp32 reference
 functions return for them (outputs, and gradients from autograd through them):
@@ -25,7 +25,9 @@ import types
 import numpy as np
 import torch as th
 
-REF = os.environ.get('WIND_RWKV_REFERENCE', '/root/reference')
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get('WIND_RWKV_REFERENCE')
+if not REF or not os.path.isdir(REF):
+    sys.exit('make_golden.py: give the upstream checkout in WIND_RWKV_REFERENCE or as the first argument')
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REF)
 sys.path.insert(0, os.path.join(REF, 'tests'))
