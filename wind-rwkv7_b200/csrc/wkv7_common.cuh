@@ -231,9 +231,20 @@ template <> __device__ __forceinline__ void load8<float>(const unsigned char* p,
     const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 16);
     f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
 }
-__device__ __forceinline__ void store8(float* p, const float (&f)[8]) {
-    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
-    *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+// Eight floats of a row in two 16-byte stores.  With the 72-float row pitch rows r and r + 4 start on the same banks
+// (also under the column swizzle, which moves both by the same 8 floats), and the eight lanes of a quarter-warp are
+// rows r..r+7: `flip` (set for rows 4..7 of every eight) makes those lanes store their second half first, so that
+// each of the two instructions touches eight different 16-byte bank groups.
+__device__ __forceinline__ void store8(float* p, const float (&f)[8], bool flip = false) {
+    float x[4], y[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        x[i] = flip ? f[4 + i] : f[i];  // goes out first
+        y[i] = flip ? f[i] : f[4 + i];
+    }
+    const int off = flip ? 4 : 0;
+    *reinterpret_cast<float4*>(p + off) = make_float4(x[0], x[1], x[2], x[3]);
+    *reinterpret_cast<float4*>(p + (4 - off)) = make_float4(y[0], y[1], y[2], y[3]);
 }
 
 // One thread = one time step x 8 adjacent key channels (lane = row + 16 * channel-half, warp =
@@ -282,12 +293,13 @@ __device__ __forceinline__ void decay_scan(const unsigned char* tq, const unsign
         if (row == 15) fw[j0 + i] = incl;
     }
     const int at = row * OPS + xcol<X>(row, j0);
-    store8(wq + at, o[0]);
-    store8(wa + at, o[1]);
-    store8(kwi + at, o[2]);
-    store8(bwi + at, o[3]);
-    if (cum_out) store8(cum_out + at, cum);
-    if (lw_out) store8(lw_out + at, lw);
+    const bool flip = (row >> 2) & 1;
+    store8(wq + at, o[0], flip);
+    store8(wa + at, o[1], flip);
+    store8(kwi + at, o[2], flip);
+    store8(bwi + at, o[3], flip);
+    if (cum_out) store8(cum_out + at, cum, flip);
+    if (lw_out) store8(lw_out + at, lw, flip);
 }
 
 // Column `col` of AI = (I - AB)^-1 for a strictly lower-triangular 16x16 AB, one lane per column.
