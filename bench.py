@@ -32,9 +32,9 @@ BWD_BYTES_PER_TOKEN_HEAD = 13 * N * 2   # r,w,k,v,a,b,dy in + six gradients out,
 # Fallback copy of the pool's measured STREAM-style bandwidth, used when MEASURED_PEAKS.json is absent.
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one backward launch at this workload, from the
-# ncu capture summarised in profiles/wkv7_fwd_bwd_config1.md: 427.9 MB read + 131.5 MB written at B = 16, scaled by 4
+# ncu capture summarised in profiles/wkv7_fwd_bwd_config1.md: 428.1 MB read + 130.8 MB written at B = 16, scaled by 4
 # (traffic is proportional to the number of chains; the workload at B = 64 is too large to capture).
-BWD_DRAM_TRAFFIC_BYTES = 2_237_340_000
+BWD_DRAM_TRAFFIC_BYTES = 2_235_450_000
 
 
 def hbm_peak():
