@@ -37,7 +37,7 @@ enum Status : int {
     kNullPointer = -6,
     kLaunchFailed = -7,    // cudaGetLastError() after launch was not cudaSuccess
     kTooLarge = -8,
-    kDeviceTimeout = -9,   // a bounded device-side wait gave up (no current kernel spin-waits)
+    kDeviceTimeout = -9,   // a bounded device-side wait (mbar_wait_bounded) gave up
 };
 
 // ---- IO element access ----------------------------------------------------------------------
@@ -338,6 +338,37 @@ template <int PREC, int X = 0> __device__ __forceinline__ void tri_inverse_colum
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Bounded wait for the phase of an mbarrier with the given parity; the one wait every kernel of this library uses.
+// Returns at once when the CTA has aborted.  When `limit` clocks pass without the phase completing it raises the
+// CTA's abort flag (every later wait then falls through), records kDeviceTimeout in the device status word and
+// returns: a lost copy or a missing arrival ends with an error code, never with a hung GPU.
+// SLEEP: the thread is suspended by the hardware (try_wait with a time hint) instead of polling.
+constexpr long long MBAR_WAIT_LIMIT = 1LL << 28;  // clocks (~0.15 s): far beyond any legitimate wait
+template <bool SLEEP>
+__device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort, int* status, long long limit = MBAR_WAIT_LIMIT) {
+    const uint32_t addr = smem_u32(bar);
+    long long start = 0;
+    // (Polling variant: the abort flag is read after every failed probe.  A tighter loop that looked at it only every
+    // 32nd probe made the tcgen05 forward 1.3 % slower: the chain's polls take issue slots from the working warps.)
+    for (int spin = 0;; ++spin) {
+        uint32_t ok;
+        if (SLEEP)
+            asm volatile("{\n.reg .pred P;\nmbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\nselp.u32 %0, 1, 0, P;\n}\n"
+                         : "=r"(ok) : "r"(addr), "r"(parity), "r"(4000u) : "memory");
+        else
+            asm volatile("{\n.reg .pred P;\nmbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\nselp.u32 %0, 1, 0, P;\n}\n"
+                         : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return;
+        if (*abort) return;
+        if (spin == 0) start = clock64();
+        else if ((SLEEP || (spin & 63) == 0) && clock64() - start > limit) {
+            *abort = 1;
+            atomicExch(status, (int)kDeviceTimeout);  // the launchers always pass the device status word
+            return;
+        }
+    }
+}
 
 // 16-byte asynchronous copy global -> shared through the load/store unit (no TMA request)
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {

@@ -91,7 +91,7 @@ constexpr int C_XY = 128;   // two buffers of X (16) | Y (16)
 constexpr int C_U = 192;    // U (16)
 constexpr int C_SCORE = 208;  // + 32 * group: [AK|AB] in lanes 0-15, [QK|QB] in lanes 32-47
 
-constexpr long long WAIT_LIMIT = 1LL << 28;  // cycles (~0.15 s): far beyond any legitimate wait
+constexpr long long WAIT_LIMIT = MBAR_WAIT_LIMIT;
 
 struct Ctrl {
     uint64_t full[4], done[4], rdone[4], score[4], hop;
@@ -118,25 +118,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // chain's own short waits poll.
 template <bool SLEEP>
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, Ctrl* ctrl, int* status, long long limit = WAIT_LIMIT) {
-    const uint32_t addr = smem_u32(bar);
-    long long start = 0;
-    for (int spin = 0;; ++spin) {
-        uint32_t ok;
-        if (SLEEP)
-            asm volatile("{\n.reg .pred P;\nmbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\nselp.u32 %0, 1, 0, P;\n}\n"
-                         : "=r"(ok) : "r"(addr), "r"(parity), "r"(4000u) : "memory");
-        else
-            asm volatile("{\n.reg .pred P;\nmbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\nselp.u32 %0, 1, 0, P;\n}\n"
-                         : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-        if (ok) return;
-        if (ctrl->abort) return;
-        if (spin == 0) start = clock64();
-        else if ((SLEEP || (spin & 63) == 0) && clock64() - start > limit) {
-            ctrl->abort = 1;
-            atomicExch(status, (int)kDeviceTimeout);
-            return;
-        }
-    }
+    mbar_wait_bounded<SLEEP>(bar, parity, &ctrl->abort, status, limit);
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
