@@ -42,7 +42,7 @@ namespace wkv7 {
 
 // Tensor maps of the five [time x key] outputs (dq, dw, dk, da, db) for the bulk-store epilogue.
 // ck: the checkpoint states, for the bulk tensor loads of the chunk-start state.
-struct alignas(64) OutMaps { CUtensorMap m[6]; CUtensorMap ck, ckm; };  // m[5]: dv (attn only); ck, ckm: checkpoint states, matrices
+struct alignas(64) OutMaps { CUtensorMap m[7]; CUtensorMap ck, ckm; };  // m[5]: dv, m[6]: dg (attn_ln); ck, ckm: checkpoint states, matrices
 
 constexpr int SS = N + 8;  // row stride (floats) of the [value][key] state buffers
 constexpr int MAT_BLK = 8 * 4 * SCS;  // floats per block of the matrices buffer
@@ -83,7 +83,7 @@ template <typename IoT, int PREC, bool LN> struct BwdSmem {
     // the per-warp transposition scratch for dv / dg and as the GroupNorm reduction buffers.
     static constexpr int SCRATCH_FLOATS = WARPS * L * Lay::YS * (int)sizeof(IoT) / 4 + WARPS * L * 5;
     static constexpr int SGRAD_FLOATS = 4 * L * SCS > SCRATCH_FLOATS ? 4 * L * SCS : SCRATCH_FLOATS;
-    alignas(16) float sgrad[SGRAD_FLOATS];  // score gradient i at sgrad + i * L * SCS
+    alignas(LN && sizeof(IoT) == 2 ? 1024 : 16) float sgrad[SGRAD_FLOATS];  // score gradient i at sgrad + i * L * SCS
     // attn_ln: Ut, Dt, Yt are dead between stage C and the next chunk's stage B and double as the output staging tiles
     alignas(LN ? 1024 : 16) float Ut[L * OPS];  // U and dabu as [time][value]
     alignas(16) float Dt[L * OPS];
@@ -558,8 +558,20 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                         red2[(warp * L + tq + 1) * 3 + which] = asum[1];
                     }
                 }
-                // dg out through the per-warp scratch tile
-                {
+                // dg out.  bf16: as a 128-byte-swizzled [time][value] tile at the start of the score-gradient buffer (dead
+                // until the end of stage C's first part), stored by a bulk tensor copy issued after the barrier below and
+                // waited for before barrier (C1); otherwise through the per-warp scratch tile
+                if constexpr (TMA_OUT) {
+                    unsigned char* dgt = reinterpret_cast<unsigned char*>(sm.sgrad);
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int tq = 8 * nt + 2 * t4 + (i & 1), vc = 16 * warp + g + 8 * (i >> 1);
+                            *reinterpret_cast<__nv_bfloat16*>(dgt + tq * 128 + (((vc >> 3) ^ (tq & 7)) << 4) + (vc & 7) * 2) = __float2bfloat16_rn(Y[nt][i]);
+                        }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                } else {
                     IoT* sc = dvsc;
 #pragma unroll
                     for (int nt = 0; nt < 2; ++nt) {
@@ -579,6 +591,11 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                 }
                 if (TMA_OUT) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // previous chunk's output tiles (in Ut, Dt, Yt) have been read
                 __syncthreads();  // (D2)
+                if (TMA_OUT && tid == 0) {
+                    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];"
+                                 ::"l"(&omaps.m[6]), "r"(0), "r"((int)hi), "r"(c * L), "r"((int)bi), "r"(smem_u32(sm.sgrad)) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
 #pragma unroll
                 for (int i4 = 0; i4 < 4; ++i4) {
                     const int nt = i4 >> 1, e = i4 & 1, tq = 8 * nt + 2 * t4 + e;
@@ -701,6 +718,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
             *reinterpret_cast<float2*>(&sm.Gp[it & 1][warp][8 * nt_own + 2 * t4]) = make_float2(gp[0], gp[1]);
         }
         TICK(4)
+        if (TMA_OUT && LN) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // dg's tile lies where stage C writes the score gradients
         __syncthreads();  // (C1)
         TICK(5)
 
@@ -991,8 +1009,8 @@ template <typename IoT, int PREC, bool LN> static int launch_bwd_t(const BwdPara
     OutMaps omaps;
     memset(&omaps, 0, sizeof(omaps));
     if (Smem::TMA_OUT) {
-        void* outs[6] = {p.dr, p.dw, p.dk, p.da, p.db, p.dv};
-        for (int i = 0; i < 6; ++i)
+        void* outs[7] = {p.dr, p.dw, p.dk, p.da, p.db, p.dv, p.dg};
+        for (int i = 0; i < (LN ? 7 : 6); ++i)
             if (!encode_bthn_map(&omaps.m[i], outs[i], p.B, p.T, p.H, p.st)) return kLaunchFailed;
     }
     if (p.T >= L && !(encode_ckpt_state_map(&omaps.ck, p.ckpt, p.B * p.H * (p.T / L)) && encode_ckpt_mats_map(&omaps.ckm, p.ckpt, p.B * p.H * (p.T / L))))
