@@ -219,6 +219,26 @@ def test_strided_head_shard_matches_contiguous():
     assert th.equal(y_view, y_cont) and th.equal(sT_view, sT_cont)
 
 
+def test_strided_head_shard_backward_matches_contiguous():
+    """Backward through head-sharded views: inputs and the gradient tensors all carry stride_t = H_total*N, which is
+    what the tensor maps of the bulk output stores are encoded with."""
+    _, _, attn, synthetic, _ = _mods()
+    B, T, H = 2, 128, 4
+    d = synthetic.wkv7_inputs(B, T, H, N, seed=17, dtype=th.bfloat16, device='cuda')
+    hs = slice(N, 3 * N)   # heads 1..2 of 4
+
+    def grads(make):
+        ins = [make(d[n]).detach().requires_grad_() for n in 'rwkvab']
+        y = attn(*ins, N)
+        y.backward(make(d['dy']))
+        return [y.detach()] + [x.grad for x in ins]
+
+    g_cont = grads(lambda x: x[:, :, hs].contiguous())
+    g_view = grads(lambda x: x[:, :, hs])
+    for a, b in zip(g_view, g_cont):
+        assert th.equal(a.contiguous(), b)
+
+
 def test_empty_and_rejected_inputs():
     _, _, attn, _, _ = _mods()
     z = th.zeros(0, 16, N, dtype=th.bfloat16, device='cuda')
