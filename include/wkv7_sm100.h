@@ -14,7 +14,8 @@
  *   stride_b = T*H*N, stride_t = H*N, stride_h = N.  Head- or batch-sharded views are
  *   expressed through the strides.  Base pointers and strides must keep every row 16-byte
  *   aligned.  States s0, sT, dsT, ds0: fp32 [B, H, N, N] contiguous, S[value][key].
- *   Checkpoints: fp32 [B, H, T/16, N, N] contiguous (state at the start of every 16-step chunk).
+ *   Checkpoints: fp32 [B, H, ceil(T/16), WKV7_CHECKPOINT_FLOATS] contiguous, one record per 16-step chunk; the
+ *   contents are private to the library.  Size the buffer with wkv7_checkpoint_bytes() and nothing else.
  *   io_dtype: WKV7_BF16 (bf16 tensors, single-TF32 tensor-core products, fp32 state) or
  *   WKV7_F32 (fp32 tensors, 3xTF32 split products), or WKV7_F32_TF32 (fp32 tensors, single-TF32
  *   products: what the bf16 path computes, observable without bf16 output rounding).
@@ -38,7 +39,7 @@ extern "C" {
 #define WKV7_OK 0
 #define WKV7_ERR_SHAPE (-1)          /* negative or inconsistent dimensions */
 #define WKV7_ERR_HEAD_SIZE (-2)      /* only N == 64 is built */
-#define WKV7_ERR_CHUNK (-3)          /* T is not a multiple of 16 (WKV7, expand_loras) or C not of 64 */
+#define WKV7_ERR_CHUNK (-3)          /* expand_loras: T not a multiple of 16; ddlerp, expand_loras: C not a multiple of 64 */
 #define WKV7_ERR_ALIGN (-4)          /* a pointer or stride breaks 16-byte row alignment */
 #define WKV7_ERR_DTYPE (-5)
 #define WKV7_ERR_NULL (-6)           /* a required pointer is null */
@@ -53,10 +54,10 @@ extern "C" {
 /* Human-readable text for a status code (host pointer, static storage). */
 const char* wkv7_status_string(int status);
 
-/* Bytes of checkpoint buffer the forward writes for the backward: B*H*(T/16) records of
+/* Bytes of checkpoint buffer the forward writes for the backward: B*H*ceil(T/16) records of
  * WKV7_CHECKPOINT_FLOATS floats (the N*N chunk-start state and the chunk's four 16x16 score / inverse
  * matrices, which the backward loads instead of rebuilding).  The contents are private to the library
- * (in the bf16 and F32_TF32 classes they are rounded to TF32): only a buffer written by wkv7_fwd /
+ * (in the bf16 and F32_TF32 classes the matrices are rounded to TF32): only a buffer written by wkv7_fwd /
  * wkv7_attn_ln_fwd with the same io_dtype may be given to the backward.  0 for N != 64. */
 #define WKV7_CHECKPOINT_FLOATS (64 * 64 + 4 * 16 * 16)
 int64_t wkv7_checkpoint_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
@@ -93,12 +94,29 @@ int wkv7_get_fwd_impl(void);
  * WKV7 forward.  Replaces cuda_forward / forward_kernel of the reference
  * (wind_rwkv/rwkv7/attn.cpp:8-13, attn.cu:11-128) behind th.ops.wind.forward
  * (rwkv7_attn.py:5-11).  s0 may be null (zero initial state), sT may be null (final state not
- * wanted), ckpt may be null (no backward will follow).
+ * wanted), ckpt may be null (no backward will follow).  Any T >= 0: the reference requires T % 16 == 0
+ * (rwkv7_attn.py:22); here the missing time steps of a last, partial chunk are treated as zero inputs with no
+ * decay, nothing is read or written beyond row T-1.  WKV7_ERR_TOO_LARGE when B*H*ceil(T/16)*80 >= 2^31.
  */
 int wkv7_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
              const float* s0, void* y, float* sT, float* ckpt,
              int64_t B, int64_t T, int64_t H, int64_t N,
              int64_t stride_b, int64_t stride_t, int64_t stride_h, int io_dtype, void* stream);
+
+/*
+ * WKV7 decode step(s): the recurrence itself, time step by time step, for generation after a prefill.
+ * Restates the loop body of the reference's naive recurrence (wind_rwkv/rwkv7/time_mixer.py:13-15); the
+ * reference has no kernel for it (its chunked kernels require T % 16 == 0, rwkv7_attn.py:22).  Same
+ * tensors, strides and fp32 state format as wkv7_fwd, so a prefill's sT is this call's s0; s0 and sT may
+ * be the same buffer (update in place); s0 null = zero state, sT null = state not wanted.  Meant for T of
+ * one to a few steps (any T >= 0 is accepted; time is linear in T with one CTA per (batch, head)).  Plain
+ * fp32 arithmetic for every io_dtype: results equal the chunked kernels' up to fp32 / TF32 rounding, not
+ * bit for bit.  No checkpoints, no backward.
+ */
+int wkv7_step(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,
+              const float* s0, void* y, float* sT,
+              int64_t B, int64_t T, int64_t H, int64_t N,
+              int64_t stride_b, int64_t stride_t, int64_t stride_h, int io_dtype, void* stream);
 
 /*
  * WKV7 backward.  Replaces cuda_backward / backward_kernel of the reference

@@ -129,6 +129,15 @@ def test_upstream_test_distribution(dtype):
     run_case(2, 1024, 4, dtype, dist='upstream', seed=5)
 
 
+@pytest.mark.parametrize('dtype', [th.float32, th.bfloat16])
+@pytest.mark.parametrize('T', [1000, 5, 17])
+def test_sequence_length_not_a_multiple_of_16(T, dtype):
+    """The reference asserts T % 16 == 0 (rwkv7_attn.py:22); here the last chunk may be partial.  Forward, final
+    state and all gradients against the oracle; the output buffers are poisoned beyond nothing (they have exactly
+    T rows), so a store past row T-1 would corrupt a neighbouring tensor and show up in its comparison."""
+    run_case(2, T, 2, dtype, s0=True, dsT=True, seed=21)
+
+
 def test_golden_config0(golden):
     """The committed output of upstream's own ref_attn on config 0 (fp32 inputs)."""
     _, _, attn, _, _ = _mods()
@@ -247,9 +256,9 @@ def test_empty_and_rejected_inputs():
     s0 = th.randn(2, 2, N, N, device='cuda')
     y, sT = attn(z, z, z, z, z, z, N, s0=s0, return_state=True)
     assert y.shape == (2, 0, 2 * N) and th.equal(sT, s0)
-    bad = th.zeros(1, 24, N, dtype=th.bfloat16, device='cuda')
+    bad = th.zeros(1, 16, 32, dtype=th.bfloat16, device='cuda')
     with pytest.raises(AssertionError):
-        attn(bad, bad, bad, bad, bad, bad, N)
+        attn(bad, bad, bad, bad, bad, bad, 32)   # head size 32 is not built
     with pytest.raises(TypeError):
         h = th.zeros(1, 16, N, dtype=th.float16, device='cuda')
         attn(h, h, h, h, h, h, N)

@@ -43,6 +43,7 @@ def test_checkpoint_bytes(lib):
     assert lib.wkv7_checkpoint_bytes(64, 1024, 12, 64) == 64 * 12 * 64 * (64 * 64 + 4 * 16 * 16) * 4
     assert lib.wkv7_checkpoint_bytes(1, 64, 1, 32) == 0  # only N == 64 is built
     assert lib.wkv7_checkpoint_bytes(1, 0, 1, 64) == 0
+    assert lib.wkv7_checkpoint_bytes(1, 17, 1, 64) == 2 * (64 * 64 + 4 * 16 * 16) * 4  # a partial last chunk has a record
 
 
 def _fwd(lib, T=16, N=64, st=(1024, 64, 64), dtype=0, p=0x1000):
@@ -51,7 +52,7 @@ def _fwd(lib, T=16, N=64, st=(1024, 64, 64), dtype=0, p=0x1000):
 
 def test_validation_happens_before_any_launch(lib):
     # none of these reach CUDA: the status comes from host-side checks alone
-    assert _fwd(lib, T=17) == -3                   # T % 16
+    assert _fwd(lib, T=1 << 40) == -8              # more checkpoint records than 32-bit row coordinates reach
     assert _fwd(lib, N=32) == -2                   # head size
     assert _fwd(lib, dtype=7) == -5                # dtype
     assert _fwd(lib, st=(1024, 60, 64)) == -4      # stride breaks 16-byte rows

@@ -38,8 +38,8 @@ def _check_tc_launch_registers(log):
             if 'Used 96 registers' not in used:
                 raise RuntimeError('wkv7_fwd_tc_kernel<4,*> must be launched with 96 registers per thread '
                                    f'(setmaxnreg arithmetic); ptxas reports: {used.strip()!r}')
-    if seen == 0:
-        raise RuntimeError('ptxas log holds no wkv7_fwd_tc_kernel<4,*> entry: cannot check its register count')
+    if seen < 8:
+        raise RuntimeError('ptxas log holds fewer wkv7_fwd_tc_kernel<4,*> entries than are built: cannot check their register count')
 
 
 def build(force=False, verbose=False):

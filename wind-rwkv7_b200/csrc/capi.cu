@@ -60,12 +60,14 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 int check_common(int64_t B, int64_t T, int64_t H, int64_t N, int64_t sb, int64_t st, int64_t sh, int io_dtype) {
     if (B < 0 || T < 0 || H < 0 || N <= 0) return wkv7::kBadShape;
     if (N != wkv7::N) return wkv7::kBadHeadSize;
-    if (T % wkv7::L != 0) return wkv7::kBadChunk;
     if (io_dtype != WKV7_BF16 && io_dtype != WKV7_F32 && io_dtype != WKV7_F32_TF32) return wkv7::kBadDtype;
     const int64_t per16 = io_dtype == WKV7_BF16 ? 8 : 4;  // elements per 16 bytes
     if (sb % per16 || st % per16 || sh % per16) return wkv7::kBadAlign;
     if (sb < 0 || st < 0 || sh < 0) return wkv7::kBadShape;
     if (B * H > 0x7fffffffLL) return wkv7::kTooLarge;
+    // the kernels address checkpoint records through 32-bit row coordinates of their tensor maps (80 rows of 64 floats
+    // per record)
+    if (B * H > 0 && (T + wkv7::L - 1) / wkv7::L > (0x7fffffffLL / (wkv7::CK_FLOATS / wkv7::N)) / (B * H)) return wkv7::kTooLarge;
     return wkv7::kOk;
 }
 
@@ -78,12 +80,12 @@ const char* wkv7_status_string(int status) {
         case WKV7_OK: return "ok";
         case WKV7_ERR_SHAPE: return "bad shape: negative or inconsistent dimensions";
         case WKV7_ERR_HEAD_SIZE: return "unsupported head size: only N == 64 is built";
-        case WKV7_ERR_CHUNK: return "T must be a multiple of 16";
+        case WKV7_ERR_CHUNK: return "expand_loras: T must be a multiple of 16; ddlerp, expand_loras: C must be a multiple of 64";
         case WKV7_ERR_ALIGN: return "pointer or stride breaks 16-byte row alignment";
         case WKV7_ERR_DTYPE: return "unknown io_dtype";
         case WKV7_ERR_NULL: return "a required pointer is null";
         case WKV7_ERR_LAUNCH: return "CUDA launch failed";
-        case WKV7_ERR_TOO_LARGE: return "B*H exceeds the grid limit";
+        case WKV7_ERR_TOO_LARGE: return "B*H exceeds the grid limit, or B*H*ceil(T/16) checkpoint records exceed 32-bit row addressing";
         case WKV7_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
         case WKV7_ERR_STATIC_SCRATCH: return "problem needs more than WKV7_STATIC_SCRATCH_BYTES of built-in scratch (B*3*H*N*4 bytes); use wkv7_attn_ln_bwd with a caller-provided workspace";
         default: return "unknown status";
@@ -93,7 +95,7 @@ const char* wkv7_status_string(int status) {
 int64_t wkv7_checkpoint_bytes(int64_t B, int64_t T, int64_t H, int64_t N) {
     if (B < 0 || T < 0 || H < 0 || N < 0) return 0;
     if (N != wkv7::N) return 0;
-    return B * H * (T / wkv7::L) * (int64_t)wkv7::CK_FLOATS * (int64_t)sizeof(float);
+    return B * H * ((T + wkv7::L - 1) / wkv7::L) * (int64_t)wkv7::CK_FLOATS * (int64_t)sizeof(float);
 }
 
 __device__ long long g_selftest_cycles[4];
@@ -169,6 +171,32 @@ int wkv7_fwd(const void* r, const void* w, const void* k, const void* v, const v
              int64_t stride_b, int64_t stride_t, int64_t stride_h, int io_dtype, void* stream) {
     return fwd_common(r, w, k, v, a, b, nullptr, nullptr, false, 0.f, s0, y, sT, ckpt, B, T, H, N, stride_b, stride_t,
                       stride_h, io_dtype, stream);
+}
+
+int wkv7_step(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b, const float* s0,
+              void* y, float* sT, int64_t B, int64_t T, int64_t H, int64_t N, int64_t stride_b, int64_t stride_t,
+              int64_t stride_h, int io_dtype, void* stream) {
+    int rc = check_common(B, T, H, N, stride_b, stride_t, stride_h, io_dtype);
+    if (rc) return rc;
+    if (B == 0 || H == 0) return WKV7_OK;
+    if (T == 0) {
+        if (sT && sT != s0) {
+            size_t bytes = (size_t)B * H * N * N * sizeof(float);
+            cudaError_t e = s0 ? cudaMemcpyAsync(sT, s0, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream)
+                               : cudaMemsetAsync(sT, 0, bytes, (cudaStream_t)stream);
+            if (e != cudaSuccess) return WKV7_ERR_LAUNCH;
+        }
+        return WKV7_OK;
+    }
+    if (!r || !w || !k || !v || !a || !b || !y) return WKV7_ERR_NULL;
+    const void* ptrs[] = {r, w, k, v, a, b, y, s0, sT};
+    for (const void* q : ptrs)
+        if (q && !aligned16(q)) return WKV7_ERR_ALIGN;
+    wkv7::StepParams p{};
+    p.r = r; p.w = w; p.k = k; p.v = v; p.a = a; p.b = b; p.s0 = s0; p.y = y; p.sT = sT;
+    p.B = B; p.T = T; p.H = H;
+    p.st = wkv7::Strides{stride_b, stride_t, stride_h};
+    return wkv7::launch_step(p, io_dtype == WKV7_BF16 ? 0 : 1, (cudaStream_t)stream);
 }
 
 int wkv7_attn_ln_fwd(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,

@@ -2,8 +2,8 @@
 // walked in reverse; the gradient dS of the state stays in registers across chunks.
 //
 // Replaces the reference's backward_kernel (wind_rwkv/rwkv7/attn.cu:131-326).  The forward
-// intermediates of a chunk are rebuilt from the fp32 chunk-start state S0 the forward wrote (in the
-// single-TF32 class already rounded to TF32, so that it is loaded as an operand without conversion).
+// intermediates of a chunk are rebuilt from the fp32 chunk-start state S0 the forward wrote (exact fp32; in the
+// single-TF32 class the tensor core reads the upper 19 bits of it as an operand, no conversion instruction).
 // With the forward's notation (wq, wa, kwi, bwi, fw, QK, QB, AK, AB, AI = (I-AB)^-1, U) and
 // dSf = dS * fw[None,:]:
 //     du   = QB^T dY + bwi dSf^T          dabu = AI^T du
@@ -169,20 +169,21 @@ template <> __device__ __forceinline__ void store_pair<__nv_bfloat16>(__nv_bfloa
 // are, a warp-wide store writes 16 bytes per row (half a 32-byte sector).  Lanes t4 and t4^1 swap one
 // pair, after which the even lane holds columns 4m..4m+3 of the first tile and the odd lane the same
 // columns of the second tile (m = t4 / 2): 8-byte stores (bf16), whole sectors per row.
-// `row` points at column 16*warp of the output row.
-__device__ __forceinline__ void store_quad(__nv_bfloat16* row, float a0, float a1, float b0, float b1, int t4) {
+// `row` points at column 16*warp of the output row; live = false (rows beyond the end of the sequence) keeps the
+// exchange but skips the store.
+__device__ __forceinline__ void store_quad(__nv_bfloat16* row, float a0, float a1, float b0, float b1, int t4, bool live) {
     const __nv_bfloat162 p0 = __floats2bfloat162_rn(a0, a1), p1 = __floats2bfloat162_rn(b0, b1);  // tile 0, tile 1
     const uint32_t u0 = *reinterpret_cast<const uint32_t*>(&p0), u1 = *reinterpret_cast<const uint32_t*>(&p1);
     const bool odd = t4 & 1;
     const uint32_t got = __shfl_xor_sync(0xffffffffu, odd ? u0 : u1, 1);
     const uint2 v = odd ? make_uint2(got, u1) : make_uint2(u0, got);
-    *reinterpret_cast<uint2*>(row + 8 * (t4 & 1) + 4 * (t4 >> 1)) = v;
+    if (live) *reinterpret_cast<uint2*>(row + 8 * (t4 & 1) + 4 * (t4 >> 1)) = v;
 }
-__device__ __forceinline__ void store_quad(float* row, float a0, float a1, float b0, float b1, int t4) {
+__device__ __forceinline__ void store_quad(float* row, float a0, float a1, float b0, float b1, int t4, bool live) {
     const bool odd = t4 & 1;
     const float g0 = __shfl_xor_sync(0xffffffffu, odd ? a0 : b0, 1), g1 = __shfl_xor_sync(0xffffffffu, odd ? a1 : b1, 1);
     const float4 v = odd ? make_float4(g0, g1, b0, b1) : make_float4(a0, a1, g0, g1);
-    *reinterpret_cast<float4*>(row + 8 * (t4 & 1) + 4 * (t4 >> 1)) = v;
+    if (live) *reinterpret_cast<float4*>(row + 8 * (t4 & 1) + 4 * (t4 >> 1)) = v;
 }
 
 // Offset of element (row = value, col = key) of the chunk-start state in shared memory.  With the 72-float row pitch
@@ -218,7 +219,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
     const long long bh = blockIdx.x;
     const long long bi = bh / p.H, hi = bh % p.H;
     const long long base = bi * p.st.b + hi * p.st.h;
-    const int nchunks = (int)(p.T / L);
+    const int nchunks = (int)((p.T + L - 1) / L);  // the last chunk may be partial: its missing rows read as zeros
     const IoT* gin[5] = {(const IoT*)p.r + base, (const IoT*)p.w + base, (const IoT*)p.k + base,
                          (const IoT*)p.a + base, (const IoT*)p.b + base};
     const IoT* gv = (const IoT*)p.v + base;
@@ -260,16 +261,18 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
     auto issue_in = [&](int c) {
         for (int i = tid; i < 5 * L * CH; i += THREADS) {
             const int ten = i / (L * CH), row = (i / CH) % L, ch = i % CH;
-            cp_async16(sm.st_in[ten] + Lay::at(row, ch * (16 / (int)sizeof(IoT))),
-                       reinterpret_cast<const unsigned char*>(gin[ten] + ((long long)c * L + row) * p.st.t) + ch * 16);
+            const long long tt = (long long)c * L + row;
+            cp_async16_zfill(sm.st_in[ten] + Lay::at(row, ch * (16 / (int)sizeof(IoT))),
+                             reinterpret_cast<const unsigned char*>(gin[ten] + (tt < p.T ? tt : p.T - 1) * p.st.t) + ch * 16, tt < p.T);
         }
     };
     auto issue_vdy = [&](int c, int s) {
         for (int i = tid; i < (LN ? 3 : 2) * L * CH; i += THREADS) {
             const int ten = i / (L * CH), row = (i / CH) % L, ch = i % CH;
-            const IoT* src = (ten == 0 ? gv : ten == 1 ? gdy : gg) + ((long long)c * L + row) * p.st.t;
+            const long long tt = (long long)c * L + row;
+            const IoT* src = (ten == 0 ? gv : ten == 1 ? gdy : gg) + (tt < p.T ? tt : p.T - 1) * p.st.t;
             unsigned char* dst = (ten == 0 ? sm.st_v[s] : ten == 1 ? sm.st_dy[s] : sm.st_g[LN ? s : 0]) + Lay::at(row, ch * (16 / (int)sizeof(IoT)));
-            cp_async16(dst, reinterpret_cast<const unsigned char*>(src) + ch * 16);
+            cp_async16_zfill(dst, reinterpret_cast<const unsigned char*>(src) + ch * 16, tt < p.T);
         }
     };
     // the checkpoint record of chunk c: its start state and its four 16x16 matrices (QK, QB, AK, AI), which the
@@ -350,7 +353,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
         // ---------------- P1: decay scan and scaled operands -------------------------------------
         {
             decay_scan<IoT, PREC, 1, Lay::SWZ>(sm.st_in[0], sm.st_in[1], sm.st_in[2], sm.st_in[3], sm.st_in[4], Lay::ROWB, sm.wq, sm.wa,
-                                  sm.kwi, sm.bwi, sm.fw, sm.cum, PREC == 3 ? sm.lw : nullptr, warp, lane);
+                                  sm.kwi, sm.bwi, sm.fw, sm.cum, PREC == 3 ? sm.lw : nullptr, warp, lane,
+                                  (int)min((long long)L, p.T - (long long)c * L));
             if (LN) {  // bonus dot  sum_j r_j k_j bonus_j  per time step: 8 threads per row
                 const int row = tid >> 3, part = tid & 7;
                 float acc = 0.f;
@@ -585,8 +589,10 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                     const int row = lane >> 1, hf = lane & 1;
                     const uint4* src = reinterpret_cast<const uint4*>(sc + row * Lay::YS + 8 * hf);
                     uint4* dst = reinterpret_cast<uint4*>(gdg + ((long long)c * L + row) * p.st.t + 16 * warp + 8 * hf);
-                    dst[0] = src[0];
-                    if (sizeof(IoT) == 4) dst[1] = src[1];
+                    if ((long long)c * L + row < p.T) {
+                        dst[0] = src[0];
+                        if (sizeof(IoT) == 4) dst[1] = src[1];
+                    }
                     __syncwarp();
                 }
                 if (TMA_OUT) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // previous chunk's output tiles (in Ut, Dt, Yt) have been read
@@ -663,8 +669,10 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
             const int row = lane >> 1, hf = lane & 1;
             const uint4* src = reinterpret_cast<const uint4*>(sc + row * Lay::YS + 8 * hf);
             uint4* dst = reinterpret_cast<uint4*>(gdv + ((long long)c * L + row) * p.st.t + 16 * warp + 8 * hf);
-            dst[0] = src[0];
-            if (sizeof(IoT) == 4) dst[1] = src[1];
+            if ((long long)c * L + row < p.T) {
+                dst[0] = src[0];
+                if (sizeof(IoT) == 4) dst[1] = src[1];
+            }
         }
         // dSf, U, dabu to shared memory for stage C
 #pragma unroll
@@ -880,9 +888,10 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
 #pragma unroll
             for (int hrow = 0; hrow < 2; ++hrow) {
                 const long long off = ((long long)c * L + g + 8 * hrow) * p.st.t + 16 * warp;
+                const bool live = (long long)c * L + g + 8 * hrow < p.T;  // uniform over the lanes that exchange values
 #pragma unroll
                 for (int ten = 0; ten < 5; ++ten)
-                    store_quad(gout[ten] + off, outv[ten][0][hrow][0], outv[ten][0][hrow][1], outv[ten][1][hrow][0], outv[ten][1][hrow][1], t4);
+                    store_quad(gout[ten] + off, outv[ten][0][hrow][0], outv[ten][0][hrow][1], outv[ten][1][hrow][0], outv[ten][1][hrow][1], t4, live);
             }
         }
         cp_async_wait<0>();
@@ -1013,7 +1022,8 @@ template <typename IoT, int PREC, bool LN> static int launch_bwd_t(const BwdPara
         for (int i = 0; i < (LN ? 7 : 6); ++i)
             if (!encode_bthn_map(&omaps.m[i], outs[i], p.B, p.T, p.H, p.st)) return kLaunchFailed;
     }
-    if (p.T >= L && !(encode_ckpt_state_map(&omaps.ck, p.ckpt, p.B * p.H * (p.T / L)) && encode_ckpt_mats_map(&omaps.ckm, p.ckpt, p.B * p.H * (p.T / L))))
+    const long long records = p.B * p.H * ((p.T + L - 1) / L);
+    if (!(encode_ckpt_state_map(&omaps.ck, p.ckpt, records) && encode_ckpt_mats_map(&omaps.ckm, p.ckpt, records)))
         return kLaunchFailed;
     kern<<<(unsigned)(p.B * p.H), THREADS, smem, stream>>>(p, omaps);
     if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;

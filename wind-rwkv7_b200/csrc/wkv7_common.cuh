@@ -25,6 +25,14 @@ constexpr int CK_STATE = 0, CK_MATS = N * N;
 constexpr int CK_SC = CK_MATS, CK_AI = CK_SC + 2 * L * L, CK_QB = CK_AI + L * L;
 __host__ __device__ constexpr int ck_tile_at(int row, int chunk) { return (row >> 3) * 128 + chunk * 32 + (row & 7) * 4; }
 constexpr int CK_FLOATS = CK_QB + L * L;  // 5120 floats = 20 KB
+// Range of the decay within a chunk.  The kernels work with P_t and 1/P_t, the running decay product over up to 16
+// steps, and e^(+-80) is what fp32 holds with room for the other factors.  A chunk in which every channel keeps
+// P_16 >= e^-80 (always, for the decays RWKV-7 can produce: w <= -0.5, log P_16 >= -9.7) is computed exactly.  Where a
+// channel decays further within one chunk, the per-step log-decays -exp(w) of its 16-channel group are floored at -5 for
+// that chunk (a step that would multiply the state by less than e^-5 = 0.0067 multiplies it by e^-5), which keeps
+// P_16 >= e^-80 and the relative decay between any two steps of the chunk meaningful.
+constexpr float MIN_CHUNK_LOG_DECAY = -80.f;
+constexpr float MIN_STEP_LOG_DECAY = -5.f;
 
 // ---- status codes (mirrored in include/wkv7_sm100.h) -------------------------------------
 enum Status : int {
@@ -255,10 +263,14 @@ __device__ __forceinline__ void store8(float* p, const float (&f)[8], bool flip 
 // tq/tw/tk/ta/tb: staging tiles with row stride `rowb` bytes.
 // RAWX: the staging tiles have unpadded 128-byte rows (bf16) whose eight 16-byte segments are XOR-ed
 // with (row % 8), so that cp.async writes whole aligned lines and these 16-byte reads stay conflict-free.
+// live: number of time steps of this chunk that exist (16 except in the last chunk of a sequence whose length
+// is not a multiple of 16); rows beyond it carry zero inputs and a per-step log-decay of zero, so that the state
+// passes through them unchanged.
 template <typename IoT, int PREC, int X = 0, bool RAWX = false>
 __device__ __forceinline__ void decay_scan(const unsigned char* tq, const unsigned char* tw, const unsigned char* tk,
                                            const unsigned char* ta, const unsigned char* tb, int rowb, float* wq, float* wa,
-                                           float* kwi, float* bwi, float* fw, float* cum_out, float* lw_out, int warp, int lane) {
+                                           float* kwi, float* bwi, float* fw, float* cum_out, float* lw_out, int warp, int lane,
+                                           int live = L) {
     const int row = lane & 15, j0 = 16 * warp + 8 * (lane >> 4);
     const int off = RAWX ? row * rowb + ((((j0 * (int)sizeof(IoT)) >> 4) ^ (row & 7)) << 4) : row * rowb + j0 * (int)sizeof(IoT);
     float lw[8], cum[8], q[8], k[8], a[8], b[8];
@@ -268,7 +280,9 @@ __device__ __forceinline__ void decay_scan(const unsigned char* tq, const unsign
     load8<IoT>(ta + off, a);
     load8<IoT>(tb + off, b);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { lw[i] = -exp_p<PREC>(lw[i]); cum[i] = lw[i]; }
+    for (int i = 0; i < 8; ++i) lw[i] = row < live ? -exp_p<PREC>(lw[i]) : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) cum[i] = lw[i];
 #pragma unroll
     for (int d = 1; d < 16; d <<= 1)
 #pragma unroll
@@ -276,6 +290,24 @@ __device__ __forceinline__ void decay_scan(const unsigned char* tq, const unsign
             const float up = __shfl_up_sync(0xffffffffu, cum[i], d, 16);
             if (row >= d) cum[i] += up;
         }
+    {
+        // the chunk's total log-decay sits in row 15; out of range for some channel of this warp (never, for decays
+        // RWKV-7 can produce): floor the steps and scan again
+        bool deep = false;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) deep |= cum[i] < MIN_CHUNK_LOG_DECAY;
+        if (__any_sync(0xffffffffu, deep && row == 15)) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) cum[i] = lw[i] = fmaxf(lw[i], MIN_STEP_LOG_DECAY);
+#pragma unroll
+            for (int d = 1; d < 16; d <<= 1)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float up = __shfl_up_sync(0xffffffffu, cum[i], d, 16);
+                    if (row >= d) cum[i] += up;
+                }
+        }
+    }
     // P_t from one exp (argument clamped so that P_t and 1/P_t stay finite), 1/P_t from a reciprocal.
     float o[4][8];
 #pragma unroll
@@ -373,6 +405,11 @@ __device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, uint32_t parity
 // 16-byte asynchronous copy global -> shared through the load/store unit (no TMA request)
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
+}
+// The same copy for a row that may lie beyond the end of the sequence: when `live` is false nothing is read and the
+// 16 bytes are filled with zeros (the source address must still be a valid one).
+__device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, bool live) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem)), "l"(gmem), "r"(live ? 16 : 0) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N_> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N_) : "memory"); }

@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
     const long long bh = blockIdx.x;
     const long long bi = bh / p.H, hi = bh % p.H;
     const long long base = bi * p.st.b + hi * p.st.h;
-    const int nchunks = (int)(p.T / L);
+    const int nchunks = (int)((p.T + L - 1) / L);  // the last chunk may be partial: its missing rows read as zeros
     const IoT* gin[5] = {(const IoT*)p.r + base, (const IoT*)p.w + base, (const IoT*)p.k + base,
                          (const IoT*)p.a + base, (const IoT*)p.b + base};
     const IoT* gv = (const IoT*)p.v + base;
@@ -79,17 +79,19 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
     auto issue_in = [&](int c) {
         for (int i = tid; i < 5 * L * CH; i += THREADS) {
             int ten = i / (L * CH), row = (i / CH) % L, ch = i % CH;
-            cp_async16(sm.st_in[ten] + row * Lay::ROWB + ch * 16,
-                       reinterpret_cast<const unsigned char*>(gin[ten] + ((long long)c * L + row) * p.st.t) + ch * 16);
+            const long long tt = (long long)c * L + row;
+            cp_async16_zfill(sm.st_in[ten] + row * Lay::ROWB + ch * 16,
+                             reinterpret_cast<const unsigned char*>(gin[ten] + (tt < p.T ? tt : p.T - 1) * p.st.t) + ch * 16, tt < p.T);
         }
     };
     auto issue_v = [&](int c) {
         int s = c & 1;
         for (int i = tid; i < (LN ? 2 : 1) * L * CH; i += THREADS) {
             int ten = i / (L * CH), row = (i / CH) % L, ch = i % CH;
-            const IoT* src = (ten == 0 ? gv : gg) + ((long long)c * L + row) * p.st.t;
+            const long long tt = (long long)c * L + row;
+            const IoT* src = (ten == 0 ? gv : gg) + (tt < p.T ? tt : p.T - 1) * p.st.t;
             unsigned char* dst = (ten == 0 ? sm.st_v[s] : sm.st_g[LN ? s : 0]) + row * Lay::ROWB;
-            cp_async16(dst + ch * 16, reinterpret_cast<const unsigned char*>(src) + ch * 16);
+            cp_async16_zfill(dst + ch * 16, reinterpret_cast<const unsigned char*>(src) + ch * 16, tt < p.T);
         }
     };
     if (nchunks > 0) {
@@ -127,7 +129,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
         // ---------------- P1: decay scan and scaled operands ------------------------------------
         {
             decay_scan<IoT, PREC>(sm.st_in[0], sm.st_in[1], sm.st_in[2], sm.st_in[3], sm.st_in[4], Lay::ROWB, sm.wq, sm.wa,
-                                  sm.kwi, sm.bwi, sm.fw, nullptr, nullptr, warp, lane);
+                                  sm.kwi, sm.bwi, sm.fw, nullptr, nullptr, warp, lane, (int)min((long long)L, p.T - (long long)c * L));
             if (LN) {  // bonus dot  sum_j r_j k_j bonus_j  per time step: 8 threads per row
                 const int row = tid >> 3, part = tid & 7;
                 float acc = 0.f;
@@ -195,10 +197,10 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
             float* ck = p.ckpt + (bh * nchunks + c) * (long long)CK_FLOATS;
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
-                // in the single-TF32 class the checkpoint is stored already rounded: the backward uses it
-                // only as a tensor-core operand and skips the rounding at every load
-                *reinterpret_cast<float2*>(ck + (16 * warp + g) * N + 8 * nt + 2 * t4) = make_float2(pre<PREC>(S[nt][0]), pre<PREC>(S[nt][1]));
-                *reinterpret_cast<float2*>(ck + (16 * warp + g + 8) * N + 8 * nt + 2 * t4) = make_float2(pre<PREC>(S[nt][2]), pre<PREC>(S[nt][3]));
+                // exact fp32: in the single-TF32 class the backward's tensor-core products read the upper 19 bits without a
+                // conversion, and its carried decay term uses the full value
+                *reinterpret_cast<float2*>(ck + (16 * warp + g) * N + 8 * nt + 2 * t4) = make_float2(S[nt][0], S[nt][1]);
+                *reinterpret_cast<float2*>(ck + (16 * warp + g + 8) * N + 8 * nt + 2 * t4) = make_float2(S[nt][2], S[nt][3]);
             }
         }
         float XY[4][4] = {};  // [0..1] X^T (time blocks 0,1), [2..3] Y^T
@@ -324,8 +326,10 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
             const int row = lane >> 1, hf = lane & 1;
             const uint4* src = reinterpret_cast<const uint4*>(sc + row * Lay::YS + 8 * hf);
             uint4* dst = reinterpret_cast<uint4*>(gy + ((long long)c * L + row) * p.st.t + 16 * warp + 8 * hf);
-            dst[0] = src[0];
-            if (sizeof(IoT) == 4) dst[1] = src[1];
+            if ((long long)c * L + row < p.T) {
+                dst[0] = src[0];
+                if (sizeof(IoT) == 4) dst[1] = src[1];
+            }
         }
 
         TICK(6)

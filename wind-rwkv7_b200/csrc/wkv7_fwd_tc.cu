@@ -232,7 +232,9 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
-template <int G, bool RND, bool LN>
+// TAIL: the sequence length is not a multiple of 16 (a build of its own, so that whole-chunk sequences carry none of
+// the row tests in their register budget).
+template <int G, bool RND, bool LN, bool TAIL>
 __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams p, const __grid_constant__ CUtensorMap ckmap) {
     using IoT = __nv_bfloat16;
     constexpr int G_BYTES = LN ? G_BYTES_LN : G_BYTES_PLAIN;
@@ -253,7 +255,8 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
     const long long bh = blockIdx.x;
     const long long bi = bh / p.H, hi = bh % p.H;
     const long long base = bi * p.st.b + hi * p.st.h;
-    const int nchunks = (int)(p.T / L);
+    const int nchunks = (int)((p.T + L - 1) / L);  // the last chunk may be partial: its missing rows read as zeros
+    const int tail = TAIL ? (int)(p.T - (long long)(nchunks - 1) * L) : L;  // time steps of the last chunk (1..16)
 
     if (tid == 0) {
         for (int g = 0; g < G; ++g) {
@@ -294,7 +297,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
             for (int q = 0; q < 4; ++q) {
                 const float4 x = s0 ? *reinterpret_cast<const float4*>(s0 + cb + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
                 v[4 * q] = __float_as_uint(x.x); v[4 * q + 1] = __float_as_uint(x.y); v[4 * q + 2] = __float_as_uint(x.z); v[4 * q + 3] = __float_as_uint(x.w);
-                if (ck) *reinterpret_cast<float4*>(ck + cb + 4 * q) = make_float4(rnd(x.x), rnd(x.y), rnd(x.z), rnd(x.w));  // checkpoints are TF32-rounded
+                if (ck) *reinterpret_cast<float4*>(ck + cb + 4 * q) = x;
             }
             tmem_st16(tmem + ((uint32_t)(32 * warp) << 16) + C_S + cb, v);
         }
@@ -383,12 +386,13 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
         const IoT* gg = LN ? (const IoT*)p.g + base : nullptr;
         auto issue_raw = [&](int c, int gbuf) {  // gbuf: parity of the iteration that will process chunk c
             const int r = gt >> 3, seg = gt & 7;
-            const long long goff = ((long long)c * L + r) * p.st.t;
+            const bool live = !TAIL || c + 1 < nchunks || r < tail;  // rows beyond the end of the sequence are filled with zeros, nothing is read
+            const long long goff = ((long long)c * L + (live ? r : 0)) * p.st.t;
             const int at = r * ROWB + ((seg ^ (r & 7)) << 4);
 #pragma unroll
             for (int ten = 0; ten < 6; ++ten)
-                cp_async16(gs + G_RAW + ten * RAW_TILE + at, reinterpret_cast<const unsigned char*>(gin[ten] + goff) + seg * 16);
-            if (LN) cp_async16(gs + G_GRAW + gbuf * RAW_TILE + at, reinterpret_cast<const unsigned char*>(gg + goff) + seg * 16);
+                cp_async16_zfill(gs + G_RAW + ten * RAW_TILE + at, reinterpret_cast<const unsigned char*>(gin[ten] + goff) + seg * 16, live);
+            if (LN) cp_async16_zfill(gs + G_GRAW + gbuf * RAW_TILE + at, reinterpret_cast<const unsigned char*>(gg + goff) + seg * 16, live);
             cp_async_commit();
         };
         // Results of own chunk number kk (chunk cc): Y^T into registers, the chunk-end state straight to the
@@ -416,7 +420,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                     const float give = __uint_as_float(odd ? yv[2 * m] : yv[2 * m + 1]);
                     const float got = __shfl_xor_sync(0xffffffffu, give, 1);
                     const __nv_bfloat162 pr = odd ? __floats2bfloat162_rn(got, mine) : __floats2bfloat162_rn(mine, got);
-                    if (lane < 16) *reinterpret_cast<__nv_bfloat162*>(yo + (long long)(2 * m) * p.st.t) = pr;
+                    if (lane < 16 && (!TAIL || !last || 2 * m + odd < tail)) *reinterpret_cast<__nv_bfloat162*>(yo + (long long)(2 * m) * p.st.t) = pr;
                 }
             } else {
                 // attn_ln epilogue (reference: wind_rwkv/rwkv7/attn_ln.cu:176-205): GroupNorm over the head's 64
@@ -473,13 +477,13 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                     uint4 pk;
                     pk.x = pack_bf16x2_rn(o8[0], o8[1]); pk.y = pack_bf16x2_rn(o8[2], o8[3]);
                     pk.z = pack_bf16x2_rn(o8[4], o8[5]); pk.w = pack_bf16x2_rn(o8[6], o8[7]);
-                    *reinterpret_cast<uint4*>(gy + ((long long)cc * L + t) * p.st.t + i0) = pk;
+                    if (!TAIL || !last || t < tail) *reinterpret_cast<uint4*>(gy + ((long long)cc * L + t) * p.st.t + i0) = pk;
                 }
                 group_bar(grp);  // the scratch lies in an operand tile that is rewritten next
             }
             if (sdst && !last) {
-                // checkpoint state: rounded to TF32 (the backward uses it only as a tensor-core operand), staged in
-                // the 128-byte-swizzled layout the tensor-map store expects: half h = columns 32h..32h+31,
+                // checkpoint state: exact fp32 (the backward's tensor-core products read its upper 19 bits, its carried
+                // decay term all of them), staged in the 128-byte-swizzled layout the tensor-map store expects: half h = columns 32h..32h+31,
                 // row i at i*128 bytes, its 16-byte unit u at (u ^ (i & 7))
                 unsigned char* stage = gs + G_WAQ;
                 const int i = 16 * wg + (lane & 15);
@@ -497,8 +501,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                         for (int j = 0; j < 4; ++j) {
                             const int u = 4 * qt + j;
                             *reinterpret_cast<uint4*>(stage + (u >> 3) * 8192 + i * 128 + (((u & 7) ^ (i & 7)) << 4)) =
-                                make_uint4(tf32_rna(__uint_as_float(sv[4 * j])), tf32_rna(__uint_as_float(sv[4 * j + 1])),
-                                           tf32_rna(__uint_as_float(sv[4 * j + 2])), tf32_rna(__uint_as_float(sv[4 * j + 3])));
+                                make_uint4(sv[4 * j], sv[4 * j + 1], sv[4 * j + 2], sv[4 * j + 3]);
                         }
                     }
                 }
@@ -572,6 +575,10 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                 // log2 of the per-step decay: -exp(w) * log2(e); running sum along the 16 time rows
 #pragma unroll
                 for (int i = 0; i < 8; ++i) cum[i] = ex2_approx(cum[i] * 1.4426950408889634f) * -1.4426950408889634f;
+                if (TAIL && c + 1 == nchunks && row >= tail) {  // a row beyond the end of the sequence: no decay, the state passes through
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) cum[i] = 0.f;
+                }
                 float step[8];  // this row's own log2 decay: P_{t-1} = 2^(cum_t - step_t), cheaper than a shuffle for the row above
 #pragma unroll
                 for (int i = 0; i < 8; ++i) step[i] = cum[i];
@@ -582,6 +589,25 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                         const float up = __shfl_up_sync(0xffffffffu, cum[i], d, 16);
                         if (row >= d) cum[i] += up;
                     }
+                {
+                    // a channel of this warp that decays by more than e^-80 over the chunk (total in row 15; never, for
+                    // decays RWKV-7 can produce): floor the per-step log-decays of the warp's channels at -5 and scan
+                    // again (see MIN_CHUNK_LOG_DECAY)
+                    bool deep = false;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) deep |= cum[i] < MIN_CHUNK_LOG_DECAY * 1.4426950408889634f;
+                    if (__any_sync(0xffffffffu, deep && row == 15)) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) cum[i] = step[i] = fmaxf(step[i], MIN_STEP_LOG_DECAY * 1.4426950408889634f);
+#pragma unroll
+                        for (int d = 1; d < 16; d <<= 1)
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const float up = __shfl_up_sync(0xffffffffu, cum[i], d, 16);
+                                if (row >= d) cum[i] += up;
+                            }
+                    }
+                }
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const float cc = fmaxf(cum[i], -115.f);  // keeps P_t and 1/P_t finite (2^-115 ~ e^-80)
@@ -747,15 +773,19 @@ static bool encode_checkpoint_map(CUtensorMap* m, float* base, long long records
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int G, bool RND, bool LN> static int launch_t(const FwdParams& p, cudaStream_t stream) {
-    auto kern = wkv7_fwd_tc_kernel<G, RND, LN>;
+template <int G, bool RND, bool LN, bool TAIL> static int launch_tt(const FwdParams& p, cudaStream_t stream) {
+    auto kern = wkv7_fwd_tc_kernel<G, RND, LN, TAIL>;
     const int smem = G * (LN ? G_BYTES_LN : G_BYTES_PLAIN) + (int)sizeof(Ctrl) + 1024;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kLaunchFailed;
     alignas(64) CUtensorMap ckmap;
     memset(&ckmap, 0, sizeof(ckmap));
-    if (p.ckpt && !encode_checkpoint_map(&ckmap, p.ckpt, p.B * p.H * (p.T / L))) return kLaunchFailed;
+    if (p.ckpt && !encode_checkpoint_map(&ckmap, p.ckpt, p.B * p.H * ((p.T + L - 1) / L))) return kLaunchFailed;
     kern<<<(unsigned)(p.B * p.H), 128 * (G + 1), smem, stream>>>(p, ckmap);
     return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
+template <int G, bool RND, bool LN> static int launch_t(const FwdParams& p, cudaStream_t stream) {
+    return p.T % L ? launch_tt<G, RND, LN, true>(p, stream) : launch_tt<G, RND, LN, false>(p, stream);
 }
 
 // Exercises the bounded wait and the abort path with the kernel's own mbar_wait: one CTA of four warps;

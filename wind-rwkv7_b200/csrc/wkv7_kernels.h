@@ -36,7 +36,18 @@ struct BwdParams {
     int* status;
 };
 
+struct StepParams {
+    const void *r, *w, *k, *v, *a, *b;  // [B,T,H,N], io dtype
+    const float* s0;                    // [B,H,N,N] or null (zeros); may be the same buffer as sT
+    void* y;                            // [B,T,H,N]
+    float* sT;                          // [B,H,N,N] or null
+    long long B, T, H;
+    Strides st;
+};
+
 int launch_fwd(const FwdParams& p, int io_dtype, bool ln, cudaStream_t stream);
+// the recurrence step by step on fp32 FMAs (decode); io_dtype 0 = bf16, otherwise fp32 tensors
+int launch_step(const StepParams& p, int io_dtype, cudaStream_t stream);
 int launch_bwd(const BwdParams& p, int io_dtype, bool ln, cudaStream_t stream);
 // tcgen05 forward (bf16 IO; attn, or attn_ln with ln = true); |groups| = preparation groups per CTA (2..4); negative: operands are
 // not rounded to TF32 by their producer (the tensor core truncates them)

@@ -18,6 +18,14 @@ CHUNK = 16
 # chunk's four 16x16 matrices; the checkpoint tensor is [B, H, T/16, CKPT_FLOATS] fp32
 CKPT_FLOATS = 64 * 64 + 4 * 16 * 16
 
+
+
+def chunks(T):
+    """Checkpoint records per chain: one per 16 time steps, the last chunk may be partial (upstream requires
+    T % 16 == 0, rwkv7_attn.py:22; here any T is accepted)."""
+    return (T + CHUNK - 1) // CHUNK
+
+
 _lib = None
 
 _vp, _i64, _int, _f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
@@ -30,6 +38,7 @@ _SIGNATURES = {
     'wkv7_set_fwd_impl': (_int, [_int]),
     'wkv7_get_fwd_impl': (_int, []),
     'wkv7_fwd': (_int, [_vp] * 10 + [_i64] * 7 + [_int, _vp]),
+    'wkv7_step': (_int, [_vp] * 9 + [_i64] * 7 + [_int, _vp]),
     'wkv7_bwd': (_int, [_vp] * 17 + [_i64] * 7 + [_int, _vp]),
     'wkv7_attn_ln_fwd': (_int, [_vp] * 12 + [_f32] + [_i64] * 7 + [_int, _vp]),
     'wkv7_attn_ln_bwd_workspace_bytes': (_i64, [_i64] * 3),

@@ -28,7 +28,7 @@ def fw_attn(w, q, k, v, a, b, s0, save_checkpoints=True):
     if y.stride() != v.stride():
         y = th.empty_strided(v.shape, v.stride(), dtype=v.dtype, device=v.device)
     sT = th.empty(B, H, C, C, dtype=th.float32, device=w.device)
-    s = th.empty(B, H, T // _lib.CHUNK if save_checkpoints else 0, _lib.CKPT_FLOATS, dtype=th.float32, device=w.device)
+    s = th.empty(B, H, _lib.chunks(T) if save_checkpoints else 0, _lib.CKPT_FLOATS, dtype=th.float32, device=w.device)
     sb, st, sh = _lib.strides4(w)
     rc = _lib.lib().wkv7_fwd(q.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
                              _lib.ptr(s0), y.data_ptr(), sT.data_ptr(), s.data_ptr() if save_checkpoints else None,
@@ -56,7 +56,7 @@ def bw_attn(w, q, k, v, a, b, s, dy, dsT, sT):
 def _fake_fw(w, q, k, v, a, b, s0, save_checkpoints=True):
     B, T, H, C = w.shape
     return (th.empty_like(v), w.new_empty((B, H, C, C), dtype=th.float32),
-            w.new_empty((B, H, T // _lib.CHUNK if save_checkpoints else 0, _lib.CKPT_FLOATS), dtype=th.float32))
+            w.new_empty((B, H, _lib.chunks(T) if save_checkpoints else 0, _lib.CKPT_FLOATS), dtype=th.float32))
 
 
 def _fake_bw(w, q, k, v, a, b, s, dy, dsT, sT):
@@ -72,7 +72,6 @@ _bw_op = _lib.opaque_op('attn_bwd', bw_attn, _fake_bw,
 
 def _check_inputs(w, q, k, v, a, b, s0):
     B, T, H, C = w.shape
-    assert T % _lib.CHUNK == 0, 'T must be a multiple of 16'
     assert C == _lib.HEAD_SIZE, 'only head size 64 is built'
     assert all(i.dtype == w.dtype for i in [q, k, v, a, b]), 'r,w,k,v,a,b must share one dtype'
     assert all(i.shape == w.shape for i in [q, k, v, a, b])
@@ -134,3 +133,29 @@ def attn(r, w, k, v, a, b, HEAD_SIZE, *, s0=None, return_state=False):
     y, sT, _ = WindRWKV7.apply(w, r, k, v, a, b, s0)
     y = y.view(B, T, HC)
     return (y, sT) if return_state else y
+
+
+def attn_step(r, w, k, v, a, b, HEAD_SIZE, state=None, *, inplace=False):
+    """Decode: advances the recurrence over the T (typically 1) time steps of [B,T,H*HEAD_SIZE] tensors.
+
+    Returns (y, new_state).  `state` is the fp32 [B,H,HEAD_SIZE,HEAD_SIZE] state `attn(..., return_state=True)`
+    returns (None = zeros); with inplace=True it is overwritten and returned.  No autograd, no checkpoints.
+    Upstream has no counterpart; this is the loop body of its naive recurrence (time_mixer.py:13-15) as a kernel."""
+    B, T, HC = w.shape
+    C = HEAD_SIZE
+    H = HC // C
+    assert C == _lib.HEAD_SIZE, 'only head size 64 is built'
+    _lib.require_cuda(r, w, k, v, a, b, state)
+    r, w, k, v, a, b = [i.contiguous().view(B, T, H, C) for i in [r, w, k, v, a, b]]
+    assert all(i.dtype == w.dtype for i in [r, k, v, a, b]), 'r,w,k,v,a,b must share one dtype'
+    if state is not None:
+        assert state.dtype == th.float32 and list(state.shape) == [B, H, C, C] and state.is_contiguous()
+    y = th.empty_like(v)
+    sT = state if (inplace and state is not None) else th.empty(B, H, C, C, dtype=th.float32, device=w.device)
+    sb, st, sh = _lib.strides4(w)
+    with th.cuda.device(w.device):
+        rc = _lib.lib().wkv7_step(r.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
+                                  _lib.ptr(state), y.data_ptr(), sT.data_ptr(), B, T, H, C, sb, st, sh,
+                                  _lib.io_dtype(w), _lib.stream_of(w))
+    _lib.check(rc, 'wkv7_step')
+    return y.view(B, T, HC), sT

@@ -20,7 +20,7 @@ def fw_attn_ln(w, q, k, v, a, b, g, params, s0, save_checkpoints=True):
         w, q, k, v, a, b, g = [i.contiguous() for i in (w, q, k, v, a, b, g)]
     y = th.empty_strided(v.shape, v.stride(), dtype=v.dtype, device=v.device)
     sT = th.empty(B, H, C, C, dtype=th.float32, device=w.device)
-    s = th.empty(B, H, T // _lib.CHUNK if save_checkpoints else 0, _lib.CKPT_FLOATS, dtype=th.float32, device=w.device)
+    s = th.empty(B, H, _lib.chunks(T) if save_checkpoints else 0, _lib.CKPT_FLOATS, dtype=th.float32, device=w.device)
     sb, st, sh = _lib.strides4(w)
     rc = _lib.lib().wkv7_attn_ln_fwd(q.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(),
                                      b.data_ptr(), g.data_ptr(), params.data_ptr(), _lib.ptr(s0), y.data_ptr(),
@@ -53,7 +53,7 @@ def bw_attn_ln(w, q, k, v, a, b, g, params, s, dy, dsT, sT):
 def _fake_fw(w, q, k, v, a, b, g, params, s0, save_checkpoints=True):
     B, T, H, C = w.shape
     return (th.empty_like(v), w.new_empty((B, H, C, C), dtype=th.float32),
-            w.new_empty((B, H, T // _lib.CHUNK if save_checkpoints else 0, _lib.CKPT_FLOATS), dtype=th.float32))
+            w.new_empty((B, H, _lib.chunks(T) if save_checkpoints else 0, _lib.CKPT_FLOATS), dtype=th.float32))
 
 
 def _fake_bw(w, q, k, v, a, b, g, params, s, dy, dsT, sT):
