@@ -9,6 +9,10 @@ torchrun, one rank per GPU) every rank processes its own batch shard; chains are
 there is no collective on the data path ("weak" scaling) and NCCL is used only to take the maximum
 time over ranks.  One JSON line is printed by rank 0.
 
+`--workload attn_ln|prefill|ddlerp|expand_loras|mixer` time the other workloads of the path (prefill also under
+torchrun: config 4 with its 8 sequences sharded over the ranks, "strong" scaling); the default run reports them under
+`secondary`.  `--impl reference-cuda` times the reference's own CUDA kernels from baseline/_ref (context only).
+
 `--impl reference` times the reference's own CPU implementation of the path — the naive per-step
 recurrence, restated in oracle/wkv7_ref.py, forward + autograd backward — on the host cores, on a
 bounded batch slice of the same workload.
@@ -31,9 +35,9 @@ FWD_BYTES_PER_TOKEN_HEAD = 7 * N * 2    # r,w,k,v,a,b in + y out, bf16
 BWD_BYTES_PER_TOKEN_HEAD = 13 * N * 2   # r,w,k,v,a,b,dy in + six gradients out, bf16
 # Fallback copy of the pool's measured STREAM-style bandwidth, used when MEASURED_PEAKS.json is absent.
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one backward launch at this workload, from the
-# ncu capture summarised in profiles/wkv7_fwd_bwd_config1.md: 428.1 MB read + 130.8 MB written at B = 16, scaled by 4
-# (traffic is proportional to the number of chains; the workload at B = 64 is too large to capture).
+# dram__bytes_read.sum + dram__bytes_write.sum of one backward launch at this workload, from an ncu capture of
+# `python bench.py --no-e2e --no-cpu-baseline --steps 1 --warmup 1 --batch 16`: 428.1 MB read + 130.8 MB written at
+# B = 16, scaled by 4 (traffic is proportional to the number of chains; the B = 64 workload is too large to capture).
 BWD_DRAM_TRAFFIC_BYTES = 2_235_450_000
 
 
@@ -105,7 +109,9 @@ def max_over_ranks(ms, dist, device):
 
 
 def cpu_reference_run(sample_B, steps, warmup):
-    """The reference's CPU recurrence (restated in oracle/wkv7_ref.py) on a batch slice, fwd+bwd."""
+    """The reference's CPU recurrence (restated in oracle/wkv7_ref.py) on a batch slice, fwd+bwd, on all host cores
+    (torchrun exports OMP_NUM_THREADS=1 to its ranks; the thread count is set here explicitly)."""
+    th.set_num_threads(max(1, os.cpu_count() or 1))
     sys.path.insert(0, os.path.join(ROOT, 'oracle'))
     import wkv7_ref
     from wind_rwkv.rwkv7 import synthetic
@@ -135,13 +141,179 @@ def run_reference(args):
         'impl': 'reference', 'metric': METRIC, 'value': val, 'unit': 'Mtokens/s', 'n_gpus': args.gpus,
         'steps': max(1, min(args.steps, 3)), 'warmup': 1 if args.warmup else 0, 'ms_per_step': sec * 1e3,
         'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
-        'config': {'workload': f'WKV7 fwd+bwd B{B_PER_GPU} T{T} H{H} N{N} (bounded sample: B={sample_B} of {B_PER_GPU})'},
+        'config': {'workload': f'WKV7 fwd+bwd B{B_PER_GPU} T{T} H{H} N{N} (bounded sample: B={sample_B} of {B_PER_GPU})',
+                   'note': 'CPU arm: one process on the host cores of the box; its value does not depend on --gpus'},
         'cpu_baseline': {'value': val, 'unit': 'Mtokens/s', 'cores': cores, 'kind': 'port',
                          'sample': f'B={sample_B} of {B_PER_GPU}, T={T}, H={H}: torch fp32 per-step recurrence, '
                                    f'forward + autograd backward, {cores} threads'},
         'e2e': {'value': val, 'unit': 'Mtokens/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
     }
     print(json.dumps(line))
+
+
+def bind_to_gpu_numa_node(device_index):
+    """Restricts this process to the CPUs of the NUMA node its GPU is attached to, so that the pinned host buffers
+    allocated afterwards (first touch) come from that node's memory.  Returns what was found and done."""
+    info = {'numa_node': None, 'cpus': None}
+    try:
+        import pynvml as nv
+        nv.nvmlInit()
+        h = nv.nvmlDeviceGetHandleByUUID('GPU-' + str(th.cuda.get_device_properties(device_index).uuid))
+        bus = nv.nvmlDeviceGetPciInfo(h).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        bus = bus.lower()
+        if len(bus.split(':')[0]) == 8:       # NVML prints an 8-digit PCI domain, sysfs a 4-digit one
+            bus = bus[4:]
+        node = int(open(f'/sys/bus/pci/devices/{bus}/numa_node').read())
+        info['numa_node'] = node
+        if node < 0:
+            return info
+        cpus = set()
+        for part in open(f'/sys/devices/system/node/node{node}/cpulist').read().strip().split(','):
+            lo, _, hi = part.partition('-')
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            info['cpus'] = len(cpus)
+    except Exception as e:  # no NVML / no sysfs entry: leave the affinity alone and say so
+        info['error'] = repr(e)
+    return info
+
+
+def run_prefill(args):
+    """Config 4 (B8 T65536 H40, s0 -> sT, forward only) with the batch sharded over the ranks: "strong" scaling,
+    every rank runs B/N of the 8 sequences, no collective on the data path."""
+    from wind_rwkv.rwkv7 import _lib, attn, synthetic
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    th.cuda.set_device(local)
+    dev = th.device('cuda', local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group('nccl', device_id=dev)
+    Bt, Tn, Hn = (8 if args.batch == B_PER_GPU else args.batch), 65536, 40
+    lo, hi = shard_of(rank, world, Bt)
+    B = hi - lo
+    assert B > 0, 'more ranks than sequences'
+    d = synthetic.wkv7_inputs(B, Tn, Hn, N, seed=4 + 100 * rank, dtype=th.bfloat16, device=dev, s0_std=0.1)
+    ins = [d[n] for n in 'rwkvab']
+    step = lambda: attn(*ins, N, s0=d['s0'], return_state=True)
+    for _ in range(max(args.warmup, 3)):
+        y, sT = step()
+    th.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    th.cuda.synchronize()
+    e0, e1 = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            y, sT = step()
+        e1.record()
+        th.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if dist:
+        ms = max_over_ranks(ms, dist, dev)
+    ms /= args.steps
+    finite = bool(th.isfinite(sT).all()) and bool(th.isfinite(y[:, -1]).all())
+    status = _lib.device_status()
+    if rank == 0:
+        peak, which = hbm_peak()
+        alg = Bt * Tn * Hn * FWD_BYTES_PER_TOKEN_HEAD
+        print(json.dumps({
+            'metric': f'WKV7 prefill forward B{Bt} T{Tn} H{Hn} N{N} bf16, s0 -> sT (config 4), Mtokens/s', 'value': Bt * Tn / (ms * 1e-3) / 1e6,
+            'unit': 'Mtokens/s', 'n_gpus': world, 'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms,
+            'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
+            'config': {'workload': f'WKV7 prefill forward B{Bt} T{Tn} H{Hn} N{N} (config 4)', 'global_batch': Bt,
+                       'parallelism': f'batch-sharded x{world} ({B} sequences = {B * Hn} chains per GPU), no collective',
+                       'l2': 'inputs (6 x 2.7 GB / N) exceed the 126 MB L2; no explicit flush'},
+            'roofline': {'bound': 'hbm', 'kernel': 'wkv7_fwd_tc_kernel (tcgen05)', 'achieved': alg / world / (ms * 1e-3) / 1e9, 'peak': peak,
+                         'unit': 'GB/s', 'frac': alg / world / (ms * 1e-3) / 1e9 / peak, 'peak_source': which,
+                         'algorithmic_bytes': alg // world, 'traffic': None, 'note': 'per GPU'},
+            'gpu_launches': args.steps, 'clocks': clocks.summary(), 'finite': finite, 'device_status': status}))
+    if dist:
+        dist.destroy_process_group()
+
+
+def run_reference_cuda(args):
+    """The reference's own CUDA kernels (its attn.cu / attn_ln.cu, installed unmodified under baseline/_ref and built
+    there for sm_100 through its own load_attn), timed device-resident with CUDA events at the config-1 shape.  Runs
+    in this process with baseline/_ref first on sys.path, so nothing of this repository's package is imported.  Not
+    the arm the driver's ratio uses (that is `--impl reference`, the CPU path): a second baseline for context."""
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    ref = os.path.join(ROOT, 'baseline', '_ref')
+    op = 'attn_ln' if args.workload == 'attn_ln' else 'attn'
+    src = os.path.join(ref, 'wind_rwkv', 'rwkv7', 'attn.cu')
+    if not os.path.exists(src) or not th.cuda.is_available():
+        print(json.dumps({'impl': 'reference-cuda', 'unavailable': 'baseline/_ref (the reference install with its .cu sources) or a GPU is missing'}))
+        return
+    sys.path[:] = [p for p in sys.path if not p.endswith('wind-rwkv7_b200')]
+    sys.path.insert(0, ref)
+    os.environ.setdefault('TORCH_CUDA_ARCH_LIST', '10.0')
+    os.environ.setdefault('TORCH_EXTENSIONS_DIR', os.path.join(ref, '_build_' + op))
+    Fn = th.nn.functional
+    dev = th.device('cuda', 0)
+    th.cuda.set_device(0)
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)   # the extension build is verbose on stdout (ninja and nvcc too): keep the JSON line alone there
+    try:
+        if op == 'attn':
+            from wind_rwkv.rwkv7.rwkv7_attn import attn as fn, load_attn
+            load_attn(N)
+            B, Tn, Hn = args.batch, T, H
+        else:
+            from wind_rwkv.rwkv7.rwkv7_attn_ln import attn_ln as fn, load_attn_ln
+            load_attn_ln(N)
+            B, Tn, Hn = (16 if args.batch == B_PER_GPU else args.batch), 4096, 32
+    except Exception as e:
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        print(json.dumps({'impl': 'reference-cuda', 'unavailable': 'building or loading the reference extension failed: ' + repr(e)[:200]}))
+        return
+    sys.stdout.flush()
+    os.dup2(saved_stdout, 1)
+    gen = th.Generator(device=dev).manual_seed(1)
+    rn = lambda *sh: th.randn(*sh, generator=gen, device=dev)
+    r, k, v = [rn(B, Tn, Hn * N).bfloat16().requires_grad_() for _ in range(3)]
+    w = (rn(B, Tn, Hn * N) * 0.5 - 0.6).bfloat16().requires_grad_()
+    kap = Fn.normalize(rn(B, Tn, Hn, N), dim=-1).view(B, Tn, Hn * N)
+    a = (-kap).bfloat16().requires_grad_()
+    b = (kap * th.sigmoid(rn(B, Tn, Hn * N))).bfloat16().requires_grad_()
+    ins = [r, w, k, v, a, b]
+    if op == 'attn_ln':
+        ins += [th.sigmoid(rn(B, Tn, Hn * N)).bfloat16().requires_grad_(), rn(3, Hn * N).requires_grad_()]
+    dy = rn(B, Tn, Hn * N).bfloat16()
+
+    def step():
+        fn(*ins, N).backward(dy)
+        for x in ins:
+            x.grad = None
+    for _ in range(max(args.warmup, 3)):
+        step()
+    th.cuda.synchronize()
+    steps = max(1, min(args.steps, 50))
+    e0, e1 = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clocks:
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        th.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    print(json.dumps({'impl': 'reference-cuda', 'metric': METRIC if op == 'attn' else 'attn_ln fwd+bwd Mtokens/s', 'value': B * Tn / (ms * 1e-3) / 1e6,
+                      'unit': 'Mtokens/s', 'n_gpus': 1, 'steps': steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms,
+                      'higher_is_better': True, 'dtype': 'bf16', 'data': 'synthetic',
+                      'config': {'workload': f'reference {op} fwd+bwd B{B} T{Tn} H{Hn} N{N} through its own Python entry point '
+                                             '(includes its zero-fills and allocations, as a user of it pays them)'},
+                      'clocks': clocks.summary()}))
 
 
 def run_ours(args):
@@ -203,6 +375,7 @@ def run_ours(args):
 
     # end to end through the public API with host buffers: H2D of r,w,k,v,a,b,dy from pinned memory,
     # attn() forward + autograd backward, D2H of y and the six gradients.
+    numa = bind_to_gpu_numa_node(local)
     host_in = {n: d[n].cpu().pin_memory() for n in list('rwkvab') + ['dy']}
     host_out = [th.empty(B, T, H * N, dtype=th.bfloat16).pin_memory() for _ in range(7)]
 
@@ -288,11 +461,28 @@ def run_ours(args):
                                  'frac': fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak},
                          'step_frac': (fwd_bytes + bwd_bytes) / (ms_per_step * 1e-3) / 1e9 / peak},
             'e2e': {'value': e2e_value, 'unit': 'Mtokens/s', 'h2d_bytes_per_step': 7 * nbytes,
-                    'd2h_bytes_per_step': 7 * nbytes, 'steps': e2e_steps},
+                    'd2h_bytes_per_step': 7 * nbytes, 'steps': e2e_steps, 'per_gpu': e2e_value / world,
+                    'host_buffers': {'pinned': True, 'numa': numa},
+                    'note': 'bound by the host link: 1.41 GB cross PCIe per step and GPU, against 2.0 GB of HBM traffic'},
             'gpu_launches': 2 * args.steps,
             'clocks': clocks.summary(),
             'device_status': status,
         }
+        if world == 1 and not args.no_secondary:
+            # the other workloads of the path, a few steps each (device-resident, whole op forward + backward), so that
+            # their numbers are measured by the same run as the headline
+            del host_in, host_out, dev_in
+            th.cuda.empty_cache()
+            sec = {}
+            for wl in ('attn_ln', 'prefill', 'ddlerp', 'expand_loras', 'mixer'):
+                try:
+                    ol = other_line(wl, None, 5, 3)
+                    sec[wl] = {'workload': ol['config']['workload'], 'value': ol['value'], 'unit': ol['unit'], 'ms_per_step': ol['ms_per_step'],
+                               'roofline_frac': None if ol['roofline'] is None else ol['roofline']['frac'], 'steps': 5}
+                except Exception as e:
+                    sec[wl] = {'error': repr(e)[:200]}
+                th.cuda.empty_cache()
+            line['secondary'] = sec
         if world == 1 and not args.no_cpu_baseline:
             sample_B = 4
             val, sec = cpu_reference_run(sample_B, 2, 1)
@@ -305,16 +495,19 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def run_other(args):
-    """Secondary workloads (not the headline line): device-resident, forward + backward through the
-    public API, CUDA events, algorithmic-byte roofline.  One JSON line each."""
+def other_line(wl, batch, steps, warmup):
+    """Secondary workloads (not the headline value): device-resident, forward + backward through the
+    public API, CUDA events, algorithmic-byte roofline.  Returns the JSON-able line."""
     from wind_rwkv.rwkv7 import TimeMixer, attn, attn_ln, ddlerp, expand_loras, synthetic
-    dev = th.device('cuda', 0)
-    th.cuda.set_device(0)
+    dev = th.device('cuda', th.cuda.current_device())
     gen = th.Generator(device=dev).manual_seed(3)
     rn = lambda *sh, std=1.0: th.randn(*sh, generator=gen, device=dev) * std
     bf = th.bfloat16
-    wl = args.workload
+
+    class args:  # the shapes below read args.batch; None selects each workload's own batch
+        pass
+    args.batch = B_PER_GPU if batch is None else batch
+    args.steps, args.warmup = steps, warmup
     if wl == 'attn_ln':      # config 2: B16 T4096 H32
         B, Tn, Hn = args.batch if args.batch != B_PER_GPU else 16, 4096, 32
         d = synthetic.wkv7_inputs(B, Tn, Hn, N, seed=2, dtype=bf, device=dev)
@@ -380,7 +573,7 @@ def run_other(args):
         step()
     th.cuda.synchronize()
     e0, e1 = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
-    with ClockSampler(0) as clocks:
+    with ClockSampler(th.cuda.current_device()) as clocks:
         e0.record()
         for _ in range(args.steps):
             step()
@@ -395,15 +588,23 @@ def run_other(args):
                                                    'frac': alg / (ms * 1e-3) / 1e9 / peak, 'peak_source': which,
                                                    'algorithmic_bytes': alg, 'note': 'whole step (all kernels of the op, forward and backward)'},
             'clocks': clocks.summary()}
-    print(json.dumps(line))
+    return line
+
+
+def run_other(args):
+    th.cuda.set_device(0)
+    print(json.dumps(other_line(args.workload, None if args.batch == B_PER_GPU else args.batch, args.steps, args.warmup)))
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
-    ap.add_argument('--steps', type=int, default=50)
+    ap.add_argument('--steps', type=int, default=400, help='timed steps (default: a timed region of about 0.6 s)')
     ap.add_argument('--warmup', type=int, default=3)
-    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference', 'reference-cuda'],
+                    help="reference: the reference's CPU recurrence (the driver's reference arm); reference-cuda: the "
+                         "reference's own CUDA kernels from baseline/_ref (context only)")
+    ap.add_argument('--no-secondary', action='store_true', help='skip the secondary workloads of the headline line')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer leg (profiling runs)')
     ap.add_argument('--batch', type=int, default=B_PER_GPU, help='batch per GPU (default: the benchmark shape)')
@@ -412,6 +613,10 @@ def main():
     args = ap.parse_args()
     if args.impl == 'reference':
         run_reference(args)
+    elif args.impl == 'reference-cuda':
+        run_reference_cuda(args)
+    elif args.workload == 'prefill':
+        run_prefill(args)
     elif args.workload != 'wkv7':
         run_other(args)
     else:

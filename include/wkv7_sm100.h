@@ -62,10 +62,16 @@ const char* wkv7_status_string(int status);
 #define WKV7_CHECKPOINT_FLOATS (64 * 64 + 4 * 16 * 16)
 int64_t wkv7_checkpoint_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
 
-/* Reads and clears the device-side status word of the current device (synchronises the
- * device).  The tcgen05 forward waits on mbarriers with a cycle limit; a wait that runs out makes the
- * CTA finish early and leaves WKV7_ERR_DEVICE_TIMEOUT here.  0 otherwise. */
+/* Device-side errors.  The kernels wait on mbarriers with a cycle limit; a wait that runs out makes its CTA finish
+ * early and writes WKV7_ERR_DEVICE_TIMEOUT into a status word (one per process, a managed variable inside the library that
+ * host and GPUs can both access; nothing is allocated for it).  No reference counterpart (the reference's kernels have no waits that could be bounded).
+ * wkv7_device_status(): synchronises the current device (all its streams), then returns the word and clears it, in
+ *   one atomic step.  0 = no error since the last call.
+ * wkv7_peek_status(): returns the word without synchronising and without clearing it: a plain host load, cheap
+ *   enough for every call.  It sees the errors of kernels that have finished; the Python wrappers look at it
+ *   before every launch, so a timeout surfaces at the next call at the latest, without a device-wide sync. */
 int wkv7_device_status(void);
+int wkv7_peek_status(void);
 
 /*
  * Self-test of the bounded device-side wait (no reference counterpart).  Launches one 128-thread CTA in

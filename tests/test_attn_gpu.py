@@ -4,12 +4,15 @@ the reference-shaped Python entry points, which call the C ABI of libwkv7_sm100.
 Tolerances (max-abs error relative to the RMS of the oracle tensor, the metric of the task):
   fp32 path (3xTF32 products)                       <= 1e-4
   bf16 path arithmetic (single-TF32 products),
-  observed on fp32 outputs                          <= 2e-2
+  observed on fp32 outputs                          <= 2e-2   (measured: y, sT, dr, dk, dv <= 7e-3; da, db <= 1.5e-2;
+                                                               dw <= 1.9e-2)
   bf16 outputs: rounding the exact result to bf16 already costs about 2.5e-2 of RMS (half an ulp
-  of the largest elements), above the 2e-2 bound, so the literal metric cannot hold for any bf16
-  output.  They are held to 3x that floor measured on the same tensor (a correctly rounded
-  result moved by at most one output ulp) and to a relative L2 error <= 4e-3 (bf16 rounding
-  alone gives 1.7e-3; upstream's own tolerance is 1e-2, tests/utils.py:18).
+  of the largest elements; 3e-2 to 7e-2 for the heavy-tailed da, db, dw), above the 2e-2 bound, so the
+  literal metric cannot hold for any bf16 output.  A bf16 output is the rounding of a value that the
+  arithmetic bound allows to lie 2e-2 of RMS from the oracle, so it is held to (rounding floor measured
+  on the same tensor) + 2e-2 (measured: 1.0 to 1.25 times the floor; 1.6 to 1.7 times on 3 of about 150 tensors), and to a
+  relative L2 error <= 4e-3 (bf16 rounding alone gives 1.7e-3; upstream's own tolerance is 1e-2,
+  tests/utils.py:18).
 """
 import ctypes
 
@@ -56,13 +59,20 @@ def floor_of(ref, dtype):
     return maxabs_rms(th.from_numpy(np.asarray(ref, np.float64)).to(dtype), ref)
 
 
-def check(name, x, ref, dtype):
+def check(name, x, ref, dtype, through_groupnorm=False):
+    """through_groupnorm: gradients of the fused attn_ln op.  At a time step where the recurrence output of a head has
+    a small spread, GroupNorm divides by that spread and amplifies the arithmetic error of that step's gradients (the
+    fp32 path shows the same amplification at its own level); the per-element bound there is 3 x the rounding floor,
+    and tests/test_attn_ln_gpu.py::test_config2_full_batch checks where the excess sits."""
     if dtype == th.float32:
         e = maxabs_rms(x, ref)
         assert e <= 1e-4, f'{name}: {e:.2e} > 1e-4'
     else:
         e, fl, r = maxabs_rms(x, ref), floor_of(ref, dtype), rel_l2(x, ref)
-        assert e <= 3 * fl, f'{name}: {e:.2e} vs bf16 rounding floor {fl:.2e}'
+        if through_groupnorm:
+            assert e <= 3 * fl, f'{name}: {e:.2e} vs 3 x bf16 rounding floor {fl:.2e}'
+        else:
+            assert e <= fl + 2e-2, f'{name}: {e:.2e} vs bf16 rounding floor {fl:.2e} + 2e-2'
         assert r <= 4e-3, f'{name}: rel L2 {r:.2e}'
 
 
@@ -150,15 +160,13 @@ def test_golden_config0(golden):
         assert maxabs_rms(x.grad, g['d' + n]) <= 1e-4, n
 
 
-def test_bf16_arithmetic_on_fp32_outputs():
-    """Single-TF32 products (what the bf16 path computes) with fp32 tensors, i.e. free of bf16
-    output rounding.  Calls the C ABI directly.  Outputs of the forward and the gradients that are
-    plain contractions (dr, dk, dv) meet the literal 2e-2 bound with margin; da, db and dw have
-    heavy-tailed distributions (max/RMS near 20) and reach 2.5e-2 at their largest elements, which
-    is still below their own bf16 rounding floor (3e-2 to 6e-2), so they are held to 4e-2 here."""
+def _single_tf32_on_fp32_outputs(B, T, H, seed, dist, w=None):
+    """Runs forward + backward of the WKV7_F32_TF32 class (fp32 tensors, single-TF32 products: the bf16 path's
+    arithmetic without bf16 output rounding) through the C ABI and returns max-abs/RMS errors against the oracle."""
     c_oracle, _lib, _, synthetic, _ = _mods()
-    B, T, H = 2, 512, 2
-    d = synthetic.wkv7_inputs(B, T, H, N, seed=9, dtype=th.bfloat16)  # bf16-representable values
+    d = synthetic.wkv7_inputs(B, T, H, N, seed=seed, dtype=th.bfloat16, dist=dist)  # bf16-representable values
+    if w is not None:
+        d['w'] = w.to(th.bfloat16)
     dev = {n: d[n].float().cuda().view(B, T, H, N).contiguous() for n in list(NAMES) + ['dy']}
     y = th.empty_like(dev['r'])
     sT = th.empty(B, H, N, N, device='cuda')
@@ -179,8 +187,50 @@ def test_bf16_arithmetic_on_fp32_outputs():
     errs = {'y': maxabs_rms(y, yo), 'sT': maxabs_rms(sT, sTo)}
     errs.update({'d' + n: maxabs_rms(x, ref) for n, x, ref in zip(NAMES, grads, go)})
     print({k: f'{v:.2e}' for k, v in errs.items()})
+    assert _lib.device_status() == 0
+    return errs
+
+
+@pytest.mark.parametrize('dist', ['baseline', 'upstream'])
+def test_bf16_arithmetic_on_fp32_outputs(dist, fwd_impl):
+    """The bf16 path's arithmetic meets the stated 2e-2 bound on all eight tensors at T = 1024, both input
+    distributions, when bf16 output rounding is taken out of the picture."""
+    if fwd_impl == 0:
+        pytest.skip('fp32 tensors always run the warp-MMA forward: one run is enough')
+    errs = _single_tf32_on_fp32_outputs(2, 1024, 2, 9, dist)
     for k, v in errs.items():
-        assert v <= (4e-2 if k in ('da', 'db', 'dw') else 2e-2), f'{k}: {v:.2e}'
+        assert v <= 2e-2, f'{k}: {v:.2e}'
+
+
+def test_strong_decay(fwd_impl):
+    """Decays far stronger than the workload's.  (a) w ~ N(0.5, 1) cut at 1.6: per-step decays down to e^-5, chunk
+    products down to e^-70, the range in which the kernels are exact; normal tolerances, except dw, whose
+    large cancelling terms leave it near 5e-2 here.  (b) w ~ N(1, 1): a third of the chunks have a channel whose
+    16-step decay product leaves fp32's useful range (below e^-80); the kernels then floor the per-step
+    log-decays of that chunk at -5, which bounds the error (measured 5e-2 on y; an unbounded product gave errors
+    of several times the RMS), and everything stays finite.  RWKV-7 itself cannot produce either: w <= -0.5."""
+    if fwd_impl == 0:
+        pytest.skip('one run is enough')
+    gen = th.Generator().manual_seed(13)
+    B, T, H = 2, 256, 2
+    w = (th.randn(B, T, H * N, generator=gen) + 0.5).clamp(max=1.6)
+    errs = _single_tf32_on_fp32_outputs(B, T, H, 13, 'baseline', w=w)
+    for k, v in errs.items():
+        assert v <= (8e-2 if k == 'dw' else 2e-2), f'{k}: {v:.2e}'
+    w = th.randn(B, T, H * N, generator=gen) + 1.0
+    errs = _single_tf32_on_fp32_outputs(B, T, H, 13, 'baseline', w=w)
+    for k in ('y', 'sT', 'dr', 'dk', 'dv'):
+        assert errs[k] <= 0.15, f'{k}: {errs[k]:.2e}'
+    # the same inputs through the bf16 kernels (tcgen05 forward): finite, same bound on y
+    c_oracle, _lib, attn, synthetic, _ = _mods()
+    d = synthetic.wkv7_inputs(B, T, H, N, seed=13, dtype=th.bfloat16, device='cuda')
+    ins = [d[n].requires_grad_() for n in NAMES]
+    ins[1] = w.to(th.bfloat16).cuda().requires_grad_()
+    y = attn(*ins, N)
+    y.backward(d['dy'])
+    assert bool(th.isfinite(y).all()) and all(bool(th.isfinite(x.grad).all()) for x in ins)
+    yo, _ = c_oracle.wkv7_fwd(*[x.detach().double().cpu().numpy().reshape(B, T, H, N) for x in ins])
+    assert maxabs_rms(y.view(B, T, H, N), yo) <= 0.15
 
 
 def test_bounded_wait_gives_up_and_reports(fwd_impl):
@@ -289,21 +339,24 @@ def test_config1_full_size_properties():
 
 
 def test_config4_long_context_prefill():
-    """T = 65536 with a non-zero fp32 initial state (the 2.9B prefill shape, H = 40) on one batch
-    entry: forward only, no checkpoints; y and the final state against the oracle, and the chained
-    property (two 32768-step calls) bit for bit."""
+    """The 2.9B prefill shape at its real batch: B8 T65536 H40, non-zero fp32 initial state, forward only, no
+    checkpoints.  The whole batch for the chained property (two 32768-step calls reproduce one call bit for bit),
+    batch entry 5, heads 0-3 for y and the final state against the oracle."""
     c_oracle, _lib, attn, synthetic, _ = _mods()
-    B, T, H = 1, 65536, 40
+    B, T, H = 8, 65536, 40
     d = synthetic.wkv7_inputs(B, T, H, N, seed=4, dtype=th.bfloat16, device='cuda', s0_std=0.1)
     ins = [d[n] for n in NAMES]
     with th.no_grad():
         y, sT = attn(*ins, N, s0=d['s0'], return_state=True)
-        y1, s1 = attn(*[x[:, :T // 2].contiguous() for x in ins], N, s0=d['s0'], return_state=True)
-        y2, s2 = attn(*[x[:, T // 2:].contiguous() for x in ins], N, s0=s1, return_state=True)
-    assert th.equal(th.cat([y1, y2], 1), y) and th.equal(s2, sT)
-    hs = slice(0, 4 * N)  # four heads through the oracle
-    cpu = [x[:, :, hs].double().cpu().numpy().reshape(B, T, 4, N) for x in ins]
-    yo, sTo = c_oracle.wkv7_fwd(*cpu, s0=d['s0'][:, :4].double().cpu().numpy())
-    check('y', y[:, :, hs], yo, th.bfloat16)
-    assert maxabs_rms(sT[:, :4], sTo) <= 2e-2
+        y1, s1 = attn(*[x[:, :T // 2] for x in ins], N, s0=d['s0'], return_state=True)   # strided views, no copies
+        assert th.equal(y1, y[:, :T // 2])
+        del y1
+        y2, s2 = attn(*[x[:, T // 2:] for x in ins], N, s0=s1, return_state=True)
+    assert th.equal(y2, y[:, T // 2:]) and th.equal(s2, sT)
+    del y2
+    bsel, hs = 5, slice(0, 4 * N)  # four heads of one batch entry through the oracle
+    cpu = [x[bsel:bsel + 1, :, hs].double().cpu().numpy().reshape(1, T, 4, N) for x in ins]
+    yo, sTo = c_oracle.wkv7_fwd(*cpu, s0=d['s0'][bsel:bsel + 1, :4].double().cpu().numpy())
+    check('y', y[bsel:bsel + 1, :, hs], yo, th.bfloat16)
+    assert maxabs_rms(sT[bsel:bsel + 1, :4], sTo) <= 2e-2
     assert _lib.device_status() == 0

@@ -42,7 +42,7 @@ def run_case(B, T, H, dtype, seed=0, upstream_params=False, s0=False):
     go = c_oracle.attn_ln_bwd(*[cpu[n] for n in NAMES], g4, params.double().numpy(), cpu['dy'], s0=s0n)
     check('y', y, out, dtype)
     for n, x, ref in zip(NAMES, dev, go[:6]):
-        check('d' + n, x.grad, ref, dtype)
+        check('d' + n, x.grad, ref, dtype, through_groupnorm=True)
     check('dg', gd.grad, go[6], dtype)
     e = maxabs_rms(pd.grad, go[7])
     assert e <= (1e-4 if dtype == th.float32 else 2e-2), f'dparams: {e:.2e}'
@@ -93,11 +93,18 @@ def test_dparams_is_deterministic():
     assert th.equal(res[0], res[1])
 
 
-def test_config2_shape_slice():
-    """1.5B shape (T4096, H32) on a batch of 1: finite everywhere, 2 heads against the oracle."""
+def test_config2_full_batch():
+    """1.5B shape at its real batch (B16 T4096 H32): finite everywhere; batch entry 11, heads 5-6 against the oracle.
+
+    y and dparams meet the usual bounds.  For the gradients the per-element bound of check() (rounding floor + 2e-2)
+    is exceeded at a handful of time steps: over 4096 steps there are steps where the recurrence output of a head has
+    a spread far below its RMS, GroupNorm divides by that spread and amplifies the TF32-level error of y in that step's
+    gradients (the fp32 path shows the same amplification at its own level).  That explanation is tested, not assumed:
+    no step exceeds 3 x floor, at most 0.2 % of the steps exceed floor + 2e-2 (measured: 0 to 6 of 8192), and at least
+    half of those lie in the lowest decile of spread / RMS of the oracle's recurrence output."""
     import c_oracle
-    from wind_rwkv.rwkv7 import attn_ln, synthetic
-    B, T, H = 1, 4096, 32
+    from wind_rwkv.rwkv7 import _lib, attn_ln, synthetic
+    B, T, H = 16, 4096, 32
     d = synthetic.wkv7_inputs(B, T, H, N, seed=7, dtype=th.bfloat16, device='cuda')
     g, params = synthetic.attn_ln_extras(B, T, H, N, seed=7, dtype=th.bfloat16, device='cuda')
     dev = [d[n].requires_grad_() for n in NAMES]
@@ -105,17 +112,43 @@ def test_config2_shape_slice():
     y = attn_ln(*dev, gd, pd, N)
     y.backward(d['dy'])
     assert bool(th.isfinite(y).all()) and all(bool(th.isfinite(x.grad).all()) for x in dev + [gd, pd])
+    bsel, hs = 11, slice(5 * N, 7 * N)
+    cut = lambda x: x.detach()[bsel:bsel + 1, :, hs].double().cpu().numpy().reshape(1, T, 2, N)
+    ins = [cut(x) for x in dev]
+    prm = params.detach()[:, hs].double().cpu().numpy()
+    out, _, _ = c_oracle.attn_ln_fwd(*ins, cut(gd), prm)
+    go = c_oracle.attn_ln_bwd(*ins, cut(gd), prm, cut(d['dy']))
+    check('y', y[bsel:bsel + 1, :, hs], out, th.bfloat16)
+    yrec, _ = c_oracle.wkv7_fwd(*ins)                     # the recurrence output the GroupNorm sees
+    spread = yrec.std(axis=-1) / np.sqrt(np.mean(yrec ** 2))   # [1, T, 2]
+    low = np.quantile(spread, 0.1)
+    for n, x, ref in zip(list(NAMES) + ['g'], dev + [gd], go[:7]):
+        got = x.grad[bsel:bsel + 1, :, hs].double().cpu().numpy().reshape(1, T, 2, N)
+        rms = np.sqrt(np.mean(ref ** 2))
+        fl = np.abs(th.from_numpy(ref).to(th.bfloat16).double().numpy() - ref).max() / rms
+        per_step = np.abs(got - ref).max(axis=-1) / rms
+        over = per_step > fl + 2e-2
+        print(f'd{n}: max {per_step.max():.2e}, floor {fl:.2e}, steps over floor + 2e-2: {int(over.sum())} of {over.size}, '
+              f'of which in the lowest decile of spread: {int((spread[over] <= low).sum())}')
+        assert rel_l2(x.grad[bsel:bsel + 1, :, hs], ref) <= 4e-3, n
+        assert per_step.max() <= 3 * fl, f'd{n}: {per_step.max():.2e} vs floor {fl:.2e}'
+        assert over.sum() <= 0.002 * over.size, f'd{n}: {int(over.sum())} steps over floor + 2e-2'
+        assert over.sum() < 2 or (spread[over] <= low).sum() * 2 >= over.sum(), f'd{n}: the outliers are not at low-spread steps'
+    # dparams sums over the whole batch: the oracle on this slice cannot check it; it is checked at B = 1 below
+    assert _lib.device_status() == 0
+
+
+def test_config2_dparams_slice():
+    """dparams at the config-2 sequence length (B1 T4096, 2 of 32 heads against the oracle)."""
+    import c_oracle
+    from wind_rwkv.rwkv7 import attn_ln, synthetic
+    B, T, H = 1, 4096, 32
+    d = synthetic.wkv7_inputs(B, T, H, N, seed=7, dtype=th.bfloat16, device='cuda')
+    g, params = synthetic.attn_ln_extras(B, T, H, N, seed=7, dtype=th.bfloat16, device='cuda')
+    dev = [d[n] for n in NAMES]
+    pd = params.requires_grad_()
+    attn_ln(*dev, g, pd, N).backward(d['dy'])
     hs = slice(5 * N, 7 * N)
     cut = lambda x: x.detach()[:, :, hs].double().cpu().numpy().reshape(B, T, 2, N)
-    out, _, _ = c_oracle.attn_ln_fwd(*[cut(x) for x in dev], cut(gd), params.detach()[:, hs].double().cpu().numpy())
-    go = c_oracle.attn_ln_bwd(*[cut(x) for x in dev], cut(gd), params.detach()[:, hs].double().cpu().numpy(), cut(d['dy']))
-    check('y', y[:, :, hs], out, th.bfloat16)
-    # Over 4096 steps there are time steps where the recurrence output of a head is two orders of
-    # magnitude smaller than the state it is contracted from; GroupNorm divides by that small
-    # spread, so the TF32-level absolute error of y is amplified in the gradients of that step
-    # (the fp32 path shows the same amplification at its own level, 1e-4 .. 2e-4).  The relative
-    # L2 bound stays; the worst single element is held to a quarter of the tensor's RMS.
-    for n, x, ref in zip(list(NAMES) + ['g'], dev + [gd], go[:7]):
-        r, e = rel_l2(x.grad[:, :, hs], ref), maxabs_rms(x.grad[:, :, hs], ref)
-        assert r <= 4e-3 and e <= 0.25, f'd{n}: rel L2 {r:.2e}, max-abs/RMS {e:.2e}'
+    go = c_oracle.attn_ln_bwd(*[cut(x) for x in dev], cut(g), params.detach()[:, hs].double().cpu().numpy(), cut(d['dy']))
     assert maxabs_rms(pd.grad[:, hs], go[7]) <= 2e-2

@@ -75,3 +75,20 @@ def test_python_ops_refuse_cpu_tensors(lib):
     x = th.zeros(1, 16, 64, dtype=th.bfloat16)
     with pytest.raises(RuntimeError, match='CUDA'):
         attn(x, x, x, x, x, x, 64)
+
+
+def test_launchers_need_all_tensors_on_one_cuda_device(lib):
+    """The wrappers make the tensors' device current for the launch and refuse mixed devices (a kernel launched on
+    the current device with another device's pointers would fail or touch the wrong memory)."""
+    import torch as th
+    from wind_rwkv.rwkv7 import _lib
+    with pytest.raises(RuntimeError, match='one device'):
+        _lib.on_device(th.zeros(1), th.zeros(1, device='meta'))
+    with pytest.raises(RuntimeError, match='CUDA'):
+        _lib.on_device(th.zeros(1), None)
+
+
+def test_status_word_is_readable_without_a_device(lib):
+    """wkv7_peek_status is a host load of a managed variable; without a GPU it reports a launch error rather than
+    crashing."""
+    assert lib.wkv7_peek_status() in (0, -7)

@@ -17,12 +17,19 @@ static __device__ __align__(256) float g_attn_ln_static_scratch[WKV7_STATIC_SCRA
 
 namespace {
 
-__device__ int g_status_word = 0;
+// The status word that a kernel's bounded wait writes when it gives up: a managed variable, part of the library's
+// image (nothing is allocated at run time), one per process, readable by the host while kernels run (concurrent
+// managed access), so that wkv7_peek_status() is a plain load that synchronises nothing.  The page stays on the host
+// side unless a kernel reports an error.
+__managed__ int g_status_word = 0;
 
 int* status_ptr() {
-    int* p = nullptr;
-    if (cudaGetSymbolAddress((void**)&p, g_status_word) != cudaSuccess) return nullptr;
-    return p;
+    static int* word = [] {
+        int* p = nullptr;
+        if (cudaGetSymbolAddress((void**)&p, g_status_word) != cudaSuccess) p = nullptr;
+        return p;
+    }();
+    return word;
 }
 
 // Device address of g_attn_ln_static_scratch on the current device, looked up on the first call
@@ -125,10 +132,15 @@ int wkv7_set_fwd_impl(int impl) {
 int wkv7_get_fwd_impl(void) { return fwd_impl().load(std::memory_order_relaxed); }
 
 int wkv7_device_status(void) {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_status_word, sizeof(int)) != cudaSuccess) return WKV7_ERR_LAUNCH;
-    if (v != 0) cudaMemcpyToSymbol(g_status_word, &zero, sizeof(int));
-    return v;
+    int* w = status_ptr();
+    if (!w) return WKV7_ERR_LAUNCH;
+    if (cudaDeviceSynchronize() != cudaSuccess) return WKV7_ERR_LAUNCH;  // every stream of the current device, non-blocking ones too
+    return __atomic_exchange_n(w, 0, __ATOMIC_ACQ_REL);                  // read and clear in one step
+}
+
+int wkv7_peek_status(void) {
+    int* w = status_ptr();
+    return w ? __atomic_load_n(w, __ATOMIC_ACQUIRE) : WKV7_ERR_LAUNCH;
 }
 
 static int fwd_common(const void* r, const void* w, const void* k, const void* v, const void* a, const void* b,

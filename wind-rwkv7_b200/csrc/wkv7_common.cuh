@@ -396,7 +396,8 @@ __device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, uint32_t parity
         if (spin == 0) start = clock64();
         else if ((SLEEP || (spin & 63) == 0) && clock64() - start > limit) {
             *abort = 1;
-            atomicExch(status, (int)kDeviceTimeout);  // the launchers always pass the device status word
+            *reinterpret_cast<volatile int*>(status) = (int)kDeviceTimeout;  // the launchers always pass the status word (host-visible)
+            __threadfence_system();
             return;
         }
     }

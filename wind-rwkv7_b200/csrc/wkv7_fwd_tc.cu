@@ -95,8 +95,10 @@ constexpr long long WAIT_LIMIT = MBAR_WAIT_LIMIT;
 
 struct Ctrl {
     uint64_t full[4], done[4], rdone[4], score[4], hop;
+    uint64_t drain[5];         // abort path only: completion of a thread's outstanding tensor-core work (chain, groups)
     uint32_t tmem_base;
     volatile int abort;
+    volatile int zero;         // stays 0: the abort-path drain waits with this in place of the abort flag
     float lnp[3 * N];          // attn_ln: GroupNorm weight, bias, bonus of this head
     float bdot[4][2][4][L];    // attn_ln: per-warp partial bonus dots [group][iteration parity][warp][time]
 };
@@ -125,6 +127,12 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Abort path: commits everything this thread has issued to the tensor core to a barrier of its own and waits for
+// it, bounded and regardless of the CTA's abort flag, so that tensor memory is not released under products in flight.
+__device__ __forceinline__ void drain_tensor_work(uint64_t* bar, volatile int* never_set, int* status) {
+    tc_commit(bar);
+    mbar_wait_bounded<false>(bar, 0, never_set, status);
 }
 // named barrier of one preparation group; immediate ids, so that ptxas counts G + 1 barriers for the CTA
 // and not all sixteen
@@ -266,7 +274,9 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
             mbar_init(&ctrl->score[g], 1);
         }
         mbar_init(&ctrl->hop, 1);
+        for (int g = 0; g <= G; ++g) mbar_init(&ctrl->drain[g], 1);
         ctrl->abort = 0;
+        ctrl->zero = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (LN) {
@@ -320,6 +330,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
             long long tacc[8] = {}, tprev = clock64();
 #endif
             for (int c = 0; c < nchunks; ++c) {
+                if (ctrl->abort) break;  // a wait of this CTA ran out: issue nothing more
                 const int g = c % G, k = c / G;
                 const uint32_t gb = sb + g * G_BYTES;
                 const uint64_t dWAQ = desc_kmajor(gb + G_WAQ, 2048), dSC = desc_kmajor(gb + G_SC, 512), dAI = desc_kmajor(gb + G_AI, 512),
@@ -367,6 +378,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                 tc_fence_after();
                 TCK(7)
             }
+            if (ctrl->abort) drain_tensor_work(&ctrl->drain[G], &ctrl->zero, p.status);
 #ifdef WKV7_TIMING
             if (blockIdx.x == 0)
                 printf("chain: loop %lld | wait full %lld | wait rdone %lld | issue hop1+decay %lld | wait hop1 %lld | hop2+kwf issue+wait %lld | issue hop3 %lld | wait last %lld (cycles per chunk)\n",

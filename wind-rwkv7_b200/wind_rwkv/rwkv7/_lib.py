@@ -34,6 +34,7 @@ _SIGNATURES = {
     'wkv7_status_string': (ctypes.c_char_p, [_int]),
     'wkv7_checkpoint_bytes': (_i64, [_i64] * 4),
     'wkv7_device_status': (_int, []),
+    'wkv7_peek_status': (_int, []),
     'wkv7_selftest_bounded_wait': (_int, [_i64, ctypes.POINTER(ctypes.c_int64), _vp]),
     'wkv7_set_fwd_impl': (_int, [_int]),
     'wkv7_get_fwd_impl': (_int, []),
@@ -73,9 +74,27 @@ def lib():
 
 
 def check(status, what):
+    """Raises on a non-zero return code of a C-ABI call, and on a device-side error that an earlier, finished kernel
+    left in the status word (looked at without synchronising; see wkv7_peek_status in the header)."""
     if status != 0:
         msg = lib().wkv7_status_string(status).decode()
         raise RuntimeError(f'{what} failed: {msg} (status {status})')
+    dev = lib().wkv7_peek_status()
+    if dev != 0:
+        raise RuntimeError(f'an earlier wkv7 kernel reported: {lib().wkv7_status_string(dev).decode()} (status {dev}); '
+                           'its results are invalid.  wkv7_device_status() reads and clears the error.')
+
+
+def on_device(*tensors):
+    """Context manager that makes the tensors' device current for a launch (kernels run on the current device, the
+    stream argument alone does not select it); all tensors must live on one CUDA device."""
+    devs = {t.device for t in tensors if t is not None}
+    if len(devs) != 1:
+        raise RuntimeError(f'wkv7 ops need all tensors on one device, got {sorted(str(d) for d in devs)}')
+    dev = devs.pop()
+    if dev.type != 'cuda':
+        raise RuntimeError('wkv7 ops run on CUDA tensors only (sm_100a); there is no CPU path')
+    return th.cuda.device(dev)
 
 
 def io_dtype(t):

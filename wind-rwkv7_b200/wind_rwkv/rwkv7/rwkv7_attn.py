@@ -30,9 +30,10 @@ def fw_attn(w, q, k, v, a, b, s0, save_checkpoints=True):
     sT = th.empty(B, H, C, C, dtype=th.float32, device=w.device)
     s = th.empty(B, H, _lib.chunks(T) if save_checkpoints else 0, _lib.CKPT_FLOATS, dtype=th.float32, device=w.device)
     sb, st, sh = _lib.strides4(w)
-    rc = _lib.lib().wkv7_fwd(q.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
-                             _lib.ptr(s0), y.data_ptr(), sT.data_ptr(), s.data_ptr() if save_checkpoints else None,
-                             B, T, H, C, sb, st, sh, _lib.io_dtype(w), _lib.stream_of(w))
+    with _lib.on_device(w, q, k, v, a, b, s0):
+        rc = _lib.lib().wkv7_fwd(q.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
+                                 _lib.ptr(s0), y.data_ptr(), sT.data_ptr(), s.data_ptr() if save_checkpoints else None,
+                                 B, T, H, C, sb, st, sh, _lib.io_dtype(w), _lib.stream_of(w))
     _lib.check(rc, 'wkv7_fwd')
     return y, sT, s
 
@@ -45,10 +46,11 @@ def bw_attn(w, q, k, v, a, b, s, dy, dsT, sT):
     dw, dq, dk, dv, da, db = [th.empty_strided(w.shape, w.stride(), dtype=w.dtype, device=w.device) for _ in range(6)]
     ds0 = th.empty(B, H, C, C, dtype=th.float32, device=w.device)
     sb, st, sh = _lib.strides4(w)
-    rc = _lib.lib().wkv7_bwd(q.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
-                             dy.data_ptr(), s.data_ptr(), _lib.ptr(dsT), _lib.ptr(sT if dsT is not None else None),
-                             dq.data_ptr(), dw.data_ptr(), dk.data_ptr(), dv.data_ptr(), da.data_ptr(), db.data_ptr(),
-                             ds0.data_ptr(), B, T, H, C, sb, st, sh, _lib.io_dtype(w), _lib.stream_of(w))
+    with _lib.on_device(w, q, k, v, a, b, s, dy, dsT):
+        rc = _lib.lib().wkv7_bwd(q.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
+                                 dy.data_ptr(), s.data_ptr(), _lib.ptr(dsT), _lib.ptr(sT if dsT is not None else None),
+                                 dq.data_ptr(), dw.data_ptr(), dk.data_ptr(), dv.data_ptr(), da.data_ptr(), db.data_ptr(),
+                                 ds0.data_ptr(), B, T, H, C, sb, st, sh, _lib.io_dtype(w), _lib.stream_of(w))
     _lib.check(rc, 'wkv7_bwd')
     return dw, dq, dk, dv, da, db, ds0
 
@@ -153,7 +155,7 @@ def attn_step(r, w, k, v, a, b, HEAD_SIZE, state=None, *, inplace=False):
     y = th.empty_like(v)
     sT = state if (inplace and state is not None) else th.empty(B, H, C, C, dtype=th.float32, device=w.device)
     sb, st, sh = _lib.strides4(w)
-    with th.cuda.device(w.device):
+    with _lib.on_device(r, w, k, v, a, b, state):
         rc = _lib.lib().wkv7_step(r.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
                                   _lib.ptr(state), y.data_ptr(), sT.data_ptr(), B, T, H, C, sb, st, sh,
                                   _lib.io_dtype(w), _lib.stream_of(w))

@@ -22,10 +22,11 @@ def fw_attn_ln(w, q, k, v, a, b, g, params, s0, save_checkpoints=True):
     sT = th.empty(B, H, C, C, dtype=th.float32, device=w.device)
     s = th.empty(B, H, _lib.chunks(T) if save_checkpoints else 0, _lib.CKPT_FLOATS, dtype=th.float32, device=w.device)
     sb, st, sh = _lib.strides4(w)
-    rc = _lib.lib().wkv7_attn_ln_fwd(q.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(),
-                                     b.data_ptr(), g.data_ptr(), params.data_ptr(), _lib.ptr(s0), y.data_ptr(),
-                                     sT.data_ptr(), s.data_ptr() if save_checkpoints else None, EPS, B, T, H, C, sb, st, sh,
-                                     _lib.io_dtype(w), _lib.stream_of(w))
+    with _lib.on_device(w, q, k, v, a, b, g, params, s0):
+        rc = _lib.lib().wkv7_attn_ln_fwd(q.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(),
+                                         b.data_ptr(), g.data_ptr(), params.data_ptr(), _lib.ptr(s0), y.data_ptr(),
+                                         sT.data_ptr(), s.data_ptr() if save_checkpoints else None, EPS, B, T, H, C, sb, st, sh,
+                                         _lib.io_dtype(w), _lib.stream_of(w))
     _lib.check(rc, 'wkv7_attn_ln_fwd')
     return y, sT, s
 
@@ -40,12 +41,13 @@ def bw_attn_ln(w, q, k, v, a, b, g, params, s, dy, dsT, sT):
     ws = th.empty(B, 3, H * C, dtype=th.float32, device=w.device)
     ds0 = th.empty(B, H, C, C, dtype=th.float32, device=w.device)
     sb, st, sh = _lib.strides4(w)
-    rc = _lib.lib().wkv7_attn_ln_bwd(
-        q.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(), g.data_ptr(),
-        params.data_ptr(), dy.data_ptr(), s.data_ptr(), _lib.ptr(dsT), _lib.ptr(sT if dsT is not None else None),
-        dq.data_ptr(), dw.data_ptr(), dk.data_ptr(), dv.data_ptr(), da.data_ptr(), db.data_ptr(), dg.data_ptr(),
-        dparams.data_ptr(), ws.data_ptr(), ds0.data_ptr(), EPS, B, T, H, C, sb, st, sh,
-        _lib.io_dtype(w), _lib.stream_of(w))
+    with _lib.on_device(w, q, k, v, a, b, g, params, s, dy, dsT):
+        rc = _lib.lib().wkv7_attn_ln_bwd(
+            q.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(), g.data_ptr(),
+            params.data_ptr(), dy.data_ptr(), s.data_ptr(), _lib.ptr(dsT), _lib.ptr(sT if dsT is not None else None),
+            dq.data_ptr(), dw.data_ptr(), dk.data_ptr(), dv.data_ptr(), da.data_ptr(), db.data_ptr(), dg.data_ptr(),
+            dparams.data_ptr(), ws.data_ptr(), ds0.data_ptr(), EPS, B, T, H, C, sb, st, sh,
+            _lib.io_dtype(w), _lib.stream_of(w))
     _lib.check(rc, 'wkv7_attn_ln_bwd')
     return dw, dq, dk, dv, da, db, dg, dparams, ds0
 

@@ -16,8 +16,9 @@ def fw_ddlerp(x, ab, Lb, Rb, bb):
     D = Rb.shape[2]
     m = th.empty(B, T, 4 * D, dtype=th.bfloat16, device=x.device)
     y = th.empty(4, B, T, C, dtype=th.bfloat16, device=x.device)
-    rc = _lib.lib().wkv7_ddlerp_fwd(x.data_ptr(), ab.data_ptr(), Lb.data_ptr(), Rb.data_ptr(), bb.data_ptr(),
-                                    m.data_ptr(), y.data_ptr(), B, T, C, D, _lib.stream_of(x))
+    with _lib.on_device(x, ab, Lb, Rb, bb):
+        rc = _lib.lib().wkv7_ddlerp_fwd(x.data_ptr(), ab.data_ptr(), Lb.data_ptr(), Rb.data_ptr(), bb.data_ptr(),
+                                        m.data_ptr(), y.data_ptr(), B, T, C, D, _lib.stream_of(x))
     _lib.check(rc, 'wkv7_ddlerp_fwd')
     return m, y
 
@@ -33,10 +34,11 @@ def bw_ddlerp(x, ab, Lb, Rb, bb, m, dy0, dy1, dy2, dy3):
     dL = th.empty(4 * D, C, dtype=th.float32, device=dev)
     dR = th.empty(4, C, D, dtype=th.float32, device=dev)
     dbeta = th.empty(4, 1, 1, C, dtype=th.float32, device=dev)
-    rc = _lib.lib().wkv7_ddlerp_bwd(x.data_ptr(), ab.data_ptr(), Lb.data_ptr(), Rb.data_ptr(), bb.data_ptr(),
-                                    m.data_ptr(), dy0.data_ptr(), dy1.data_ptr(), dy2.data_ptr(), dy3.data_ptr(),
-                                    dpre.data_ptr(), dx.data_ptr(), dalpha.data_ptr(), dL.data_ptr(), dR.data_ptr(),
-                                    dbeta.data_ptr(), B, T, C, D, _lib.stream_of(x))
+    with _lib.on_device(x, ab, Lb, Rb, bb, m, dy0, dy1, dy2, dy3):
+        rc = _lib.lib().wkv7_ddlerp_bwd(x.data_ptr(), ab.data_ptr(), Lb.data_ptr(), Rb.data_ptr(), bb.data_ptr(),
+                                        m.data_ptr(), dy0.data_ptr(), dy1.data_ptr(), dy2.data_ptr(), dy3.data_ptr(),
+                                        dpre.data_ptr(), dx.data_ptr(), dalpha.data_ptr(), dL.data_ptr(), dR.data_ptr(),
+                                        dbeta.data_ptr(), B, T, C, D, _lib.stream_of(x))
     _lib.check(rc, 'wkv7_ddlerp_bwd')
     return dx, dalpha, dL, dR, dbeta
 

@@ -14,7 +14,8 @@ def fw_loras(w_in, k_in, z_in, a_in, ma_in, mk_in, Wz, Wa, Wma, Wmk, w_bias, a_b
     D = z_in.shape[2]
     ins = [w_in, k_in, z_in, a_in, ma_in, mk_in, Wz, Wa, Wma, Wmk, w_bias, a_bias, ma_bias, mk_bias]
     outs = [th.empty_like(w_in) for _ in range(4)]
-    rc = _lib.lib().wkv7_expand_loras_fwd(*[i.data_ptr() for i in ins + outs], B, T, C, D, _lib.stream_of(w_in))
+    with _lib.on_device(*ins):
+        rc = _lib.lib().wkv7_expand_loras_fwd(*[i.data_ptr() for i in ins + outs], B, T, C, D, _lib.stream_of(w_in))
     _lib.check(rc, 'wkv7_expand_loras_fwd')
     return tuple(outs)
 
@@ -31,8 +32,9 @@ def bw_loras(w_in, k_in, z_in, a_in, ma_in, mk_in, Wz, Wa, Wma, Wmk, w_bias, a_b
     dW = [th.empty(C, D, dtype=th.float32, device=dev) for _ in range(4)]
     dbias = [th.empty(C, dtype=th.float32, device=dev) for _ in range(4)]
     ws = th.empty(_lib.lib().wkv7_expand_loras_bwd_workspace_bytes(B, T, C, D), dtype=th.uint8, device=dev)
-    rc = _lib.lib().wkv7_expand_loras_bwd(*[i.data_ptr() for i in acts + pb + [dw, dk, dkk, db] + dact + dW + dbias],
-                                          ws.data_ptr(), B, T, C, D, _lib.stream_of(w_in))
+    with _lib.on_device(*acts, *pb, dw, dk, dkk, db):
+        rc = _lib.lib().wkv7_expand_loras_bwd(*[i.data_ptr() for i in acts + pb + [dw, dk, dkk, db] + dact + dW + dbias],
+                                              ws.data_ptr(), B, T, C, D, _lib.stream_of(w_in))
     _lib.check(rc, 'wkv7_expand_loras_bwd')
     return tuple(dact + dW + dbias)
 
