@@ -190,7 +190,7 @@ int wkv7_ddlerp_bwd(const void* x, const void* alpha, const void* L, const void*
  * expand_loras: second-stage LoRA expansion producing (w, k, kk, b) for the mixer.  Replaces
  * fw_triton_ (wind_rwkv/rwkv7/rwkv7_expand_loras.py:32-89) behind ExpandLoras.forward (:215-231).
  * All tensors bf16, contiguous: w_in,k_in [B,T,C]; z_in,a_in,ma_in,mk_in [B,T,D]; W* [C,D];
- * biases [C]; outputs [B,T,C].  Head size 64 (C % 64 == 0), T % 16 == 0, D in {16,32,64}.
+ * biases [C]; outputs [B,T,C].  Head size 64 (C % 64 == 0), T % 16 == 0, D in {16,32,64,128}.
  *   w = -softplus(-(w_bias+w_in)) - 0.5 ;  z = tanh(z_in)@Wz^T + k_in ;  kk = z/||z||_head
  *   a, ma, mk = sigmoid(x_in@W^T + bias) ;  k = k_in*(ma+a-ma*a)*exp(w*mk) ;  b = -kk*a
  */

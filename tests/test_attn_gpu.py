@@ -203,34 +203,39 @@ def test_bf16_arithmetic_on_fp32_outputs(dist, fwd_impl):
 
 
 def test_strong_decay(fwd_impl):
-    """Decays far stronger than the workload's.  (a) w ~ N(0.5, 1) cut at 1.6: per-step decays down to e^-5, chunk
-    products down to e^-70, the range in which the kernels are exact; normal tolerances, except dw, whose
-    large cancelling terms leave it near 5e-2 here.  (b) w ~ N(1, 1): a third of the chunks have a channel whose
-    16-step decay product leaves fp32's useful range (below e^-80); the kernels then floor the per-step
-    log-decays of that chunk at -5, which bounds the error (measured 5e-2 on y; an unbounded product gave errors
-    of several times the RMS), and everything stays finite.  RWKV-7 itself cannot produce either: w <= -0.5."""
+    """Decays far stronger than the workload's.  Inside a chunk the kernels work with the running decay product and its
+    reciprocal; they keep both inside fp32's range by a power-of-two shift of the product (exact) and a floor of -7.75
+    on the per-step log-decay -exp(w).  (a) w ~ N(0.5, 1) cut at 2.0 (per-step decays down to e^-7.4, chunk products
+    down to e^-110): no floor acts, normal tolerances except for dw, whose large cancelling terms leave it near 6e-2.
+    (b) w ~ N(1, 1), uncut: 15 % of the steps are at the floor (they multiply the state by e^-7.75 = 4e-4 instead of
+    less); the stated 2e-2 still holds for everything but dw.  RWKV-7 itself cannot produce either: w <= -0.5."""
     if fwd_impl == 0:
         pytest.skip('one run is enough')
     gen = th.Generator().manual_seed(13)
     B, T, H = 2, 256, 2
-    w = (th.randn(B, T, H * N, generator=gen) + 0.5).clamp(max=1.6)
+    w = (th.randn(B, T, H * N, generator=gen) + 0.5).clamp(max=2.0)
     errs = _single_tf32_on_fp32_outputs(B, T, H, 13, 'baseline', w=w)
     for k, v in errs.items():
-        assert v <= (8e-2 if k == 'dw' else 2e-2), f'{k}: {v:.2e}'
+        assert v <= (0.1 if k == 'dw' else 2e-2), f'{k}: {v:.2e}'
     w = th.randn(B, T, H * N, generator=gen) + 1.0
     errs = _single_tf32_on_fp32_outputs(B, T, H, 13, 'baseline', w=w)
-    for k in ('y', 'sT', 'dr', 'dk', 'dv'):
-        assert errs[k] <= 0.15, f'{k}: {errs[k]:.2e}'
-    # the same inputs through the bf16 kernels (tcgen05 forward): finite, same bound on y
+    for k, v in errs.items():
+        assert v <= (0.5 if k == 'dw' else 2e-2), f'{k}: {v:.2e}'
+    # the same inputs through the bf16 kernels (tcgen05 forward) and the fp32 kernels
     c_oracle, _lib, attn, synthetic, _ = _mods()
-    d = synthetic.wkv7_inputs(B, T, H, N, seed=13, dtype=th.bfloat16, device='cuda')
-    ins = [d[n].requires_grad_() for n in NAMES]
-    ins[1] = w.to(th.bfloat16).cuda().requires_grad_()
-    y = attn(*ins, N)
-    y.backward(d['dy'])
-    assert bool(th.isfinite(y).all()) and all(bool(th.isfinite(x.grad).all()) for x in ins)
-    yo, _ = c_oracle.wkv7_fwd(*[x.detach().double().cpu().numpy().reshape(B, T, H, N) for x in ins])
-    assert maxabs_rms(y.view(B, T, H, N), yo) <= 0.15
+    for dtype in (th.bfloat16, th.float32):
+        d = synthetic.wkv7_inputs(B, T, H, N, seed=13, dtype=dtype, device='cuda')
+        ins = [d[n].requires_grad_() for n in NAMES]
+        ins[1] = w.to(dtype).cuda().requires_grad_()
+        y, sT = attn(*ins, N, return_state=True)
+        y.backward(d['dy'])
+        assert bool(th.isfinite(y).all()) and all(bool(th.isfinite(x.grad).all()) for x in ins)
+        yo, sTo = c_oracle.wkv7_fwd(*[x.detach().double().cpu().numpy().reshape(B, T, H, N) for x in ins])
+        if dtype == th.bfloat16:
+            check('y', y.view(B, T, H, N), yo, dtype)
+            assert maxabs_rms(sT, sTo) <= 2e-2
+        else:  # the floor's own effect: e^-7.75 of a channel's content per floored step
+            assert maxabs_rms(y.view(B, T, H, N), yo) <= 5e-3 and maxabs_rms(sT, sTo) <= 5e-3   # measured 2e-3
 
 
 def test_bounded_wait_gives_up_and_reports(fwd_impl):

@@ -55,6 +55,10 @@ def test_rank64():
     run_case(1, 64, 128, 64, seed=3)
 
 
+def test_rank128():
+    run_case(1, 64, 128, 128, seed=5)
+
+
 def test_mixer_shape():
     """C = 768, D = 16 as in the time mixer (tests/test_expand_loras.py:48-52), batch 2."""
     run_case(2, 1024, 768, 16, seed=4)

@@ -296,7 +296,7 @@ int wkv7_attn_ln_bwd_static(const void* r, const void* w, const void* k, const v
 static int ddlerp_check(int64_t B, int64_t T, int64_t C, int64_t D) {
     if (B < 0 || T < 0 || C <= 0 || D <= 0) return WKV7_ERR_SHAPE;
     if (C % 64 != 0) return WKV7_ERR_CHUNK;
-    if (D != 16 && D != 32 && D != 64) return WKV7_ERR_SHAPE;
+    if (D != 16 && D != 32 && D != 64) return WKV7_ERR_SHAPE;  // rank 128: the backward's resident L and R blocks exceed shared memory
     return WKV7_OK;
 }
 
@@ -343,7 +343,7 @@ int wkv7_ddlerp_bwd(const void* x, const void* alpha, const void* L, const void*
 static int loras_check(int64_t B, int64_t T, int64_t C, int64_t D) {
     if (B < 0 || T < 0 || C <= 0 || D <= 0) return WKV7_ERR_SHAPE;
     if (T % 16 != 0 || C % 64 != 0) return WKV7_ERR_CHUNK;
-    if (D != 16 && D != 32 && D != 64) return WKV7_ERR_SHAPE;
+    if (D != 16 && D != 32 && D != 64 && D != 128) return WKV7_ERR_SHAPE;
     return WKV7_OK;
 }
 

@@ -439,6 +439,7 @@ int launch_loras_fwd(const LorasParams& p, cudaStream_t stream) {
         case 16: return launch_loras_fwd_t<16>(p, stream);
         case 32: return launch_loras_fwd_t<32>(p, stream);
         case 64: return launch_loras_fwd_t<64>(p, stream);
+        case 128: return launch_loras_fwd_t<128>(p, stream);
         default: return kBadShape;
     }
 }
@@ -447,6 +448,7 @@ int launch_loras_bwd(const LorasParams& p, cudaStream_t stream) {
         case 16: return launch_loras_bwd_t<16>(p, stream);
         case 32: return launch_loras_bwd_t<32>(p, stream);
         case 64: return launch_loras_bwd_t<64>(p, stream);
+        case 128: return launch_loras_bwd_t<128>(p, stream);
         default: return kBadShape;
     }
 }

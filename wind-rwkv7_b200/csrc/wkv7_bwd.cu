@@ -220,6 +220,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
     const long long bi = bh / p.H, hi = bh % p.H;
     const long long base = bi * p.st.b + hi * p.st.h;
     const int nchunks = (int)((p.T + L - 1) / L);  // the last chunk may be partial: its missing rows read as zeros
+    const bool has_tail = (p.T % L) != 0;
     const IoT* gin[5] = {(const IoT*)p.r + base, (const IoT*)p.w + base, (const IoT*)p.k + base,
                          (const IoT*)p.a + base, (const IoT*)p.b + base};
     const IoT* gv = (const IoT*)p.v + base;
@@ -262,8 +263,9 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
         for (int i = tid; i < 5 * L * CH; i += THREADS) {
             const int ten = i / (L * CH), row = (i / CH) % L, ch = i % CH;
             const long long tt = (long long)c * L + row;
-            cp_async16_zfill(sm.st_in[ten] + Lay::at(row, ch * (16 / (int)sizeof(IoT))),
+            if (has_tail) cp_async16_zfill(sm.st_in[ten] + Lay::at(row, ch * (16 / (int)sizeof(IoT))),
                              reinterpret_cast<const unsigned char*>(gin[ten] + (tt < p.T ? tt : p.T - 1) * p.st.t) + ch * 16, tt < p.T);
+            else cp_async16(sm.st_in[ten] + Lay::at(row, ch * (16 / (int)sizeof(IoT))), reinterpret_cast<const unsigned char*>(gin[ten] + tt * p.st.t) + ch * 16);
         }
     };
     auto issue_vdy = [&](int c, int s) {
@@ -272,7 +274,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
             const long long tt = (long long)c * L + row;
             const IoT* src = (ten == 0 ? gv : ten == 1 ? gdy : gg) + (tt < p.T ? tt : p.T - 1) * p.st.t;
             unsigned char* dst = (ten == 0 ? sm.st_v[s] : ten == 1 ? sm.st_dy[s] : sm.st_g[LN ? s : 0]) + Lay::at(row, ch * (16 / (int)sizeof(IoT)));
-            cp_async16_zfill(dst, reinterpret_cast<const unsigned char*>(src) + ch * 16, tt < p.T);
+            if (has_tail) cp_async16_zfill(dst, reinterpret_cast<const unsigned char*>(src) + ch * 16, tt < p.T);
+            else cp_async16(dst, reinterpret_cast<const unsigned char*>(src) + ch * 16);
         }
     };
     // the checkpoint record of chunk c: its start state and its four 16x16 matrices (QK, QB, AK, AI), which the
@@ -315,7 +318,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
             if (d) {
                 float2 lo = *reinterpret_cast<const float2*>(d + (16 * warp + g) * N + 8 * nt + 2 * t4);
                 float2 hi2 = *reinterpret_cast<const float2*>(d + (16 * warp + g + 8) * N + 8 * nt + 2 * t4);
-                dS[nt][0] = lo.x; dS[nt][1] = lo.y; dS[nt][2] = hi2.x; dS[nt][3] = hi2.y;
+                // the state gradient is carried as 2^64 dS, the counterpart of the forward's S~ = 2^-64 S (see ANCHOR_LN)
+                dS[nt][0] = lo.x * STATE_UNSCALE; dS[nt][1] = lo.y * STATE_UNSCALE; dS[nt][2] = hi2.x * STATE_UNSCALE; dS[nt][3] = hi2.y * STATE_UNSCALE;
             } else {
                 dS[nt][0] = dS[nt][1] = dS[nt][2] = dS[nt][3] = 0.f;
             }
@@ -397,8 +401,9 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
         auto du_dv = [&]() {
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
-                const float2 f = *reinterpret_cast<const float2*>(sm.fw + 8 * nt + 2 * t4);
-                dS[nt][0] *= f.x; dS[nt][1] *= f.y; dS[nt][2] *= f.x; dS[nt][3] *= f.y;
+                const float2 f = *reinterpret_cast<const float2*>(sm.fw + 8 * nt + 2 * t4);  // P~_L = 2^64 P_L
+                dS[nt][0] = dS[nt][0] * STATE_SCALE * f.x; dS[nt][1] = dS[nt][1] * STATE_SCALE * f.y;
+                dS[nt][2] = dS[nt][2] * STATE_SCALE * f.x; dS[nt][3] = dS[nt][3] * STATE_SCALE * f.y;
             }
 #pragma unroll
             for (int sb = 0; sb < 2; ++sb)
@@ -822,11 +827,11 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int i = e + 2 * hrow;
-                    const float incl = exp_p<PREC>(fmaxf(cuv[e], -80.f));
+                    const float incl = decay_up<PREC>(cuv[e]);   // P~_t, as the scan formed it
                     const float inv = rcp_p<PREC>(incl);
                     // P_{t-1} = exp(cum_{t-1}) with cum_{t-1} = cum_t - lw_t (0 for the first row): an exponential on the idle
                     // special-function unit instead of two shuffles for the row above
-                    const float non = exp_p<PREC>(fmaxf(cuv[e] - lwa[e], -80.f));
+                    const float non = decay_up<PREC>(cuv[e] - lwa[e]);
                     o_a[e] = non * DA[nt][i];
                     o_q[e] = incl * DQ[nt][i];
                     o_b[e] = inv * DB[nt][i];
@@ -939,8 +944,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
         float* o = p.ds0 + bh * N * N;
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
-            *reinterpret_cast<float2*>(o + (16 * warp + g) * N + 8 * nt + 2 * t4) = make_float2(dS[nt][0], dS[nt][1]);
-            *reinterpret_cast<float2*>(o + (16 * warp + g + 8) * N + 8 * nt + 2 * t4) = make_float2(dS[nt][2], dS[nt][3]);
+            *reinterpret_cast<float2*>(o + (16 * warp + g) * N + 8 * nt + 2 * t4) = make_float2(dS[nt][0] * STATE_SCALE, dS[nt][1] * STATE_SCALE);
+            *reinterpret_cast<float2*>(o + (16 * warp + g + 8) * N + 8 * nt + 2 * t4) = make_float2(dS[nt][2] * STATE_SCALE, dS[nt][3] * STATE_SCALE);
         }
     }
 }

@@ -25,14 +25,23 @@ constexpr int CK_STATE = 0, CK_MATS = N * N;
 constexpr int CK_SC = CK_MATS, CK_AI = CK_SC + 2 * L * L, CK_QB = CK_AI + L * L;
 __host__ __device__ constexpr int ck_tile_at(int row, int chunk) { return (row >> 3) * 128 + chunk * 32 + (row & 7) * 4; }
 constexpr int CK_FLOATS = CK_QB + L * L;  // 5120 floats = 20 KB
-// Range of the decay within a chunk.  The kernels work with P_t and 1/P_t, the running decay product over up to 16
-// steps, and e^(+-80) is what fp32 holds with room for the other factors.  A chunk in which every channel keeps
-// P_16 >= e^-80 (always, for the decays RWKV-7 can produce: w <= -0.5, log P_16 >= -9.7) is computed exactly.  Where a
-// channel decays further within one chunk, the per-step log-decays -exp(w) of its 16-channel group are floored at -5 for
-// that chunk (a step that would multiply the state by less than e^-5 = 0.0067 multiplies it by e^-5), which keeps
-// P_16 >= e^-80 and the relative decay between any two steps of the chunk meaningful.
-constexpr float MIN_CHUNK_LOG_DECAY = -80.f;
-constexpr float MIN_STEP_LOG_DECAY = -5.f;
+// Range of the decay within a chunk.  The kernels factor the decay between two steps of a chunk as P_t * (1 / P_s), with
+// P_t the running decay product since the chunk start: over 16 steps of strong decay P_t leaves what fp32 holds.  Two
+// measures keep every chunk inside, without a data-dependent branch:
+//  * the products are kept as P~_t = 2^64 P_t and 1 / P~_t, so that both use the exponent range on either side of 1
+//    (P~ from 2^64 down to e^-80, its reciprocal from 2^-64 up to e^80); every formula of the chunked algorithm is invariant
+//    under P -> 2^64 P when the state is carried as S~ = 2^-64 S and its gradient as 2^64 dS (power-of-two scalings,
+//    exact): initial states are scaled on the way in, final states and state gradients on the way out, and the
+//    checkpoints hold S~;
+//  * the per-step log-decay -exp(w) has a floor of -7.75 (16 * 7.75 = 124 = 80 + 64 ln 2): a step that would multiply the
+//    state by less than e^-7.75 = 4.3e-4 (w > 2.05) multiplies it by e^-7.75.  RWKV-7 parameterises w <= -0.5 (per-step
+//    log-decay >= -0.61) and never comes near it; N(-0.6, 0.5^2) inputs reach it at 5.3 sigma.
+constexpr float ANCHOR_LN = 44.361419555836498f;      // 64 ln 2
+constexpr float ANCHOR_LOG2 = 64.f;
+constexpr float STATE_SCALE = 5.421010862427522e-20f;  // 2^-64
+constexpr float STATE_UNSCALE = 18446744073709551616.f;  // 2^64
+constexpr float MIN_CUM_LOG_DECAY = -(80.f + ANCHOR_LN);
+constexpr float MIN_STEP_LOG_DECAY = -7.75f;
 
 // ---- status codes (mirrored in include/wkv7_sm100.h) -------------------------------------
 enum Status : int {
@@ -222,6 +231,12 @@ __device__ __forceinline__ float rcp_mufu(float x) {
 // exp() and 1/x by precision class: MUFU for the single-TF32 class, libdevice for the fp32 class.
 template <int PREC> __device__ __forceinline__ float exp_p(float x) { return PREC == 3 ? expf(x) : exp_mufu(x); }
 template <int PREC> __device__ __forceinline__ float rcp_p(float x) { return PREC == 3 ? 1.f / x : rcp_mufu(x); }
+// P~ = 2^64 exp(c) for a running log-decay c <= 0 (clamped at MIN_CUM_LOG_DECAY).  fp32 class: exact power-of-two scaling
+// of expf(c) wherever that has not underflowed.
+template <int PREC> __device__ __forceinline__ float decay_up(float c) {
+    if (PREC == 3) return c >= -80.f ? expf(c) * STATE_UNSCALE : expf(fmaxf(c, MIN_CUM_LOG_DECAY) + ANCHOR_LN);
+    return exp_mufu(c + ANCHOR_LN);  // exp_mufu clamps its argument at -80
+}
 
 // ---- decay scan (state-independent chunk preparation, shared by forward and backward) ----------
 // 8 consecutive IO elements (16 or 32 bytes) -> floats
@@ -280,7 +295,7 @@ __device__ __forceinline__ void decay_scan(const unsigned char* tq, const unsign
     load8<IoT>(ta + off, a);
     load8<IoT>(tb + off, b);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) lw[i] = row < live ? -exp_p<PREC>(lw[i]) : 0.f;
+    for (int i = 0; i < 8; ++i) lw[i] = row < live ? fmaxf(-exp_p<PREC>(lw[i]), MIN_STEP_LOG_DECAY) : 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) cum[i] = lw[i];
 #pragma unroll
@@ -290,39 +305,20 @@ __device__ __forceinline__ void decay_scan(const unsigned char* tq, const unsign
             const float up = __shfl_up_sync(0xffffffffu, cum[i], d, 16);
             if (row >= d) cum[i] += up;
         }
-    {
-        // the chunk's total log-decay sits in row 15; out of range for some channel of this warp (never, for decays
-        // RWKV-7 can produce): floor the steps and scan again
-        bool deep = false;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) deep |= cum[i] < MIN_CHUNK_LOG_DECAY;
-        if (__any_sync(0xffffffffu, deep && row == 15)) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) cum[i] = lw[i] = fmaxf(lw[i], MIN_STEP_LOG_DECAY);
-#pragma unroll
-            for (int d = 1; d < 16; d <<= 1)
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float up = __shfl_up_sync(0xffffffffu, cum[i], d, 16);
-                    if (row >= d) cum[i] += up;
-                }
-        }
-    }
     // P_t from one exp (argument clamped so that P_t and 1/P_t stay finite), 1/P_t from a reciprocal.
     float o[4][8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const float cc = fmaxf(cum[i], -80.f);
-        const float incl = exp_p<PREC>(cc);
+        const float incl = decay_up<PREC>(cum[i]);   // P~_t
         const float inv = rcp_p<PREC>(incl);
         // P_{t-1} = exp(cum_t - lw_t) (row 0: exp(0) = 1): one more exponential on the idle special-function unit is
         // cheaper here than fetching the row above with a shuffle
-        const float non = exp_p<PREC>(fmaxf(cum[i] - lw[i], -80.f));
+        const float non = decay_up<PREC>(cum[i] - lw[i]);
         o[0][i] = pre<PREC>(q[i] * incl);
         o[1][i] = pre<PREC>(a[i] * non);
         o[2][i] = pre<PREC>(k[i] * inv);
         o[3][i] = pre<PREC>(b[i] * inv);
-        if (row == 15) fw[j0 + i] = incl;
+        if (row == 15) fw[j0 + i] = incl;  // P~_16 = 2^64 P_16: users multiply by it first and by 2^-64 afterwards
     }
     const int at = row * OPS + xcol<X>(row, j0);
     const bool flip = (row >> 2) & 1;

@@ -12,6 +12,7 @@
 // Per chunk (rows = time, P_t = prod_{s<=t} exp(-exp(w_s)) per key channel, S0 = state at the
 // chunk start, S[value][key]):
 //     wq = q*P_t     wa = a*P_{t-1}     kwi = k/P_t     bwi = b/P_t     fw = P_L
+// (in the code P_t is kept as 2^64 P_t and the state as 2^-64 S, which leaves every formula as it is: see ANCHOR_LN)
 //     QK = tril(wq kwi^T)  QB = tril(wq bwi^T)  AK = stril(wa kwi^T)  AB = stril(wa bwi^T)
 //     X = AK V + wa S0^T ;  U = (I-AB)^-1 X ;  Y = QK V + QB U + wq S0^T
 //     S' = (S0 + V^T kwi + U^T bwi) * fw[None,:]
@@ -61,6 +62,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
     const long long bi = bh / p.H, hi = bh % p.H;
     const long long base = bi * p.st.b + hi * p.st.h;
     const int nchunks = (int)((p.T + L - 1) / L);  // the last chunk may be partial: its missing rows read as zeros
+    const bool has_tail = (p.T % L) != 0;
     const IoT* gin[5] = {(const IoT*)p.r + base, (const IoT*)p.w + base, (const IoT*)p.k + base,
                          (const IoT*)p.a + base, (const IoT*)p.b + base};
     const IoT* gv = (const IoT*)p.v + base;
@@ -80,8 +82,9 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
         for (int i = tid; i < 5 * L * CH; i += THREADS) {
             int ten = i / (L * CH), row = (i / CH) % L, ch = i % CH;
             const long long tt = (long long)c * L + row;
-            cp_async16_zfill(sm.st_in[ten] + row * Lay::ROWB + ch * 16,
+            if (has_tail) cp_async16_zfill(sm.st_in[ten] + row * Lay::ROWB + ch * 16,
                              reinterpret_cast<const unsigned char*>(gin[ten] + (tt < p.T ? tt : p.T - 1) * p.st.t) + ch * 16, tt < p.T);
+            else cp_async16(sm.st_in[ten] + row * Lay::ROWB + ch * 16, reinterpret_cast<const unsigned char*>(gin[ten] + tt * p.st.t) + ch * 16);
         }
     };
     auto issue_v = [&](int c) {
@@ -91,7 +94,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
             const long long tt = (long long)c * L + row;
             const IoT* src = (ten == 0 ? gv : gg) + (tt < p.T ? tt : p.T - 1) * p.st.t;
             unsigned char* dst = (ten == 0 ? sm.st_v[s] : sm.st_g[LN ? s : 0]) + row * Lay::ROWB;
-            cp_async16_zfill(dst + ch * 16, reinterpret_cast<const unsigned char*>(src) + ch * 16, tt < p.T);
+            if (has_tail) cp_async16_zfill(dst + ch * 16, reinterpret_cast<const unsigned char*>(src) + ch * 16, tt < p.T);
+            else cp_async16(dst + ch * 16, reinterpret_cast<const unsigned char*>(src) + ch * 16);
         }
     };
     if (nchunks > 0) {
@@ -112,7 +116,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
             if (s0) {
                 float2 lo = *reinterpret_cast<const float2*>(s0 + (16 * warp + g) * N + 8 * nt + 2 * t4);
                 float2 hi2 = *reinterpret_cast<const float2*>(s0 + (16 * warp + g + 8) * N + 8 * nt + 2 * t4);
-                S[nt][0] = lo.x; S[nt][1] = lo.y; S[nt][2] = hi2.x; S[nt][3] = hi2.y;
+                // the state is carried as S~ = 2^-64 S (see ANCHOR_LN)
+                S[nt][0] = lo.x * STATE_SCALE; S[nt][1] = lo.y * STATE_SCALE; S[nt][2] = hi2.x * STATE_SCALE; S[nt][3] = hi2.y * STATE_SCALE;
             } else {
                 S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.f;
             }
@@ -341,8 +346,9 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
                 mma<PREC>(S[nt], vf[kk], fragB_kn<PREC, true>(sm.kwi, OPS, 8 * nt, 8 * kk, g, t4));
                 mma<PREC>(S[nt], ua[kk], fragB_kn<PREC, true>(sm.bwi, OPS, 8 * nt, 8 * kk, g, t4));
             }
-            const float2 f = *reinterpret_cast<const float2*>(sm.fw + 8 * nt + 2 * t4);
-            S[nt][0] *= f.x; S[nt][1] *= f.y; S[nt][2] *= f.x; S[nt][3] *= f.y;
+            const float2 f = *reinterpret_cast<const float2*>(sm.fw + 8 * nt + 2 * t4);  // P~_L = 2^64 P_L
+            S[nt][0] = S[nt][0] * f.x * STATE_SCALE; S[nt][1] = S[nt][1] * f.y * STATE_SCALE;
+            S[nt][2] = S[nt][2] * f.x * STATE_SCALE; S[nt][3] = S[nt][3] * f.y * STATE_SCALE;
         }
         cp_async_wait<0>();
         __syncthreads();  // (E) operand and score buffers are free again
@@ -358,8 +364,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
         float* sT = p.sT + bh * N * N;
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
-            *reinterpret_cast<float2*>(sT + (16 * warp + g) * N + 8 * nt + 2 * t4) = make_float2(S[nt][0], S[nt][1]);
-            *reinterpret_cast<float2*>(sT + (16 * warp + g + 8) * N + 8 * nt + 2 * t4) = make_float2(S[nt][2], S[nt][3]);
+            *reinterpret_cast<float2*>(sT + (16 * warp + g) * N + 8 * nt + 2 * t4) = make_float2(S[nt][0] * STATE_UNSCALE, S[nt][1] * STATE_UNSCALE);
+            *reinterpret_cast<float2*>(sT + (16 * warp + g + 8) * N + 8 * nt + 2 * t4) = make_float2(S[nt][2] * STATE_UNSCALE, S[nt][3] * STATE_UNSCALE);
         }
     }
 }

@@ -95,7 +95,7 @@ constexpr long long WAIT_LIMIT = MBAR_WAIT_LIMIT;
 
 struct Ctrl {
     uint64_t full[4], done[4], rdone[4], score[4], hop;
-    uint64_t drain[5];         // abort path only: completion of a thread's outstanding tensor-core work (chain, groups)
+    uint64_t drain;            // abort path only: completion of the chain thread's outstanding tensor-core work
     uint32_t tmem_base;
     volatile int abort;
     volatile int zero;         // stays 0: the abort-path drain waits with this in place of the abort flag
@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
             mbar_init(&ctrl->score[g], 1);
         }
         mbar_init(&ctrl->hop, 1);
-        for (int g = 0; g <= G; ++g) mbar_init(&ctrl->drain[g], 1);
+        mbar_init(&ctrl->drain, 1);
         ctrl->abort = 0;
         ctrl->zero = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -305,7 +305,8 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
             uint32_t v[16];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                const float4 x = s0 ? *reinterpret_cast<const float4*>(s0 + cb + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 x = s0 ? *reinterpret_cast<const float4*>(s0 + cb + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                x.x *= STATE_SCALE; x.y *= STATE_SCALE; x.z *= STATE_SCALE; x.w *= STATE_SCALE;  // the state is carried as S~ = 2^-64 S (see ANCHOR_LN)
                 v[4 * q] = __float_as_uint(x.x); v[4 * q + 1] = __float_as_uint(x.y); v[4 * q + 2] = __float_as_uint(x.z); v[4 * q + 3] = __float_as_uint(x.w);
                 if (ck) *reinterpret_cast<float4*>(ck + cb + 4 * q) = x;
             }
@@ -330,7 +331,6 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
             long long tacc[8] = {}, tprev = clock64();
 #endif
             for (int c = 0; c < nchunks; ++c) {
-                if (ctrl->abort) break;  // a wait of this CTA ran out: issue nothing more
                 const int g = c % G, k = c / G;
                 const uint32_t gb = sb + g * G_BYTES;
                 const uint64_t dWAQ = desc_kmajor(gb + G_WAQ, 2048), dSC = desc_kmajor(gb + G_SC, 512), dAI = desc_kmajor(gb + G_AI, 512),
@@ -378,7 +378,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                 tc_fence_after();
                 TCK(7)
             }
-            if (ctrl->abort) drain_tensor_work(&ctrl->drain[G], &ctrl->zero, p.status);
+            if (ctrl->abort) drain_tensor_work(&ctrl->drain, &ctrl->zero, p.status);
 #ifdef WKV7_TIMING
             if (blockIdx.x == 0)
                 printf("chain: loop %lld | wait full %lld | wait rdone %lld | issue hop1+decay %lld | wait hop1 %lld | hop2+kwf issue+wait %lld | issue hop3 %lld | wait last %lld (cycles per chunk)\n",
@@ -402,9 +402,14 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
             const long long goff = ((long long)c * L + (live ? r : 0)) * p.st.t;
             const int at = r * ROWB + ((seg ^ (r & 7)) << 4);
 #pragma unroll
-            for (int ten = 0; ten < 6; ++ten)
-                cp_async16_zfill(gs + G_RAW + ten * RAW_TILE + at, reinterpret_cast<const unsigned char*>(gin[ten] + goff) + seg * 16, live);
-            if (LN) cp_async16_zfill(gs + G_GRAW + gbuf * RAW_TILE + at, reinterpret_cast<const unsigned char*>(gg + goff) + seg * 16, live);
+            for (int ten = 0; ten < 6; ++ten) {
+                if (TAIL) cp_async16_zfill(gs + G_RAW + ten * RAW_TILE + at, reinterpret_cast<const unsigned char*>(gin[ten] + goff) + seg * 16, live);
+                else cp_async16(gs + G_RAW + ten * RAW_TILE + at, reinterpret_cast<const unsigned char*>(gin[ten] + goff) + seg * 16);
+            }
+            if (LN) {
+                if (TAIL) cp_async16_zfill(gs + G_GRAW + gbuf * RAW_TILE + at, reinterpret_cast<const unsigned char*>(gg + goff) + seg * 16, live);
+                else cp_async16(gs + G_GRAW + gbuf * RAW_TILE + at, reinterpret_cast<const unsigned char*>(gg + goff) + seg * 16);
+            }
             cp_async_commit();
         };
         // Results of own chunk number kk (chunk cc): Y^T into registers, the chunk-end state straight to the
@@ -540,6 +545,8 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                         tc_fence_before();
                         mbar_arrive(&ctrl->rdone[grp]);
                     }
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) sv[e] = __float_as_uint(__uint_as_float(sv[e]) * STATE_UNSCALE);  // S = 2^64 S~
                     if (lane < 16) {
 #pragma unroll
                         for (int q8 = 0; q8 < 2; ++q8)
@@ -586,7 +593,8 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                 }
                 // log2 of the per-step decay: -exp(w) * log2(e); running sum along the 16 time rows
 #pragma unroll
-                for (int i = 0; i < 8; ++i) cum[i] = ex2_approx(cum[i] * 1.4426950408889634f) * -1.4426950408889634f;
+                for (int i = 0; i < 8; ++i)  // with the per-step floor (see MIN_STEP_LOG_DECAY)
+                    cum[i] = fmaxf(ex2_approx(cum[i] * 1.4426950408889634f) * -1.4426950408889634f, MIN_STEP_LOG_DECAY * 1.4426950408889634f);  // log2 units
                 if (TAIL && c + 1 == nchunks && row >= tail) {  // a row beyond the end of the sequence: no decay, the state passes through
 #pragma unroll
                     for (int i = 0; i < 8; ++i) cum[i] = 0.f;
@@ -601,32 +609,15 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                         const float up = __shfl_up_sync(0xffffffffu, cum[i], d, 16);
                         if (row >= d) cum[i] += up;
                     }
-                {
-                    // a channel of this warp that decays by more than e^-80 over the chunk (total in row 15; never, for
-                    // decays RWKV-7 can produce): floor the per-step log-decays of the warp's channels at -5 and scan
-                    // again (see MIN_CHUNK_LOG_DECAY)
-                    bool deep = false;
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) deep |= cum[i] < MIN_CHUNK_LOG_DECAY * 1.4426950408889634f;
-                    if (__any_sync(0xffffffffu, deep && row == 15)) {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) cum[i] = step[i] = fmaxf(step[i], MIN_STEP_LOG_DECAY * 1.4426950408889634f);
-#pragma unroll
-                        for (int d = 1; d < 16; d <<= 1)
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const float up = __shfl_up_sync(0xffffffffu, cum[i], d, 16);
-                                if (row >= d) cum[i] += up;
-                            }
-                    }
-                }
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const float cc = fmaxf(cum[i], -115.f);  // keeps P_t and 1/P_t finite (2^-115 ~ e^-80)
+                    // P~_t = 2^64 P_t and its reciprocal (see ANCHOR_LN): both finite for cum >= -179 (2^-115 ~ e^-80)
+                    const float ca = cum[i] + ANCHOR_LOG2;
+                    const float cc = fmaxf(ca, -115.f);
                     const float incl = ex2_approx(cc);
                     const float inv = ex2_approx(-cc);
-                    const float non = ex2_approx(fmaxf(cum[i] - step[i], -115.f));
-                    const float fw = __shfl_sync(0xffffffffu, incl, 15, 16);
+                    const float non = ex2_approx(fmaxf(ca - step[i], -115.f));
+                    const float fw = __shfl_sync(0xffffffffu, incl, 15, 16);  // P~_L = 2^64 P_L (P_L itself may lie below fp32's normal range)
                     o[0][i] = q[i] * incl;   // wq
                     o[1][i] = a[i] * non;    // wa
                     o[2][i] = kk[i] * inv;   // kwi
@@ -653,7 +644,7 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                 store8t<RND>(gs + G_KB + kchunk(16 + row, jc, 2048), gs + G_KB + kchunk(16 + row, jc + 1, 2048), o[3]);
                 const int mo = (j0 >> 5) * 2048 + row * 128 + ((((j0 & 31) >> 3) ^ (row & 3)) << 5);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { o[2][i] *= fwv[i]; o[3][i] *= fwv[i]; }
+                for (int i = 0; i < 8; ++i) { o[2][i] = o[2][i] * fwv[i] * STATE_SCALE; o[3][i] = o[3][i] * fwv[i] * STATE_SCALE; }  // k P_L / P_t first, then 2^-64
                 const bool flip = (row >> 2) & 1;
                 store8mn<RND>(gs + G_KWF + mo, o[2], flip);
                 store8mn<RND>(gs + G_BWF + mo, o[3], flip);
@@ -661,7 +652,10 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                 if (row == 15) {
                     unsigned char* df = gs + G_DF + (j0 >> 3) * 256;
 #pragma unroll
-                    for (int n = 0; n < 8; ++n) *reinterpret_cast<float*>(df + (n >> 2) * 128 + n * 16 + (n & 3) * 4) = RND ? rnd(fwv[n]) : fwv[n];
+                    for (int n = 0; n < 8; ++n) {
+                        const float pl = fwv[n] * STATE_SCALE;  // P_L; where it underflows, so does S~ P_L
+                        *reinterpret_cast<float*>(df + (n >> 2) * 128 + n * 16 + (n & 3) * 4) = RND ? rnd(pl) : pl;
+                    }
                 }
             }
             fence_async_smem();
