@@ -38,8 +38,14 @@ __device__ __forceinline__ Gates lora_gates(float xa, float xm, float xk, float 
     return o;
 }
 
+constexpr int GLD = HC + 8;  // row stride (bf16) of the [token][channel] tiles: 4-byte accesses in the MMA fragment pattern
+                             // (rows g, columns 2 * t4) and 16-byte row accesses are both free of bank conflicts
 template <int D> struct LorasFwdSmem {
     bf16 W[4][HC][D + 8];  // [channel][rank]
+    // [token][channel] tiles of one head: w_in, k_in on the way in (16-byte cp.async, whole 128-byte rows), the four
+    // outputs on the way out (written in the fragment pattern, stored as whole rows).  Global accesses in the
+    // fragment pattern itself would touch 16 bytes per row and instruction.
+    bf16 io[4][64][GLD];
 };
 
 // A fragments of a [16, D] input block straight from global memory (rows r0+g, r0+g+8).
@@ -73,18 +79,26 @@ __global__ void __launch_bounds__(128) loras_fwd_kernel(LorasParams p) {
         const int l = i / (HC * (D / 8)), r = (i / (D / 8)) % HC, ch = i % (D / 8);
         cp_async16(&sm.W[l][r][ch * 8], (const bf16*)p.W[l] + (long long)(h * HC + r) * D + ch * 8);
     }
+    {   // this CTA's 64 tokens of w_in and k_in; rows past the end are filled with zeros
+        const long long t0 = (long long)blockIdx.y * 64;
+        for (int i = tid; i < 2 * 64 * 8; i += 128) {
+            const int ten = i / 512, r = (i / 8) % 64, ch = i % 8;
+            const bool live = t0 + r < p.rows;
+            const bf16* src = (const bf16*)(ten ? p.k_in : p.w_in) + (live ? t0 + r : 0) * C + h * HC + ch * 8;
+            cp_async16_zfill(&sm.io[ten][r][ch * 8], src, live);
+        }
+    }
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
     if (r0 >= p.rows) return;
+    const int lr = 16 * warp;  // this warp's first tile row
 
     uint32_t az[D / 16][4], aa[D / 16][4], am[D / 16][4], ak[D / 16][4];
     load_in_frags<D, true>(az, (const bf16*)p.lin[0], r0, g, t4);
     load_in_frags<D, false>(aa, (const bf16*)p.lin[1], r0, g, t4);
     load_in_frags<D, false>(am, (const bf16*)p.lin[2], r0, g, t4);
     load_in_frags<D, false>(ak, (const bf16*)p.lin[3], r0, g, t4);
-    const long long e0 = (r0 + g) * C + h * HC + 2 * t4, e1 = e0 + 8LL * C;  // element offsets of rows g, g+8
-
     float z[8][4];
     float ss0 = 0.f, ss1 = 0.f;
 #pragma unroll
@@ -96,8 +110,8 @@ __global__ void __launch_bounds__(128) loras_fwd_kernel(LorasParams p) {
             ldB_nk(b, &sm.W[0][0][0], D + 8, 8 * j, 16 * ks, g, t4);
             mma_bf16(z[j], az[ks], b);
         }
-        const float2 k0 = unpack_bf16x2(*reinterpret_cast<const uint32_t*>((const bf16*)p.k_in + e0 + 8 * j));
-        const float2 k1 = unpack_bf16x2(*reinterpret_cast<const uint32_t*>((const bf16*)p.k_in + e1 + 8 * j));
+        const float2 k0 = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(&sm.io[1][lr + g][8 * j + 2 * t4]));
+        const float2 k1 = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(&sm.io[1][lr + g + 8][8 * j + 2 * t4]));
         z[j][0] += k0.x; z[j][1] += k0.y; z[j][2] += k1.x; z[j][3] += k1.y;
         ss0 += z[j][0] * z[j][0] + z[j][1] * z[j][1];
         ss1 += z[j][2] * z[j][2] + z[j][3] * z[j][3];
@@ -123,9 +137,9 @@ __global__ void __launch_bounds__(128) loras_fwd_kernel(LorasParams p) {
         const float2 kb = unpack_bf16x2(*reinterpret_cast<const uint32_t*>((const bf16*)p.bias[2] + c));
 #pragma unroll
         for (int hrow = 0; hrow < 2; ++hrow) {
-            const long long e = (hrow ? e1 : e0) + 8 * j;
-            const float2 wi = unpack_bf16x2(*reinterpret_cast<const uint32_t*>((const bf16*)p.w_in + e));
-            const float2 ki = unpack_bf16x2(*reinterpret_cast<const uint32_t*>((const bf16*)p.k_in + e));
+            const int tr = lr + g + 8 * hrow, tc = 8 * j + 2 * t4;
+            const float2 wi = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(&sm.io[0][tr][tc]));
+            const float2 ki = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(&sm.io[1][tr][tc]));
             const float inorm = hrow ? in1 : in0;
             float ow[2], ok[2], okk[2], ob[2];
 #pragma unroll
@@ -139,21 +153,36 @@ __global__ void __launch_bounds__(128) loras_fwd_kernel(LorasParams p) {
                 okk[x] = kk;
                 ob[x] = -kk * gt.a;
             }
-            *reinterpret_cast<uint32_t*>((bf16*)p.w_out + e) = pack_bf16x2(ow[0], ow[1]);
-            *reinterpret_cast<uint32_t*>((bf16*)p.k_out + e) = pack_bf16x2(ok[0], ok[1]);
-            *reinterpret_cast<uint32_t*>((bf16*)p.kk_out + e) = pack_bf16x2(okk[0], okk[1]);
-            *reinterpret_cast<uint32_t*>((bf16*)p.b_out + e) = pack_bf16x2(ob[0], ob[1]);
+            // w and k replace w_in and k_in in their tiles (this thread's element, already read); kk and b get their own
+            *reinterpret_cast<uint32_t*>(&sm.io[0][tr][tc]) = pack_bf16x2(ow[0], ow[1]);
+            *reinterpret_cast<uint32_t*>(&sm.io[1][tr][tc]) = pack_bf16x2(ok[0], ok[1]);
+            *reinterpret_cast<uint32_t*>(&sm.io[2][tr][tc]) = pack_bf16x2(okk[0], okk[1]);
+            *reinterpret_cast<uint32_t*>(&sm.io[3][tr][tc]) = pack_bf16x2(ob[0], ob[1]);
         }
+    }
+    __syncwarp();
+    {   // the warp's 16 rows of the four outputs leave as whole 128-byte rows (live rows only)
+        bf16* outs[4] = {(bf16*)p.w_out, (bf16*)p.k_out, (bf16*)p.kk_out, (bf16*)p.b_out};
+#pragma unroll
+        for (int ten = 0; ten < 4; ++ten)
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+                const int r = lr + 4 * it + (lane >> 3), ch = lane & 7;
+                const long long row = (long long)blockIdx.y * 64 + r;
+                if (row < p.rows) *reinterpret_cast<uint4*>(outs[ten] + row * C + h * HC + ch * 8) = *reinterpret_cast<const uint4*>(&sm.io[ten][r][ch * 8]);
+            }
     }
 }
 
 // ------------------------------------------------------------------------------------------------
-constexpr int GLD = HC + 8;  // row stride (bf16) of the [token][channel] gradient tiles
 
 template <int D> struct LorasBwdSmem {
     bf16 W[4][HC][D + 8];        // [channel][rank]: B operand of the forward, [k][n] operand of d(input)
     bf16 in[4][64][D + 16];      // tanh(z_in), a_in, ma_in, mk_in; column D is all ones (bias gradient)
-    bf16 gr[5][64][GLD];         // pre-activation gradients of z, a, ma, mk, and dw_in, [token][channel]
+    // [token][channel] tiles of one head.  On the way in (16-byte cp.async, whole 128-byte rows) tiles 0..5 hold
+    // w_in, k_in, dw_out, dk_out, db_out, dkk_out.  Each thread replaces, element by element, what it has read: tiles
+    // 0..4 become the pre-activation gradients of z, a, ma, mk and dw_in (the gradient of w_in), tile 5 becomes dk_in.
+    bf16 gr[6][64][GLD];
 };
 
 template <int D>
@@ -201,12 +230,21 @@ __global__ void __launch_bounds__(128) loras_bwd_kernel(LorasParams p) {
             }
             *reinterpret_cast<uint4*>(&sm.in[l][r][ch * 8]) = v;
         }
+        {
+            const bf16* src6[6] = {(const bf16*)p.w_in, (const bf16*)p.k_in, (const bf16*)p.dw_out, (const bf16*)p.dk_out,
+                                   (const bf16*)p.db_out, (const bf16*)p.dkk_out};
+            for (int i = tid; i < 6 * 64 * 8; i += 128) {
+                const int ten = i / 512, r = (i / 8) % 64, ch = i % 8;
+                const bool live = t0 + r < T;
+                cp_async16_zfill(&sm.gr[ten][r][ch * 8], src6[ten] + (b0 + (live ? t0 + r : 0)) * C + h * HC + ch * 8, live);
+            }
+            cp_async_commit();
+        }
         cp_async_wait<0>();
         __syncthreads();
 
         if (valid) {
             const int lr = 16 * warp;  // first tile row of this warp
-            const long long e0 = (r0 + g) * C + h * HC + 2 * t4, e1 = e0 + 8LL * C;
             uint32_t az[D / 16][4], aa[D / 16][4], am[D / 16][4], ak[D / 16][4];
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
@@ -231,10 +269,10 @@ __global__ void __launch_bounds__(128) loras_bwd_kernel(LorasParams p) {
                 const float2 ab = unpack_bf16x2(*reinterpret_cast<const uint32_t*>((const bf16*)p.bias[0] + h * HC + 8 * j + 2 * t4));
 #pragma unroll
                 for (int hrow = 0; hrow < 2; ++hrow) {
-                    const long long e = (hrow ? e1 : e0) + 8 * j;
-                    const float2 ki = unpack_bf16x2(*reinterpret_cast<const uint32_t*>((const bf16*)p.k_in + e));
-                    const float2 dk = unpack_bf16x2(*reinterpret_cast<const uint32_t*>((const bf16*)p.dkk_out + e));
-                    const float2 db = unpack_bf16x2(*reinterpret_cast<const uint32_t*>((const bf16*)p.db_out + e));
+                    const int tr = lr + g + 8 * hrow, tc = 8 * j + 2 * t4;
+                    const float2 ki = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(&sm.gr[1][tr][tc]));
+                    const float2 dk = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(&sm.gr[5][tr][tc]));
+                    const float2 db = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(&sm.gr[4][tr][tc]));
 #pragma unroll
                     for (int x = 0; x < 2; ++x) {
                         const int i = 2 * hrow + x;
@@ -270,12 +308,12 @@ __global__ void __launch_bounds__(128) loras_bwd_kernel(LorasParams p) {
                 const float2 kb = unpack_bf16x2(*reinterpret_cast<const uint32_t*>((const bf16*)p.bias[2] + c));
 #pragma unroll
                 for (int hrow = 0; hrow < 2; ++hrow) {
-                    const long long e = (hrow ? e1 : e0) + 8 * j;
-                    const float2 wi = unpack_bf16x2(*reinterpret_cast<const uint32_t*>((const bf16*)p.w_in + e));
-                    const float2 ki = unpack_bf16x2(*reinterpret_cast<const uint32_t*>((const bf16*)p.k_in + e));
-                    const float2 gw = unpack_bf16x2(*reinterpret_cast<const uint32_t*>((const bf16*)p.dw_out + e));
-                    const float2 gk = unpack_bf16x2(*reinterpret_cast<const uint32_t*>((const bf16*)p.dk_out + e));
-                    const float2 gb = unpack_bf16x2(*reinterpret_cast<const uint32_t*>((const bf16*)p.db_out + e));
+                    const int tr = lr + g + 8 * hrow, tc = 8 * j + 2 * t4;
+                    const float2 wi = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(&sm.gr[0][tr][tc]));
+                    const float2 ki = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(&sm.gr[1][tr][tc]));
+                    const float2 gw = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(&sm.gr[2][tr][tc]));
+                    const float2 gk = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(&sm.gr[3][tr][tc]));
+                    const float2 gb = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(&sm.gr[4][tr][tc]));
                     float o_dw[2], o_dk[2], o_z[2], o_a[2], o_m[2], o_k[2];
 #pragma unroll
                     for (int x = 0; x < 2; ++x) {
@@ -301,9 +339,7 @@ __global__ void __launch_bounds__(128) loras_bwd_kernel(LorasParams p) {
                         o_m[x] = dma * ma * (1.f - ma);
                         o_k[x] = dmk * mk * (1.f - mk);
                     }
-                    *reinterpret_cast<uint32_t*>((bf16*)p.dw_in + e) = pack_bf16x2(o_dw[0], o_dw[1]);
-                    *reinterpret_cast<uint32_t*>((bf16*)p.dk_in + e) = pack_bf16x2(o_dk[0], o_dk[1]);
-                    const int tr = lr + g + 8 * hrow, tc = 8 * j + 2 * t4;
+                    *reinterpret_cast<uint32_t*>(&sm.gr[5][tr][tc]) = pack_bf16x2(o_dk[0], o_dk[1]);
                     *reinterpret_cast<uint32_t*>(&sm.gr[0][tr][tc]) = pack_bf16x2(o_z[0], o_z[1]);
                     *reinterpret_cast<uint32_t*>(&sm.gr[1][tr][tc]) = pack_bf16x2(o_a[0], o_a[1]);
                     *reinterpret_cast<uint32_t*>(&sm.gr[2][tr][tc]) = pack_bf16x2(o_m[0], o_m[1]);
@@ -312,6 +348,17 @@ __global__ void __launch_bounds__(128) loras_bwd_kernel(LorasParams p) {
                 }
             }
             __syncwarp();
+            {   // dw_in (tile 4) and dk_in (tile 5) of the warp's 16 rows leave as whole 128-byte rows (live rows only)
+#pragma unroll
+                for (int ten = 4; ten < 6; ++ten)
+#pragma unroll
+                    for (int it = 0; it < 4; ++it) {
+                        const int r = lr + 4 * it + (lane >> 3), ch = lane & 7;
+                        if (t0 + r < T)
+                            *reinterpret_cast<uint4*>((bf16*)(ten == 4 ? p.dw_in : p.dk_in) + (b0 + t0 + r) * C + h * HC + ch * 8) =
+                                *reinterpret_cast<const uint4*>(&sm.gr[ten][r][ch * 8]);
+                    }
+            }
             // ---- d(input) partial of this head: [16, D] = grad[16, 64] @ W[64, D] ----------------------------
 #pragma unroll
             for (int l = 0; l < 4; ++l) {

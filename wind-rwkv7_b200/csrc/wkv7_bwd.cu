@@ -34,9 +34,6 @@
 #include <cstring>
 
 #include "wkv7_kernels.h"
-#ifdef WKV7_TIMING
-#include <cstdio>
-#endif
 
 namespace wkv7 {
 
@@ -207,7 +204,9 @@ __device__ __forceinline__ void s0_wait(uint64_t* bar, uint32_t parity, volatile
     mbar_wait_bounded<false>(bar, parity, abort, status);
 }
 
-template <typename IoT, int PREC, bool LN>
+// TAIL: the sequence length is not a multiple of 16 (an instantiation of its own, so that whole-chunk sequences carry
+// none of the row tests).
+template <typename IoT, int PREC, bool LN, bool TAIL>
 __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __grid_constant__ OutMaps omaps) {
     using Lay = BwdLayout<IoT>;
     using Smem = BwdSmem<IoT, PREC, LN>;
@@ -220,7 +219,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
     const long long bi = bh / p.H, hi = bh % p.H;
     const long long base = bi * p.st.b + hi * p.st.h;
     const int nchunks = (int)((p.T + L - 1) / L);  // the last chunk may be partial: its missing rows read as zeros
-    const bool has_tail = (p.T % L) != 0;
+    constexpr bool has_tail = TAIL;
     const IoT* gin[5] = {(const IoT*)p.r + base, (const IoT*)p.w + base, (const IoT*)p.k + base,
                          (const IoT*)p.a + base, (const IoT*)p.b + base};
     const IoT* gv = (const IoT*)p.v + base;
@@ -272,7 +271,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
         for (int i = tid; i < (LN ? 3 : 2) * L * CH; i += THREADS) {
             const int ten = i / (L * CH), row = (i / CH) % L, ch = i % CH;
             const long long tt = (long long)c * L + row;
-            const IoT* src = (ten == 0 ? gv : ten == 1 ? gdy : gg) + (tt < p.T ? tt : p.T - 1) * p.st.t;
+            const IoT* src = (ten == 0 ? gv : ten == 1 ? gdy : gg) + (!TAIL || tt < p.T ? tt : p.T - 1) * p.st.t;
             unsigned char* dst = (ten == 0 ? sm.st_v[s] : ten == 1 ? sm.st_dy[s] : sm.st_g[LN ? s : 0]) + Lay::at(row, ch * (16 / (int)sizeof(IoT)));
             if (has_tail) cp_async16_zfill(dst, reinterpret_cast<const unsigned char*>(src) + ch * 16, tt < p.T);
             else cp_async16(dst, reinterpret_cast<const unsigned char*>(src) + ch * 16);
@@ -326,12 +325,6 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
         }
     }
 
-#ifdef WKV7_TIMING
-    long long tacc[10] = {}, tprev = clock64();
-#define TICK(i) { long long now_ = clock64(); tacc[i] += now_ - tprev; tprev = now_; }
-#else
-#define TICK(i)
-#endif
     // this thread's offsets into the chunk-start state: rows 16*warp + g (and + 8) at columns 2*t4 + 8*block, and
     // rows 2*t4 (and + 1) + 8*block at column 16*warp + g
     const float* const s0_mk = sm.S0s + s0_at(16 * warp + g, 2 * t4);
@@ -358,7 +351,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
         {
             decay_scan<IoT, PREC, 1, Lay::SWZ>(sm.st_in[0], sm.st_in[1], sm.st_in[2], sm.st_in[3], sm.st_in[4], Lay::ROWB, sm.wq, sm.wa,
                                   sm.kwi, sm.bwi, sm.fw, sm.cum, PREC == 3 ? sm.lw : nullptr, warp, lane,
-                                  (int)min((long long)L, p.T - (long long)c * L));
+                                  TAIL ? (int)min((long long)L, p.T - (long long)c * L) : L);
             if (LN) {  // bonus dot  sum_j r_j k_j bonus_j  per time step: 8 threads per row
                 const int row = tid >> 3, part = tid & 7;
                 float acc = 0.f;
@@ -373,11 +366,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                 if (part == 0) sm.bdot[row] = acc;
             }
         }
-        TICK(0)
         if (TMA_OUT && !LN) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // previous chunk's output tiles have been read
         __syncthreads();  // (A)
-        TICK(1)
-
         if (c > 0) {
             issue_in(c - 1);
             issue_vdy(c - 1, vs ^ 1);
@@ -430,9 +420,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
             }
         };
         if (!LN) du_dv();
-        TICK(2)
         if (LN) s0_wait(&sm.s0_bar, it & 1, &sm.abort, p.status);
-        TICK(3)
         float U[2][4] = {};
         float dvx[2][4] = {};  // LN: bonus-term contribution to dv
         {
@@ -594,7 +582,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                     const int row = lane >> 1, hf = lane & 1;
                     const uint4* src = reinterpret_cast<const uint4*>(sc + row * Lay::YS + 8 * hf);
                     uint4* dst = reinterpret_cast<uint4*>(gdg + ((long long)c * L + row) * p.st.t + 16 * warp + 8 * hf);
-                    if ((long long)c * L + row < p.T) {
+                    if (!TAIL || (long long)c * L + row < p.T) {
                         dst[0] = src[0];
                         if (sizeof(IoT) == 4) dst[1] = src[1];
                     }
@@ -674,7 +662,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
             const int row = lane >> 1, hf = lane & 1;
             const uint4* src = reinterpret_cast<const uint4*>(sc + row * Lay::YS + 8 * hf);
             uint4* dst = reinterpret_cast<uint4*>(gdv + ((long long)c * L + row) * p.st.t + 16 * warp + 8 * hf);
-            if ((long long)c * L + row < p.T) {
+            if (!TAIL || (long long)c * L + row < p.T) {
                 dst[0] = src[0];
                 if (sizeof(IoT) == 4) dst[1] = src[1];
             }
@@ -730,11 +718,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
             const int nt_own = (b2 ? 1 : 0) + (b1 ? 2 : 0) + (b0 ? 4 : 0);
             *reinterpret_cast<float2*>(&sm.Gp[it & 1][warp][8 * nt_own + 2 * t4]) = make_float2(gp[0], gp[1]);
         }
-        TICK(4)
         if (TMA_OUT && LN) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // dg's tile lies where stage C writes the score gradients
         __syncthreads();  // (C1)
-        TICK(5)
-
         // ---------------- stage C: contractions over the value index --------------------------
         float DA[2][4] = {}, DQ[2][4] = {}, DB[2][4] = {}, DK[2][4] = {};
         {
@@ -773,9 +758,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                     make_float2(keep(g + 8, s) ? pre<PREC>(d[nt][2]) : 0.f, keep(g + 8, s + 1) ? pre<PREC>(d[nt][3]) : 0.f);
             }
         }
-        TICK(6)
         __syncthreads();  // (C2) score gradients visible; S0s free
-        TICK(7)
         if (c > 0) issue_s0(c - 1);
         cp_async_commit();
 
@@ -797,8 +780,6 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                 mma<PREC>(DK[nt], tAK, ba); mma<PREC>(DK[nt], tQK, bq);
             }
         }
-
-        TICK(8)
         // ---------------- epilogue: thread holds rows g, g+8 x key columns n0+2*t4, +1 ---------
         float outv[5][2][2][2];  // [dq, dw, dk, da, db][tile][row half][column]
 #pragma unroll
@@ -893,7 +874,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
 #pragma unroll
             for (int hrow = 0; hrow < 2; ++hrow) {
                 const long long off = ((long long)c * L + g + 8 * hrow) * p.st.t + 16 * warp;
-                const bool live = (long long)c * L + g + 8 * hrow < p.T;  // uniform over the lanes that exchange values
+                const bool live = !TAIL || (long long)c * L + g + 8 * hrow < p.T;  // uniform over the lanes that exchange values
 #pragma unroll
                 for (int ten = 0; ten < 5; ++ten)
                     store_quad(gout[ten] + off, outv[ten][0][hrow][0], outv[ten][0][hrow][1], outv[ten][1][hrow][0], outv[ten][1][hrow][1], t4, live);
@@ -908,15 +889,8 @@ __global__ void __launch_bounds__(THREADS) wkv7_bwd_kernel(BwdParams p, const __
                              ::"l"(&omaps.m[ten]), "r"(0), "r"((int)hi), "r"(c * L), "r"((int)bi), "r"(smem_u32(ten < 5 ? sm.out_tiles() + ten * 2048 : sm.dv_tile())) : "memory");
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
-        TICK(9)
     }
     if (TMA_OUT) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory must outlive the last stores
-#ifdef WKV7_TIMING
-    if (blockIdx.x == 0 && lane == 0)
-        printf("bwd warp %d: P1 %lld | syncA %lld | du/dV %lld | s0 wait %lld | stageB %lld | syncC1 %lld | Ca %lld | syncC2 %lld | Cb %lld | epi+syncE %lld\n", warp,
-               tacc[0] / nchunks, tacc[1] / nchunks, tacc[2] / nchunks, tacc[3] / nchunks, tacc[4] / nchunks, tacc[5] / nchunks, tacc[6] / nchunks,
-               tacc[7] / nchunks, tacc[8] / nchunks, tacc[9] / nchunks);
-#endif
 
     if (LN) {
         // per-(batch, head) partial parameter gradients: ws[b][0..2][h*N + channel]
@@ -1016,7 +990,7 @@ static bool encode_bthn_map(CUtensorMap* m, void* base, long long B, long long T
 
 template <typename IoT, int PREC, bool LN> static int launch_bwd_t(const BwdParams& p, cudaStream_t stream) {
     using Smem = BwdSmem<IoT, PREC, LN>;
-    auto kern = wkv7_bwd_kernel<IoT, PREC, LN>;
+    auto kern = p.T % L ? wkv7_bwd_kernel<IoT, PREC, LN, true> : wkv7_bwd_kernel<IoT, PREC, LN, false>;
     const int smem = (int)sizeof(Smem);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return kLaunchFailed;

@@ -136,9 +136,7 @@ template <int PREC> __device__ __forceinline__ FragA<PREC> fragA_from_acc(const 
 //   XOR-ing the column with 8 for rows 4..7 of every block of 8 rows separates them.
 // X = 2, for unpadded 64-float rows: the column is XOR-ed with 8 * ((row ^ (row >> 2)) & 3), which gives
 //   rows g = 0..3, rows g = 4..7, rows 0,2,4,6 and rows 1,3,5,7 four different values each, so both
-//   patterns are conflict-free.  (Tried on the backward's state buffers, which cp.async fills and which
-//   it fills with fewer wavefronts when rows are 128-byte aligned; the extra address arithmetic in the
-//   inner loops cost more than that saved, so they stay padded with X = 1.)
+//   patterns are conflict-free.
 // Groups of 8 floats stay contiguous under both.  X = 0: plain layout.
 template <int X> __device__ __forceinline__ int xcol(int row, int col) {
     return X == 1 ? (col ^ ((row & 4) << 1)) : X == 2 ? (col ^ (((row ^ (row >> 2)) & 3) << 3)) : col;
@@ -185,13 +183,11 @@ __device__ __forceinline__ FragB<PREC> fragB_kn(const float* p, int ld, int n0, 
     return f;
 }
 
-// exp(x) on the FMA and integer pipes only.  Measured on B200, one MUFU (ex2 / rcp) warp
-// instruction occupies its pipe for roughly as long as fifteen FMA-pipe instructions, and these
-// kernels need up to four exponentials per input element, so the special-function unit was their
-// bottleneck.  2^t with t = x*log2(e): round(t) goes into the exponent field (the low mantissa bits
-// of t + 1.5*2^23 are round(t); shifted left by 23 they land on the exponent, the constant's own
-// bits fall off the top), the fraction in [-0.5, 0.5] through a degree-5 polynomial (relative
-// error 2e-6, far below TF32 operand rounding).  x is clamped to [-80, 80].
+// exp(x) on the FMA and integer pipes only (for kernels whose special-function unit is the busier pipe: expand_loras,
+// with seven transcendentals per element, splits them between the two).  2^t with t = x*log2(e): round(t) goes into the
+// exponent field (the low mantissa bits of t + 1.5*2^23 are round(t); shifted left by 23 they land on the exponent, the
+// constant's own bits fall off the top), the fraction in [-0.5, 0.5] through a degree-5 polynomial (relative error 2e-6,
+// far below TF32 operand rounding).  x is clamped to [-80, 80].
 __device__ __forceinline__ float exp_poly(float x) {
     const float t = fminf(fmaxf(x, -80.f), 80.f) * 1.4426950408889634f;
     const float tm = t + 12582912.f;
@@ -212,12 +208,8 @@ __device__ __forceinline__ float rcp_newton(float x) {
     y = y * fmaf(-x, y, 2.f);
     return y;
 }
-// The same two functions on the special-function unit (one MUFU instruction each, relative error
-// about 2^-22).  Which version is cheaper depends on what else a kernel puts on the XU pipe: the
-// polynomial versions were introduced when TF32 conversions (cvt.rna, also XU) and four to five
-// MUFU operations per element saturated it; with integer TF32 rounding the pipe is idle in the WKV7
-// kernels (ncu: 0.004 % in the backward) and three MUFU operations per element replace ~45 FMA-pipe
-// and integer instructions.  expand_loras, with seven transcendentals per element, keeps its mix.
+// The same two functions on the special-function unit (one MUFU instruction each, relative error about 2^-22): what the
+// WKV7 kernels use, whose XU pipe is otherwise idle (TF32 rounding is done with integer instructions).
 __device__ __forceinline__ float exp_mufu(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(fminf(fmaxf(x, -80.f), 80.f) * 1.4426950408889634f));

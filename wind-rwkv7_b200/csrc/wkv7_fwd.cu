@@ -16,13 +16,8 @@
 //     QK = tril(wq kwi^T)  QB = tril(wq bwi^T)  AK = stril(wa kwi^T)  AB = stril(wa bwi^T)
 //     X = AK V + wa S0^T ;  U = (I-AB)^-1 X ;  Y = QK V + QB U + wq S0^T
 //     S' = (S0 + V^T kwi + U^T bwi) * fw[None,:]
-// Inputs are fetched one chunk ahead with 16-byte cp.async copies issued by all threads (an
-// earlier version issued one bulk-async copy per 128-byte row; at 96 requests per chunk the
-// request rate of the copy engine, about 120 cycles each, was the bottleneck).
+// Inputs are fetched one chunk ahead with 16-byte cp.async copies issued by all threads.
 #include "wkv7_kernels.h"
-#ifdef WKV7_TIMING
-#include <cstdio>
-#endif
 
 namespace wkv7 {
 
@@ -124,12 +119,6 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
         }
     }
 
-#ifdef WKV7_TIMING
-    long long tacc[8] = {}, tprev = clock64();
-#define TICK(i) { long long now_ = clock64(); tacc[i] += now_ - tprev; tprev = now_; }
-#else
-#define TICK(i)
-#endif
     for (int c = 0; c < nchunks; ++c) {
         // ---------------- P1: decay scan and scaled operands ------------------------------------
         {
@@ -149,17 +138,12 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
                 if (part == 0) sm.bdot[row] = acc;
             }
         }
-        TICK(0)
         __syncthreads();  // (A)
-        TICK(1)
-
         if (c + 1 < nchunks) {
             issue_in(c + 1);
             issue_v(c + 1);
         }
         cp_async_commit();
-
-        TICK(2)
         // ---------------- P2: masked score matrices, one per warp ------------------------------
         {
             const float* Am = (warp & 1) ? sm.wa : sm.wq;
@@ -195,8 +179,6 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
             __syncwarp();
             if (lane < L) tri_inverse_column<PREC>(sm.AB, sm.AI, lane);
         }
-
-        TICK(3)
         // ---------------- chain, part 1: needs only S and the scaled operands ------------------
         if (p.ckpt) {
             float* ck = p.ckpt + (bh * nchunks + c) * (long long)CK_FLOATS;
@@ -216,10 +198,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
             for (int nt = 0; nt < 4; ++nt)
                 mma<PREC>(XY[nt], a, fragB_nk<PREC, true>(nt < 2 ? sm.wa : sm.wq, OPS, 8 * (nt & 1), 8 * kk, g, t4));
         }
-
-        TICK(4)
         __syncthreads();  // (B) scores and AI visible
-        TICK(5)
         if (p.ckpt) {  // the chunk's four 16x16 matrices go into the checkpoint record: 8 floats per thread
             float* ck = p.ckpt + (bh * nchunks + c) * (long long)CK_FLOATS;
             const int m = tid >> 5, r = (tid & 31) >> 1, hf = tid & 1;
@@ -336,8 +315,6 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
                 if (sizeof(IoT) == 4) dst[1] = src[1];
             }
         }
-
-        TICK(6)
         // ---------------- state update -----------------------------------------------------------
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
@@ -352,13 +329,7 @@ __global__ void __launch_bounds__(THREADS) wkv7_fwd_kernel(FwdParams p) {
         }
         cp_async_wait<0>();
         __syncthreads();  // (E) operand and score buffers are free again
-        TICK(7)
     }
-#ifdef WKV7_TIMING
-    if (blockIdx.x == 0 && (lane == 0))
-        printf("warp %d: P1 %lld | syncA %lld | issue %lld | P2P3 %lld | ckpt+step1 %lld | syncB %lld | steps2-5 %lld | step6+syncE %lld  (cycles per chunk)\n", warp,
-               tacc[0] / nchunks, tacc[1] / nchunks, tacc[2] / nchunks, tacc[3] / nchunks, tacc[4] / nchunks, tacc[5] / nchunks, tacc[6] / nchunks, tacc[7] / nchunks);
-#endif
 
     if (p.sT) {
         float* sT = p.sT + bh * N * N;

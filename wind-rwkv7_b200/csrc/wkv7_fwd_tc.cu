@@ -51,13 +51,6 @@
 #include <cstring>
 
 #include "wkv7_kernels.h"
-#ifdef WKV7_TIMING
-#include <cstdio>
-#define TCK(i) { long long now_ = clock64(); tacc[i] += now_ - tprev; tprev = now_; }
-#else
-#define TCK(i)
-#endif
-
 namespace wkv7 {
 namespace tc {
 
@@ -327,9 +320,6 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
         if (warp == 4 * G + 3 && elect_one()) {
             const uint32_t sb = smem_u32(sm);
             uint32_t hop_phase = 0;
-#ifdef WKV7_TIMING
-            long long tacc[8] = {}, tprev = clock64();
-#endif
             for (int c = 0; c < nchunks; ++c) {
                 const int g = c % G, k = c / G;
                 const uint32_t gb = sb + g * G_BYTES;
@@ -337,13 +327,10 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                                dQB = desc_kmajor(gb + G_QB, 512), dDF = desc_kmajor(gb + G_DF, 256);
                 const uint64_t dV = desc_mnmajor(gb + G_V), dKWF = desc_mnmajor(gb + G_KWF), dBWF = desc_mnmajor(gb + G_BWF);
                 const uint32_t Sa = tmem + C_S + 64 * (c & 1), Sn = tmem + C_S + 64 * ((c + 1) & 1), XY = tmem + C_XY + 32 * (c & 1), U = tmem + C_U;
-                TCK(0)
                 mbar_wait<true>(&ctrl->full[g], k & 1, ctrl, p.status);
-                TCK(1)
                 // the Y buffer and the state buffer about to be overwritten were last read for chunk c-2
                 if (c > 1) mbar_wait<true>(&ctrl->rdone[(c - 2) % G], ((c - 2) / G) & 1, ctrl, p.status);
                 tc_fence_after();
-                TCK(2)
                 // hop 1
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) mma_ts(XY, Sa + 8 * ks, dWAQ + (uint64_t)(ks * 16), idesc(32, false, false), ks > 0);
@@ -353,10 +340,8 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                 // the decay of the old state goes into the other buffer while hop 1 drains
 #pragma unroll
                 for (int s = 0; s < 8; ++s) mma_ts(Sn + 8 * s, Sa + 8 * s, dDF + (uint64_t)(s * 16), idesc(8, false, false), 0);
-                TCK(3)
                 mbar_wait<false>(&ctrl->hop, hop_phase++ & 1, ctrl, p.status);
                 tc_fence_after();
-                TCK(4)
                 // hop 2
 #pragma unroll
                 for (int ks = 0; ks < 2; ++ks) mma_ts(U, XY + 8 * ks, dAI + (uint64_t)(ks * 16), idesc(16, false, false), ks > 0);
@@ -365,7 +350,6 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                 for (int ks = 0; ks < 2; ++ks) mma_ss(Sn, dV + (uint64_t)(ks * 64), dKWF + (uint64_t)(ks * 64), idesc(64, true, true), 1);
                 mbar_wait<false>(&ctrl->hop, hop_phase++ & 1, ctrl, p.status);
                 tc_fence_after();
-                TCK(5)
                 // hop 3 and the U part of the state update
 #pragma unroll
                 for (int ks = 0; ks < 2; ++ks) mma_ts(XY + 16, U + 8 * ks, dQB + (uint64_t)(ks * 16), idesc(16, false, false), 1);
@@ -373,17 +357,10 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                 for (int ks = 0; ks < 2; ++ks) mma_ts(Sn, U + 8 * ks, dBWF + (uint64_t)(ks * 64), idesc(64, false, true), 1);
                 tc_commit(&ctrl->done[g]);
                 tc_commit(&ctrl->hop);
-                TCK(6)
                 mbar_wait<false>(&ctrl->hop, hop_phase++ & 1, ctrl, p.status);  // S' is the next chunk's A operand
                 tc_fence_after();
-                TCK(7)
             }
             if (ctrl->abort) drain_tensor_work(&ctrl->drain, &ctrl->zero, p.status);
-#ifdef WKV7_TIMING
-            if (blockIdx.x == 0)
-                printf("chain: loop %lld | wait full %lld | wait rdone %lld | issue hop1+decay %lld | wait hop1 %lld | hop2+kwf issue+wait %lld | issue hop3 %lld | wait last %lld (cycles per chunk)\n",
-                       tacc[0] / nchunks, tacc[1] / nchunks, tacc[2] / nchunks, tacc[3] / nchunks, tacc[4] / nchunks, tacc[5] / nchunks, tacc[6] / nchunks, tacc[7] / nchunks);
-#endif
         }
         __syncwarp();
     } else {
@@ -562,14 +539,10 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
         const int row = lane & 15, j0 = 16 * wg + 8 * (lane >> 4);
         if (grp < nchunks) issue_raw(grp, 0);
         int k = 0, cprev = -1;
-#ifdef WKV7_TIMING
-        long long tacc[10] = {}, tprev = clock64();
-#endif
         for (int c = grp; c < nchunks; c += G, ++k) {
             cp_async_wait<0>();
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the matrix copy of the previous own chunk (its issuer only)
             group_bar(grp);
-            TCK(0)
             // ---------------- decay scan, into registers ---------------------------------------------
             // One thread = one time step x 8 adjacent key channels.  The three transcendentals per
             // element go to the special-function unit: with the matrix products on tcgen05 the FMA
@@ -625,7 +598,6 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                     fwv[i] = fw;
                 }
             }
-            TCK(1)
             // ---------------- results of the previous own chunk (its operand tiles are free afterwards) --
             if (cprev >= 0) {
                 read_results(cprev, k - 1);
@@ -634,7 +606,6 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                     group_bar(grp);
                 }
             }
-            TCK(2)
             // ---------------- operand tiles -----------------------------------------------------------
             {
                 const int jc = j0 >> 2;
@@ -669,8 +640,6 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                 tc_commit(&ctrl->score[grp]);
             }
             __syncwarp();
-            TCK(3)
-            TCK(4)
             if (wg < 2) {
                 mbar_wait<true>(&ctrl->score[grp], k & 1, ctrl, p.status);
                 tc_fence_after();
@@ -678,7 +647,6 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                 tmem_ld16(tlane + C_SCORE + 32 * grp, sv);
                 tmem_ld16(tlane + C_SCORE + 32 * grp + 16, sv + 16);
                 tmem_ld_wait();
-                TCK(5)
                 const int t = lane;
                 if (wg == 0) {
                     // lane t: row t of AK (strictly lower) and of AB (strictly lower, kept transposed for the inverse)
@@ -716,7 +684,6 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
                     }
                 }
             }
-            TCK(6)
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(&ctrl->full[grp]);
@@ -743,11 +710,6 @@ __global__ void __launch_bounds__(128 * (G + 1), 1) wkv7_fwd_tc_kernel(FwdParams
             read_results(cprev, k - 1);
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // ... and the last state copy
         }
-#ifdef WKV7_TIMING
-        if (blockIdx.x == 0 && lane == 0 && k > 0)
-            printf("group %d warp %d: load wait %lld | scan %lld | results %lld | tiles+bar+prefetch+score issue %lld | y store %lld | score wait %lld | P2 %lld (cycles per own chunk)\n",
-                   grp, wg, tacc[0] / k, tacc[1] / k, tacc[2] / k, tacc[3] / k, tacc[4] / k, tacc[5] / k, tacc[6] / k);
-#endif
     }
 
     tc_fence_before();
