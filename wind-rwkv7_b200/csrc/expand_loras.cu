@@ -17,21 +17,16 @@ namespace wkv7 {
 
 constexpr int HC = 64;  // channels per head
 
-// The gates of one element.  Nine transcendental evaluations in the textbook form; here seven,
-// split over two pipes because the special-function unit is the bottleneck of this op on B200: the
-// three sigmoids share ONE reciprocal (1/(pa*pm*pk), arguments clamped to +-25 so the product stays
-// finite), softplus is exp + log2, and three of the five exponentials run as polynomials on the
-// FMA pipe.   a, ma, mk = sigmoid(xa, xm, xk);  w = -softplus(-v) - 0.5;  E = exp(w * mk).
+// The gates of one element:  a, ma, mk = sigmoid(xa, xm, xk);  w = -softplus(-v) - 0.5;  E = exp(w * mk).
+// Six special-function instructions (three tanh for the sigmoids, ex2 + lg2 for the softplus, ex2 for E) and one
+// exponential as a polynomial on the FMA pipe: the op is bound by issue slots, and the textbook forms (expf, a
+// division per sigmoid) cost three to four times the instructions.
 struct Gates { float a, ma, mk, w, E, ev; };  // ev = exp(-v) (for the backward: sigmoid(-v) = ev / (1 + ev))
 __device__ __forceinline__ Gates lora_gates(float xa, float xm, float xk, float v) {
     Gates o;
-    const float pa = 1.f + exp_poly(-fminf(fmaxf(xa, -25.f), 25.f));
-    const float pm = 1.f + exp_poly(-fminf(fmaxf(xm, -25.f), 25.f));
-    const float pk = 1.f + __expf(-fminf(fmaxf(xk, -25.f), 25.f));
-    const float r = __fdividef(1.f, pa * pm * pk);
-    o.a = r * pm * pk;
-    o.ma = r * pa * pk;
-    o.mk = r * pa * pm;
+    o.a = sigmoid_f(xa);
+    o.ma = sigmoid_f(xm);
+    o.mk = sigmoid_f(xk);
     o.ev = exp_poly(-v);  // exp_poly clamps its argument to +-80
     o.w = -0.6931471805599453f * __log2f(1.f + o.ev) - 0.5f;
     o.E = __expf(o.w * o.mk);
@@ -277,7 +272,7 @@ __global__ void __launch_bounds__(128) loras_bwd_kernel(LorasParams p) {
                     for (int x = 0; x < 2; ++x) {
                         const int i = 2 * hrow + x;
                         z[j][i] += x ? ki.y : ki.x;
-                        const float a = rcp_newton(1.f + exp_poly(-fminf(fmaxf(fa[i] + (x ? ab.y : ab.x), -25.f), 25.f)));
+                        const float a = sigmoid_f(fa[i] + (x ? ab.y : ab.x));
                         dzo[j][i] = (x ? dk.y : dk.x) - (x ? db.y : db.x) * a;  // gradient of kk
                         ss[hrow] += z[j][i] * z[j][i];
                         dn[hrow] += dzo[j][i] * z[j][i];
@@ -332,7 +327,7 @@ __global__ void __launch_bounds__(128) loras_bwd_kernel(LorasParams p) {
                         const float da = -(x ? gb.y : gb.x) * kk + dkE * (kin - kin * ma);
                         const float in3 = inorm[hrow] * inorm[hrow] * inorm[hrow];
                         const float dz = dzo[j][i] * inorm[hrow] - in3 * dn[hrow] * zz;
-                        o_dw[x] = dwt * gt.ev * rcp_newton(1.f + gt.ev);  // * sigmoid(-v)
+                        o_dw[x] = dwt * sigmoid_f(-v);
                         o_dk[x] = dkE * kmix + dz;
                         o_z[x] = dz;
                         o_a[x] = da * a * (1.f - a);
