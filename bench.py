@@ -479,6 +479,8 @@ def run_ours(args):
                     ol = other_line(wl, None, 5, 3)
                     sec[wl] = {'workload': ol['config']['workload'], 'value': ol['value'], 'unit': ol['unit'], 'ms_per_step': ol['ms_per_step'],
                                'roofline_frac': None if ol['roofline'] is None else ol['roofline']['frac'], 'steps': 5}
+                    if 'cuda_graph' in ol:
+                        sec[wl]['cuda_graph'] = ol['cuda_graph']
                 except Exception as e:
                     sec[wl] = {'error': repr(e)[:200]}
                 th.cuda.empty_cache()
@@ -580,6 +582,33 @@ def other_line(wl, batch, steps, warmup):
         e1.record()
         th.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
+    # The small ops are launch-bound in eager mode (a step is a dozen launches of 25-250 us behind Python autograd code):
+    # the same step captured once in a CUDA graph and replayed shows what the kernels take without the host in the way.
+    graph_ms = None
+    if gouts is not None:
+        try:
+            side = th.cuda.Stream()
+            side.wait_stream(th.cuda.current_stream())
+            with th.cuda.stream(side):
+                step()
+            th.cuda.current_stream().wait_stream(side)
+            graph = th.cuda.CUDAGraph()
+            with th.cuda.graph(graph):
+                step()
+            for _ in range(3):
+                graph.replay()
+            th.cuda.synchronize()
+            g0, g1 = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
+            g0.record()
+            for _ in range(args.steps):
+                graph.replay()
+            g1.record()
+            th.cuda.synchronize()
+            graph_ms = g0.elapsed_time(g1) / args.steps
+            del graph
+        except Exception as e:  # capture is an extra: report why it was not possible and keep the eager number
+            graph_ms = None
+            graph_err = repr(e)[:160]
     peak, which = hbm_peak()
     line = {'metric': name + ', Mtokens/s', 'value': tokens / (ms * 1e-3) / 1e6, 'unit': 'Mtokens/s', 'n_gpus': 1,
             'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms, 'higher_is_better': True,
@@ -588,6 +617,10 @@ def other_line(wl, batch, steps, warmup):
                                                    'frac': alg / (ms * 1e-3) / 1e9 / peak, 'peak_source': which,
                                                    'algorithmic_bytes': alg, 'note': 'whole step (all kernels of the op, forward and backward)'},
             'clocks': clocks.summary()}
+    if gouts is not None:
+        line['cuda_graph'] = ({'ms_per_step': graph_ms, 'value': tokens / (graph_ms * 1e-3) / 1e6,
+                               'roofline_frac': None if alg is None else alg / (graph_ms * 1e-3) / 1e9 / peak}
+                              if graph_ms else {'unavailable': graph_err})
     return line
 
 
