@@ -59,6 +59,11 @@ def test_rank128():
     run_case(1, 64, 128, 128, seed=5)
 
 
+def test_sequence_length_not_a_multiple_of_16():
+    """T = 40: padded to 48 inside the wrapper; outputs, input gradients and weight gradients as for any other length."""
+    run_case(2, 40, 128, 16, seed=6)
+
+
 def test_mixer_shape():
     """C = 768, D = 16 as in the time mixer (tests/test_expand_loras.py:48-52), batch 2."""
     run_case(2, 1024, 768, 16, seed=4)

@@ -73,6 +73,30 @@ def test_config3_shape_runs_and_matches_oracle_on_a_slice():
         assert p.grad is not None and bool(th.isfinite(p.grad).all()), n
 
 
+def test_sequence_length_not_a_multiple_of_16():
+    """The whole layer at T = 100 (upstream's kernels need T % 16 == 0): output and input gradient against the fp32
+    oracle."""
+    import wkv7_ref
+    from wind_rwkv.rwkv7 import TimeMixer
+    th.manual_seed(1)
+    model = TimeMixer(Config(12, 2, 128), 3).cuda()
+    with th.no_grad():
+        for n, p in model.named_parameters():
+            p.add_(th.randn_like(p) * 0.02)
+        model.Wo.normal_(std=0.02)
+    x = th.randn(3, 100, 128, device='cuda').requires_grad_()
+    y = model(x)
+    dy = th.randn_like(y)
+    y.backward(dy)
+    pc = {n: p.detach().cpu() for n, p in model.named_parameters()}
+    xc = x.detach().cpu().requires_grad_()
+    yr = wkv7_ref.ref_time_mixer(pc, xc, 2)
+    yr.backward(dy.float().cpu())
+    assert y.shape == (3, 100, 128)
+    assert rel_l2(y, yr.detach().numpy()) <= 2e-2
+    assert rel_l2(x.grad, xc.grad.numpy()) <= 2e-2
+
+
 def test_other_backends_are_refused():
     from wind_rwkv.rwkv7 import TimeMixer, attn_triton
     with pytest.raises(ValueError):

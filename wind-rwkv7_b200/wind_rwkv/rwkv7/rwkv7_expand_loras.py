@@ -2,6 +2,8 @@
 (`expand_loras(w_in,k_in,z_in,a_in,ma_in,mk_in, Wz,Wa,Wma,Wmk, w_bias,a_bias,ma_bias,mk_bias, HEAD_SIZE)
  -> (w, k, kk, b)`).  As upstream (:217-218) the rank-D inputs are made contiguous and the weights and
 biases are cast to bf16; their gradients come back in fp32 and autograd casts them to the parameter dtype.
+Any sequence length: the kernels take whole 16-token groups, other lengths are zero-padded here (upstream's kernel
+walks 16-token tiles as well, rwkv7_expand_loras.py:75-76, and is only ever called with T % 16 == 0).
 """
 import torch as th
 
@@ -60,28 +62,37 @@ class ExpandLoras(th.autograd.Function):
     def forward(ctx, w_in, k_in, z_in, a_in, ma_in, mk_in, Wz, Wa, Wma, Wmk, w_bias, a_bias, ma_bias, mk_bias, HEAD_SIZE):
         if HEAD_SIZE != _lib.HEAD_SIZE:
             raise ValueError(f'only HEAD_SIZE == {_lib.HEAD_SIZE} is built, got {HEAD_SIZE}')
+        T = w_in.shape[1]
+        pad = (-T) % 16
         acts = [i.contiguous() for i in [w_in, k_in, z_in, a_in, ma_in, mk_in]]
+        if pad:  # the kernels work on whole 16-token groups of a sequence: zero rows are appended (one copy) and cut again
+            acts = [th.nn.functional.pad(i, (0, 0, 0, pad)) for i in acts]
         params = [Wz, Wa, Wma, Wmk, w_bias, a_bias, ma_bias, mk_bias]
         pb = [i.detach().to(th.bfloat16).contiguous() for i in params]
         if not th.compiler.is_compiling():
             _lib.require_cuda(*acts, *pb)
             assert all(i.dtype == th.bfloat16 for i in acts), 'activations must be bfloat16'
-            B, T, C = w_in.shape
+            B, _, C = w_in.shape
             D = z_in.shape[2]
-            assert all(list(i.shape) == [B, T, C] for i in acts[:2]) and all(list(i.shape) == [B, T, D] for i in acts[2:])
+            assert all(list(i.shape) == [B, T + pad, C] for i in acts[:2]) and all(list(i.shape) == [B, T + pad, D] for i in acts[2:])
             assert all(list(i.shape) == [C, D] for i in pb[:4]) and all(list(i.shape) == [C] for i in pb[4:])
-            assert T % 16 == 0 and C % HEAD_SIZE == 0
+            assert C % HEAD_SIZE == 0
         outs = _lib.call(_fw_op, fw_loras, *acts, *pb)
         ctx.save_for_backward(*acts, *pb)
         ctx.param_dtypes = [i.dtype for i in params]
-        return tuple(outs)
+        ctx.seq_len, ctx.pad = T, pad
+        return tuple(o[:, :T] for o in outs) if pad else tuple(outs)
 
     @staticmethod
     def backward(ctx, dw_out, dk_out, dz_out, db_out):
         saved = ctx.saved_tensors
-        douts = [th.zeros_like(saved[0]) if d is None else d.to(th.bfloat16).contiguous() for d in (dw_out, dk_out, dz_out, db_out)]
+        douts = [None if d is None else d.to(th.bfloat16) for d in (dw_out, dk_out, dz_out, db_out)]
+        if ctx.pad:
+            douts = [None if d is None else th.nn.functional.pad(d, (0, 0, 0, ctx.pad)) for d in douts]
+        douts = [th.zeros_like(saved[0]) if d is None else d.contiguous() for d in douts]
         grads = _lib.call(_bw_op, bw_loras, *saved, *douts)
-        grads = list(grads[:6]) + [g.to(t) for g, t in zip(grads[6:], ctx.param_dtypes)]
+        acts_g = [g[:, :ctx.seq_len] for g in grads[:6]] if ctx.pad else list(grads[:6])
+        grads = acts_g + [g.to(t) for g, t in zip(grads[6:], ctx.param_dtypes)]
         return (*grads, None)
 
 
