@@ -474,7 +474,7 @@ def run_ours(args):
             del host_in, host_out, dev_in
             th.cuda.empty_cache()
             sec = {}
-            for wl in ('attn_ln', 'prefill', 'ddlerp', 'expand_loras', 'mixer'):
+            for wl in ('attn_ln', 'prefill', 'prefill_b1', 'ddlerp', 'expand_loras', 'mixer'):
                 try:
                     ol = other_line(wl, None, 5, 3)
                     sec[wl] = {'workload': ol['config']['workload'], 'value': ol['value'], 'unit': ol['unit'], 'ms_per_step': ol['ms_per_step'],
@@ -527,6 +527,14 @@ def other_line(wl, batch, steps, warmup):
         gouts = None
         tokens, alg = B * Tn, B * Tn * Hn * 7 * N * 2
         name = f'WKV7 prefill forward B{B} T{Tn} H{Hn} N{N} bf16, s0 -> sT (config 4)'
+    elif wl == 'prefill_b1':  # one sequence of a 12-head model: 12 chains for 148 SMs; the sequence runs as 16 parallel segments
+        B, Tn, Hn = 1, 65536, 12
+        d = synthetic.wkv7_inputs(B, Tn, Hn, N, seed=4, dtype=bf, device=dev, s0_std=0.1)
+        ins = [d[n] for n in 'rwkvab']
+        fwd = lambda: attn(*ins, N, s0=d['s0'], return_state=True, time_split=16)[0]
+        gouts = None
+        tokens, alg = B * Tn, B * Tn * Hn * 7 * N * 2
+        name = f'WKV7 prefill forward B{B} T{Tn} H{Hn} N{N} bf16, s0 -> sT, time_split=16'
     elif wl == 'ddlerp':
         B, Tn, C, D = args.batch if args.batch != B_PER_GPU else 32, 1024, 768, 32
         x = rn(B, Tn, C).to(bf).requires_grad_()
@@ -617,6 +625,18 @@ def other_line(wl, batch, steps, warmup):
                                                    'frac': alg / (ms * 1e-3) / 1e9 / peak, 'peak_source': which,
                                                    'algorithmic_bytes': alg, 'note': 'whole step (all kernels of the op, forward and backward)'},
             'clocks': clocks.summary()}
+    if wl == 'prefill_b1':  # the same sequence as one chain per head, for comparison
+        with th.no_grad():
+            one = lambda: attn(*ins, N, s0=d['s0'], return_state=True)
+            one()
+            th.cuda.synchronize()
+            u0, u1 = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
+            u0.record()
+            for _ in range(3):
+                one()
+            u1.record()
+            th.cuda.synchronize()
+        line['unsplit_ms_per_step'] = u0.elapsed_time(u1) / 3
     if gouts is not None:
         line['cuda_graph'] = ({'ms_per_step': graph_ms, 'value': tokens / (graph_ms * 1e-3) / 1e6,
                                'roofline_frac': None if alg is None else alg / (graph_ms * 1e-3) / 1e9 / peak}
@@ -641,7 +661,7 @@ def main():
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer leg (profiling runs)')
     ap.add_argument('--batch', type=int, default=B_PER_GPU, help='batch per GPU (default: the benchmark shape)')
-    ap.add_argument('--workload', default='wkv7', choices=['wkv7', 'attn_ln', 'prefill', 'ddlerp', 'expand_loras', 'mixer'],
+    ap.add_argument('--workload', default='wkv7', choices=['wkv7', 'attn_ln', 'prefill', 'prefill_b1', 'ddlerp', 'expand_loras', 'mixer'],
                     help='wkv7 (default) is the headline line; the others time secondary workloads on one GPU')
     args = ap.parse_args()
     if args.impl == 'reference':

@@ -365,3 +365,31 @@ def test_config4_long_context_prefill():
     check('y', y[bsel:bsel + 1, :, hs], yo, th.bfloat16)
     assert maxabs_rms(sT[bsel:bsel + 1, :4], sTo) <= 2e-2
     assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize('nseg', [2, 8])
+def test_time_split_forward(nseg):
+    """attn(..., time_split=n): the sequence as n parallel segments joined by the affine form S_end = S_start M + R.
+    y and the final state against the oracle with the usual bounds, and against the unsplit call (the two differ by the
+    rounding of M, not bit for bit)."""
+    c_oracle, _lib, attn, synthetic, _ = _mods()
+    B, T, H = 1, 2048, 3
+    d = synthetic.wkv7_inputs(B, T, H, N, seed=31, dtype=th.bfloat16, device='cuda', s0_std=0.1)
+    ins = [d[n] for n in NAMES]
+    with th.no_grad():
+        y, sT = attn(*ins, N, s0=d['s0'], return_state=True, time_split=nseg)
+        y1, sT1 = attn(*ins, N, s0=d['s0'], return_state=True)
+    cpu = [x.double().cpu().numpy().reshape(B, T, H, N) for x in ins]
+    yo, sTo = c_oracle.wkv7_fwd(*cpu, s0=d['s0'].double().cpu().numpy())
+    check('y', y.view(B, T, H, N), yo, th.bfloat16)
+    assert maxabs_rms(sT, sTo) <= 2e-2
+    assert maxabs_rms(sT, sT1.double().cpu().numpy()) <= 2e-2
+    # fp32 tensors: the split is exact to the fp32 path's tolerance
+    d = synthetic.wkv7_inputs(B, 512, H, N, seed=32, dtype=th.float32, device='cuda')
+    ins = [d[n] for n in NAMES]
+    with th.no_grad():
+        y, sT = attn(*ins, N, return_state=True, time_split=nseg)
+    cpu = [x.double().cpu().numpy().reshape(B, 512, H, N) for x in ins]
+    yo, sTo = c_oracle.wkv7_fwd(*cpu)
+    assert maxabs_rms(y.view(B, 512, H, N), yo) <= 1e-4 and maxabs_rms(sT, sTo) <= 1e-4
+    assert _lib.device_status() == 0

@@ -126,11 +126,64 @@ def load_attn(HEAD_SIZE):
     _lib.lib()
 
 
-def attn(r, w, k, v, a, b, HEAD_SIZE, *, s0=None, return_state=False):
-    """y = WKV7(r,w,k,v,a,b) for [B,T,H*HEAD_SIZE] tensors (upstream: rwkv7_attn.py:53-59)."""
+def _attn_time_split(r, w, k, v, a, b, C, s0, nseg):
+    """Forward only, the sequence cut into `nseg` equal segments that run as separate chains (for B*H far below the
+    number of SMs: one CTA walks one chain, so a single long sequence otherwise occupies H SMs).
+
+    The recurrence is affine in the state: over a segment S_end = S_start M + R, with M and R independent of S_start.
+    Pass 1 runs every segment twice (two concurrent launches of nseg*B*H chains): from the zero state with the real inputs
+    (final state = R) and from the identity state with v = 0 (final state = M).  A short host loop of nseg - 1 batched
+    64x64 products gives every segment's start state; pass 2 is the ordinary forward over the segments with those.
+    Three passes of length T/nseg instead of one of length T.  Results differ from the unsplit call by the rounding
+    of M (single-TF32 products for bf16 tensors): y and sT agree within the path's tolerance, not bit for bit."""
+    B, T, HC = w.shape
+    H = HC // C
+    assert T % nseg == 0, 'time_split must divide T'
+    Ts = T // nseg
+    ins = [i.contiguous().view(B * nseg, Ts, H, C) for i in (w, r, k, v, a, b)]   # segments become batch entries: no copy
+    dev = w.device
+    eye = th.eye(C, dtype=th.float32, device=dev).expand(B * nseg, H, C, C)
+    zero = th.zeros(B * nseg, H, C, C, dtype=th.float32, device=dev)
+    # the two sets of chains read the same inputs (v apart): two launches on two streams, which share the SMs
+    side = th.cuda.Stream(dev)
+    main = th.cuda.current_stream(dev)
+    side.wait_stream(main)
+    with th.cuda.stream(side):
+        insM = list(ins)
+        insM[3] = th.zeros_like(ins[3])                                           # v = 0 for the identity chains
+        _, M, _ = fw_attn(*insM, eye.contiguous(), save_checkpoints=False)
+    _, R, _ = fw_attn(*ins, zero, save_checkpoints=False)
+    main.wait_stream(side)
+    for t in insM + [M]:
+        t.record_stream(main)
+    R, M = R.view(B, nseg, H, C, C), M.view(B, nseg, H, C, C)
+    S = th.zeros(B, H, C, C, dtype=th.float32, device=dev) if s0 is None else s0.float()
+    starts = [S]
+    prev = th.backends.cuda.matmul.allow_tf32
+    th.backends.cuda.matmul.allow_tf32 = False
+    try:
+        for j in range(nseg - 1):
+            S = S @ M[:, j] + R[:, j]
+            starts.append(S)
+    finally:
+        th.backends.cuda.matmul.allow_tf32 = prev
+    y, sT, _ = fw_attn(*ins, th.stack(starts, 1).reshape(B * nseg, H, C, C).contiguous(), save_checkpoints=False)
+    return y.view(B, T, HC), sT.view(B, nseg, H, C, C)[:, -1].contiguous()
+
+
+def attn(r, w, k, v, a, b, HEAD_SIZE, *, s0=None, return_state=False, time_split=None):
+    """y = WKV7(r,w,k,v,a,b) for [B,T,H*HEAD_SIZE] tensors (upstream: rwkv7_attn.py:53-59).
+
+    time_split=n (no upstream counterpart; inference only, no autograd): the sequence runs as n segments in
+    parallel, see _attn_time_split.  Pays when B*H is far below the number of SMs."""
     B, T, HC = w.shape
     C = HEAD_SIZE
     H = HC // C
+    if time_split is not None and time_split > 1:
+        assert C == _lib.HEAD_SIZE, 'only head size 64 is built'
+        assert not (th.is_grad_enabled() and any(i.requires_grad for i in (r, w, k, v, a, b))), 'time_split is forward only'
+        y, sT = _attn_time_split(r, w, k, v, a, b, C, s0, int(time_split))
+        return (y, sT) if return_state else y
     r, w, k, v, a, b = [i.view(B, T, H, C) for i in [r, w, k, v, a, b]]
     y, sT, _ = WindRWKV7.apply(w, r, k, v, a, b, s0)
     y = y.view(B, T, HC)
