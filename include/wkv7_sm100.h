@@ -187,6 +187,16 @@ int wkv7_ddlerp_bwd(const void* x, const void* alpha, const void* L, const void*
                     int64_t B, int64_t T, int64_t C, int64_t D, void* stream);
 
 /*
+ * Projection of the time mixer, forward: C = act(A W^T) with A [M,K], W [N,K] (an nn.Linear weight), C [M,N], all bf16,
+ * contiguous; act = tanh on the columns tanh_from <= n < tanh_to (a LoRA's first stage feeds its second through tanh),
+ * identity elsewhere (tanh_from == tanh_to: a plain projection).  Replaces the torch matmuls `x @ W.bfloat16().mT` and the
+ * separate tanh passes of the reference's mixer (wind_rwkv/rwkv7/time_mixer.py:120-131, 167).  tcgen05 products (bf16
+ * operands, fp32 accumulation in tensor memory), operands by bulk tensor loads.  N and K multiples of 8; any M.
+ */
+int wkv7_proj_gemm(const void* A, const void* W, void* C, int64_t M, int64_t N, int64_t K,
+                   int64_t tanh_from, int64_t tanh_to, void* stream);
+
+/*
  * expand_loras: second-stage LoRA expansion producing (w, k, kk, b) for the mixer.  Replaces
  * fw_triton_ (wind_rwkv/rwkv7/rwkv7_expand_loras.py:32-89) behind ExpandLoras.forward (:215-231).
  * All tensors bf16, contiguous: w_in,k_in [B,T,C]; z_in,a_in,ma_in,mk_in [B,T,D]; W* [C,D];

@@ -293,6 +293,19 @@ int wkv7_attn_ln_bwd_static(const void* r, const void* w, const void* k, const v
                       scratch, ds0, B, T, H, N, stride_b, stride_t, stride_h, io_dtype, stream);
 }
 
+int wkv7_proj_gemm(const void* A, const void* W, void* C, int64_t M, int64_t N, int64_t K, int64_t tanh_from,
+                   int64_t tanh_to, void* stream) {
+    if (M < 0 || N <= 0 || K <= 0 || tanh_from < 0 || tanh_to < tanh_from || tanh_to > N) return WKV7_ERR_SHAPE;
+    if (N % 8 != 0 || K % 8 != 0) return WKV7_ERR_ALIGN;   // 16-byte rows for the bulk tensor loads and the stores
+    if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL || (M + 127) / 128 > 65535) return WKV7_ERR_TOO_LARGE;
+    if (M == 0) return WKV7_OK;
+    if (!A || !W || !C) return WKV7_ERR_NULL;
+    if (!aligned16(A) || !aligned16(W) || !aligned16(C)) return WKV7_ERR_ALIGN;
+    int* status = status_ptr();
+    if (!status) return WKV7_ERR_LAUNCH;
+    return wkv7::launch_proj_gemm(A, W, C, M, N, K, (int)tanh_from, (int)tanh_to, status, (cudaStream_t)stream);
+}
+
 static int ddlerp_check(int64_t B, int64_t T, int64_t C, int64_t D) {
     if (B < 0 || T < 0 || C <= 0 || D <= 0) return WKV7_ERR_SHAPE;
     if (C % 64 != 0) return WKV7_ERR_CHUNK;

@@ -52,6 +52,9 @@ int launch_bwd(const BwdParams& p, int io_dtype, bool ln, cudaStream_t stream);
 // tcgen05 forward (bf16 IO; attn, or attn_ln with ln = true); |groups| = preparation groups per CTA (2..4); negative: operands are
 // not rounded to TF32 by their producer (the tensor core truncates them)
 int launch_fwd_tc(const FwdParams& p, int groups, bool ln, cudaStream_t stream);
+// C[M,N] = act(A[M,K] W[N,K]^T), bf16, tanh on columns [tanh_from, tanh_to); tcgen05 + TMA (proj_gemm.cu)
+int launch_proj_gemm(const void* A, const void* W, void* C, long long M, long long N, long long K, int tanh_from, int tanh_to,
+                     int* status, cudaStream_t stream);
 // one small CTA running the tcgen05 forward's bounded mbarrier wait on barriers nothing arrives on
 int launch_bounded_wait_selftest(long long limit_cycles, int* status, long long* cycles, cudaStream_t stream);
 

@@ -3,6 +3,7 @@ from .rwkv7_ddlerp import ddlerp
 from .rwkv7_expand_loras import expand_loras
 from .rwkv7_attn import attn, attn_step, load_attn
 from .rwkv7_attn_ln import attn_ln, load_attn_ln
+from .rwkv7_proj import proj
 
 from .time_mixer import TimeMixer
 

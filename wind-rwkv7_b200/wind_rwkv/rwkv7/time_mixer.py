@@ -13,6 +13,7 @@ import torch.nn as nn
 from .rwkv7_attn_ln import attn_ln, load_attn_ln
 from .rwkv7_ddlerp import ddlerp
 from .rwkv7_expand_loras import expand_loras
+from .rwkv7_proj import proj as fused_proj
 
 
 def ref_attn(q, w, k, v, a, b, HEAD_SIZE):
@@ -104,13 +105,18 @@ class TimeMixer(nn.Module):
             w = weights[0] if len(weights) == 1 else torch.cat(weights)
             return inp @ w.to(bf).mT
 
+        def lora1(inp, tanh_cols, *weights):
+            # first stage of one or several LoRAs on the tcgen05 projection kernel, tanh fused into the chosen columns
+            return fused_proj(inp, torch.cat(weights).to(bf) if len(weights) > 1 else weights[0].to(bf), tanh_cols)
+
         r = proj(xrg, self.Wr)
-        g = torch.tanh(proj(xrg, self.gate_w1)) @ self.gate_w2.to(bf).mT
+        g = lora1(xrg, (0, self.GATE_RANK), self.gate_w1) @ self.gate_w2.to(bf).mT
         k = proj(xk, self.Wk)
-        kk1, mk1 = proj(xk, self.time_kkk_w1, self.mk_w1).split([r16, r16], dim=2)
+        kk1, mk1 = lora1(xk, None, self.time_kkk_w1, self.mk_w1).split([r16, r16], dim=2)
         v = proj(xv, self.Wv)
-        w1, a1, ma1 = proj(xwa, self.time_decay_w1, self.time_aaa_w1, self.ma_w1).split([self.DECAY_RANK, r16, r16], dim=2)
-        w2 = torch.tanh(w1) @ self.time_decay_w2.to(bf).mT
+        w1t, a1, ma1 = lora1(xwa, (0, self.DECAY_RANK), self.time_decay_w1, self.time_aaa_w1, self.ma_w1).split(
+            [self.DECAY_RANK, r16, r16], dim=2)
+        w2 = w1t @ self.time_decay_w2.to(bf).mT
 
         w, k, kk, b = expand_loras(w2, k, kk1, a1, ma1, mk1, self.time_kkk_w2, self.time_aaa_w2, self.ma_w2, self.mk_w2,
                                    self.time_decay, self.time_aaaaa, self.time_misc_a, self.time_misc_k, self.head_size)
