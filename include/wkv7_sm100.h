@@ -177,6 +177,17 @@ int wkv7_ddlerp_fwd(const void* x, const void* alpha, const void* L, const void*
                     void* m, void* y, int64_t B, int64_t T, int64_t C, int64_t D, void* stream);
 
 /*
+ * ddlerp forward on the tcgen05 tensor cores with bulk tensor (TMA) loads and stores: same arguments, results and
+ * limits as wkv7_ddlerp_fwd, plus `workspace`: wkv7_ddlerp_fwd_tc_workspace_bytes(C, D) bytes of device scratch,
+ * 16-byte aligned, overwritten (the shifted-weight form of L and the rearranged R).  The time shift is folded into
+ * the weights, m = tanh([x_t | x_{t-1}] [L(1-alpha) | L alpha]^T), so m differs from wkv7_ddlerp_fwd's in the last
+ * bf16 bits.  May report WKV7_ERR_DEVICE_TIMEOUT through the status word (bounded waits).
+ */
+size_t wkv7_ddlerp_fwd_tc_workspace_bytes(int64_t C, int64_t D);
+int wkv7_ddlerp_fwd_tc(const void* x, const void* alpha, const void* L, const void* R, const void* beta,
+                       void* m, void* y, void* workspace, int64_t B, int64_t T, int64_t C, int64_t D, void* stream);
+
+/*
  * ddlerp backward.  Replaces bw1..bw4_triton_ (rwkv7_ddlerp.py:92-303) behind DDLerp.backward
  * (:323-334).  dy0..dy3: bf16 [B,T,C].  dpre_workspace: bf16 [B,T,4D] scratch.  dx: bf16 [B,T,C].
  * Parameter gradients are fp32 and overwritten: dalpha [C], dL [4D,C], dR [4,C,D], dbeta [4,C].

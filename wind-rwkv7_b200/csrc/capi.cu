@@ -327,6 +327,27 @@ int wkv7_ddlerp_fwd(const void* x, const void* alpha, const void* L, const void*
     return wkv7::launch_ddlerp_fwd(p, (cudaStream_t)stream);
 }
 
+size_t wkv7_ddlerp_fwd_tc_workspace_bytes(int64_t C, int64_t D) {
+    if (C <= 0 || D <= 0) return 0;
+    return wkv7::ddlerp_fwd_tc_workspace_bytes(C, (int)D);
+}
+
+int wkv7_ddlerp_fwd_tc(const void* x, const void* alpha, const void* L, const void* R, const void* beta, void* m, void* y,
+                       void* workspace, int64_t B, int64_t T, int64_t C, int64_t D, void* stream) {
+    int rc = ddlerp_check(B, T, C, D);
+    if (rc) return rc;
+    if (B == 0 || T == 0) return WKV7_OK;
+    const void* ptrs[] = {x, alpha, L, R, beta, m, y, workspace};
+    for (const void* q : ptrs) {
+        if (!q) return WKV7_ERR_NULL;
+        if (!aligned16(q)) return WKV7_ERR_ALIGN;
+    }
+    int* status = status_ptr();
+    if (!status) return WKV7_ERR_LAUNCH;
+    wkv7::DdlerpFwdParams p{x, alpha, L, R, beta, m, y, B * T, T, C, (int)D};
+    return wkv7::launch_ddlerp_fwd_tc(p, workspace, status, (cudaStream_t)stream);
+}
+
 int wkv7_ddlerp_bwd(const void* x, const void* alpha, const void* L, const void* R, const void* beta, const void* m,
                     const void* dy0, const void* dy1, const void* dy2, const void* dy3, void* dpre_workspace, void* dx,
                     float* dalpha, float* dL, float* dR, float* dbeta, int64_t B, int64_t T, int64_t C, int64_t D,

@@ -23,6 +23,9 @@ struct DdlerpBwdParams {
 };
 
 int launch_ddlerp_fwd(const DdlerpFwdParams& p, cudaStream_t stream);
+// tcgen05 + TMA form of the forward (ddlerp_tc.cu); `ws` holds ddlerp_fwd_tc_workspace_bytes(C, D) bytes of scratch
+size_t ddlerp_fwd_tc_workspace_bytes(long long C, int D);
+int launch_ddlerp_fwd_tc(const DdlerpFwdParams& p, void* ws, int* status, cudaStream_t stream);
 int launch_ddlerp_bwd(const DdlerpBwdParams& p, cudaStream_t stream);
 
 }  // namespace wkv7

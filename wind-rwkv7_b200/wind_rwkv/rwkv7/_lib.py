@@ -46,6 +46,8 @@ _SIGNATURES = {
     'wkv7_attn_ln_bwd': (_int, [_vp] * 22 + [_f32] + [_i64] * 7 + [_int, _vp]),
     'wkv7_proj_gemm': (_int, [_vp] * 3 + [_i64] * 5 + [_vp]),
     'wkv7_ddlerp_fwd': (_int, [_vp] * 7 + [_i64] * 4 + [_vp]),
+    'wkv7_ddlerp_fwd_tc': (_int, [_vp] * 8 + [_i64] * 4 + [_vp]),
+    'wkv7_ddlerp_fwd_tc_workspace_bytes': (ctypes.c_size_t, [_i64] * 2),
     'wkv7_ddlerp_bwd': (_int, [_vp] * 16 + [_i64] * 4 + [_vp]),
     'wkv7_expand_loras_fwd': (_int, [_vp] * 18 + [_i64] * 4 + [_vp]),
     'wkv7_expand_loras_bwd_workspace_bytes': (_i64, [_i64] * 4),

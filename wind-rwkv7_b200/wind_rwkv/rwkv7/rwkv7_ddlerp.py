@@ -16,10 +16,12 @@ def fw_ddlerp(x, ab, Lb, Rb, bb):
     D = Rb.shape[2]
     m = th.empty(B, T, 4 * D, dtype=th.bfloat16, device=x.device)
     y = th.empty(4, B, T, C, dtype=th.bfloat16, device=x.device)
+    # tcgen05 + TMA form; its scratch (shifted-weight form of L, rearranged R) comes from torch's allocator
+    ws = th.empty(_lib.lib().wkv7_ddlerp_fwd_tc_workspace_bytes(C, D), dtype=th.uint8, device=x.device)
     with _lib.on_device(x, ab, Lb, Rb, bb):
-        rc = _lib.lib().wkv7_ddlerp_fwd(x.data_ptr(), ab.data_ptr(), Lb.data_ptr(), Rb.data_ptr(), bb.data_ptr(),
-                                        m.data_ptr(), y.data_ptr(), B, T, C, D, _lib.stream_of(x))
-    _lib.check(rc, 'wkv7_ddlerp_fwd')
+        rc = _lib.lib().wkv7_ddlerp_fwd_tc(x.data_ptr(), ab.data_ptr(), Lb.data_ptr(), Rb.data_ptr(), bb.data_ptr(),
+                                           m.data_ptr(), y.data_ptr(), ws.data_ptr(), B, T, C, D, _lib.stream_of(x))
+    _lib.check(rc, 'wkv7_ddlerp_fwd_tc')
     return m, y
 
 
