@@ -126,12 +126,16 @@ template <int D> struct MainSmem {
 };
 
 template <int D>
-__global__ void __launch_bounds__(256) ddlerp_bwd_main_kernel(DdlerpBwdParams p) {
+__global__ void __launch_bounds__(256) ddlerp_bwd_main_kernel(DdlerpBwdParams p, int segs, int tiles_per_seg) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     auto& sm = *reinterpret_cast<MainSmem<D>*>(smem_raw);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int cb = blockIdx.x;
-    const long long b0 = (long long)blockIdx.y * p.T;  // first row of this sequence
+    // blockIdx.y = sequence * segs + segment: a sequence is cut into `segs` runs of tiles_per_seg 32-token tiles, each walked
+    // backwards by its own CTA.  A run that is not the sequence's last first processes the tile that follows it, only to
+    // obtain the carried row X of that tile's first token (its accumulators are reset afterwards, nothing is stored).
+    const int seg = (int)(blockIdx.y % segs);
+    const long long b0 = (long long)(blockIdx.y / segs) * p.T;  // first row of this sequence
     const int C = (int)p.C, T = (int)p.T;
     const bf16* x = (const bf16*)p.x;
 
@@ -159,7 +163,11 @@ __global__ void __launch_bounds__(256) ddlerp_bwd_main_kernel(DdlerpBwdParams p)
     float dR2[D / 8][4] = {};
     float dal[2][2] = {}, dbe[4][2][2] = {};
 
-    for (int t0 = ((T - 1) / 32) * 32; t0 >= 0; t0 -= 32) {
+    const int t_last = ((T - 1) / 32) * 32;                       // first token of the sequence's last tile
+    const int t_lo = seg * tiles_per_seg * 32;                    // first token of this run
+    const int t_next = t_lo + tiles_per_seg * 32;                 // first token of the following run
+    bool warm = t_next <= t_last;                                 // a run follows: start with its first tile
+    for (int t0 = warm ? t_next : t_last; t0 >= t_lo; t0 -= 32) {
         const long long r0 = b0 + t0;
         const int nrow = T - t0 < 32 ? T - t0 : 32;  // live rows of this tile (the last one may be short)
         // ---- loads -----------------------------------------------------------------------------
@@ -273,10 +281,25 @@ __global__ void __launch_bounds__(256) ddlerp_bwd_main_kernel(DdlerpBwdParams p)
         // ---- dx out (coalesced), carry X_{t0} for the previous tile ----------------------------------
         {
             const int r = tid >> 3, ch = tid & 7;
-            if (r < nrow)
+            if (r < nrow && !warm)
                 *reinterpret_cast<uint4*>((bf16*)p.dx + (r0 + r) * C + cb * 64 + ch * 8) = *reinterpret_cast<const uint4*>(&sm.dxS[r][ch * 8]);
         }
         if (tid < 64) sm.XS[32][tid] = sm.XS[0][tid];
+        if (warm) {  // the following run's tile only supplied the carry
+            warm = false;
+#pragma unroll
+            for (int j = 0; j < D / 8; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dR[j][i] = dR2[j][i] = 0.f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    dal[j][e] = 0.f;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) dbe[k][j][e] = 0.f;
+                }
+        }
         __syncthreads();
     }
 
@@ -423,7 +446,25 @@ template <int D> static int launch_ddlerp_bwd_t(const DdlerpBwdParams& p, cudaSt
         auto kern = ddlerp_bwd_main_kernel<D>;
         const int smem = (int)sizeof(MainSmem<D>);
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kLaunchFailed;
-        kern<<<dim3((unsigned)(C / 64), (unsigned)B), 256, smem, stream>>>(p);
+        // Runs per sequence: the count (up to 8) that minimises rounds of resident CTAs x tiles walked per CTA, the
+        // extra tile of a run that has a successor included (two CTAs per SM fit).
+        static const int slots = [] {
+            int dev = 0, sms = 148;
+            if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            return 2 * sms;
+        }();
+        const long long tiles = (p.T + 31) / 32;
+        int segs = 1;
+        long long best = -1;
+        for (int s = 1; s <= 8 && s <= tiles; ++s) {
+            const long long tps = (tiles + s - 1) / s;
+            if ((s - 1) * tps >= tiles) continue;  // the last run would be empty
+            const long long cost = (((long long)(C / 64) * B * s + slots - 1) / slots) * (tps + (s > 1 ? 1 : 0));
+            if (best < 0 || cost < best) { best = cost; segs = s; }
+        }
+        const int tiles_per_seg = (int)((tiles + segs - 1) / segs);
+        if (B * segs > 65535) return kTooLarge;
+        kern<<<dim3((unsigned)(C / 64), (unsigned)(B * segs)), 256, smem, stream>>>(p, segs, tiles_per_seg);
         if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
     }
     {
