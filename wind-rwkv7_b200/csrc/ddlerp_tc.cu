@@ -10,13 +10,16 @@
 //             its A blocks from x through ONE 3-D tensor map (channel, time, batch): the second half of the loop reads the
 //             same tiles one time step earlier, and the row before a sequence's first token is out of range for the map,
 //             i.e. zero.  TMA ring of 3 stages, tcgen05.mma kind::f16 into tensor memory, tanh + bf16 epilogue, bulk stores.
-//   lerp      one CTA per 128 tokens x 64 channels: bulk tensor loads of the m tile, the R' tile, the x tile and the x tile
-//             one step earlier; four K = D products z_i (tensor-memory columns 64 i ...); the epilogue reads z_i one token row
-//             per thread, forms y_i from the two x rows in shared memory and stores four [128 x 64] tiles by bulk tensor
-//             stores.  HBM traffic = x once (its re-reads hit L2) + m + the four outputs.
+//   lerp      persistent, one CTA per SM over units of 128 tokens x 64 channels: bulk tensor loads of the m tile, the R' tile
+//             and a 129-row x tile that starts one token early (two stages: the next unit's loads run under this unit's
+//             epilogue); four K = D products z_i into one of two sets of 4 x 64 tensor-memory columns; eight epilogue
+//             warps read z_i one token row per thread, form y_i from rows r and r + 1 of the x tile and store [32 x 64]
+//             pieces of the four output tiles by bulk tensor stores.  HBM traffic = x once (re-reads hit L2) + m + outputs.
+//             Rank 64 (two stages would not fit shared memory) runs the mma.sync forward of ddlerp_fwd.cu instead.
 // Every wait on an mbarrier is bounded (mbar_wait_bounded): a wait that runs out sets the CTA's abort flag, reports
 // kDeviceTimeout, and the CTA leaves without storing; tensor memory is released in every case.
 #include <cuda.h>
+#include <cstddef>
 #include <cstring>
 
 #include "ddlerp.h"
@@ -208,48 +211,53 @@ __global__ void __launch_bounds__(g1::THREADS) ddlerp_gemm1_kernel(const __grid_
 }
 
 // ---- lerp: y_i = x_t + (x_{t-1} - x_t) (m_i R_i^T + beta_i) --------------------------------------------------------------
+// Persistent: one CTA per SM walks work units (128 tokens of one sequence) x (64 channels), consecutive CTAs taking the
+// channel blocks of the same token tile (its m tile then comes out of L2).  Warp 8 issues the bulk loads of the NEXT unit
+// into the other of two shared-memory stages and the current unit's four products into the other of two accumulator
+// sets; warps 0-7 are the epilogue (warp w: token rows 32 (w % 4) ..., streams 2 (w / 4) and 2 (w / 4) + 1).
 namespace g2 {
-constexpr int BN = 64;            // channels per CTA
-constexpr int THREADS = 160;      // warps 0-3: epilogue, warp 4: bulk loads and the products
-constexpr int X_BYTES = BM * BN * 2, OUT_BYTES = BM * BN * 2;
+constexpr int BN = 64;            // channels per unit
+constexpr int EPI_WARPS = 8, THREADS = 32 * (EPI_WARPS + 1);
+constexpr int XROWS = BM + 1;     // the x tile starts one token early: row r holds x_{t0 + r - 1}
+constexpr int X_BYTES = ((XROWS * 128 + 1023) / 1024) * 1024, OUT_BYTES = BM * BN * 2;
 struct Ctrl {
-    uint64_t ops, xs, accum;      // m and R' tiles landed; the two x tiles landed; products complete
+    uint64_t ops[2], xs[2], accum[2];   // per stage: m and R' tiles landed; x tile landed; per accumulator set: products complete
+    uint64_t stage_free[2], acc_free[2];  // the epilogue warps are done with the stage's x tile / the accumulator set
     uint32_t tmem_base;
     volatile int abort;
-    float beta[4][BN];
+    alignas(16) float beta[2][4][BN];   // read as float4
 };
-// shared memory: [m tile: (4D/64) blocks of 128 rows x 128 B][R' tile: (4D/64) blocks of 64 rows x 128 B] -- reused, once the
-// products are complete, by the four output tiles --, then x_t, x_{t-1} (64 channels = 128-byte rows), then Ctrl
+static_assert(offsetof(Ctrl, beta) % 16 == 0, "beta is read with 16-byte loads");
 __host__ __device__ constexpr int ops_bytes(int D) { return (4 * D / 64) * (BM * 128 + BN * 128); }
-__host__ __device__ constexpr int out_region(int D) { return ops_bytes(D) > 4 * OUT_BYTES ? ops_bytes(D) : 4 * OUT_BYTES; }
+__host__ __device__ constexpr int stage_bytes(int D) { return ops_bytes(D) + X_BYTES; }
+__host__ __device__ constexpr int smem_bytes(int D) { return 2 * stage_bytes(D) + 4 * OUT_BYTES + (int)sizeof(Ctrl) + 1024; }
 }  // namespace g2
 
 // mapM: m as (column, time, batch), box 64 x 128 x 1;  mapR: R' as (column, channel), box 64 x 64;
-// mapX: x as (channel, time, batch), box 64 x 128 x 1;  mapY: y as (channel, time, batch, stream), box 64 x 32 x 1 x 1
+// mapX: x as (channel, time, batch), box 64 x 129 x 1;  mapY: y as (channel, time, batch, stream), box 64 x 32 x 1 x 1
 template <int D>
-__global__ void __launch_bounds__(g2::THREADS) ddlerp_lerp_kernel(const __grid_constant__ CUtensorMap mapM, const __grid_constant__ CUtensorMap mapR,
-                                                                 const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapY,
-                                                                 const __nv_bfloat16* __restrict__ beta, int C, int T, int* status) {
+__global__ void __launch_bounds__(g2::THREADS, 1) ddlerp_lerp_kernel(const __grid_constant__ CUtensorMap mapM, const __grid_constant__ CUtensorMap mapR,
+                                                                    const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapY,
+                                                                    const __nv_bfloat16* __restrict__ beta, int C, int T, int tiles_per_seq, int units, int* status) {
     using namespace g2;
     constexpr int KB = 4 * D / 64;             // 64-column blocks of the m and R' tiles
-    constexpr int NCOLS = 256;                 // tensor-memory columns: z_i at 64 i
+    constexpr int NCOLS = 512;                 // two accumulator sets of 4 x 64 columns: z_i at 256 set + 64 i
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* sm = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
-    unsigned char* smM = sm;
-    unsigned char* smR = sm + KB * (BM * 128);
-    unsigned char* smX = sm + out_region(D);
-    unsigned char* smP = smX + X_BYTES;
-    Ctrl* ctrl = reinterpret_cast<Ctrl*>(smP + X_BYTES);
+    unsigned char* smOut = sm + 2 * stage_bytes(D);
+    Ctrl* ctrl = reinterpret_cast<Ctrl*>(smOut + 4 * OUT_BYTES);
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
-    const int c0 = blockIdx.x * BN, t0 = blockIdx.y * BM, bi = blockIdx.z;
+    const int ncb = C / BN;
 
     if (tid == 0) {
-        mbar_init(&ctrl->ops, 1); mbar_init(&ctrl->xs, 1); mbar_init(&ctrl->accum, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&ctrl->ops[s], 1); mbar_init(&ctrl->xs[s], 1); mbar_init(&ctrl->accum[s], 1);
+            mbar_init(&ctrl->stage_free[s], EPI_WARPS); mbar_init(&ctrl->acc_free[s], EPI_WARPS);
+        }
         ctrl->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = tid; i < 4 * BN; i += THREADS) ctrl->beta[i / BN][i % BN] = __bfloat162float(beta[(long long)(i / BN) * C + c0 + (i % BN)]);
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctrl->tmem_base)), "r"(NCOLS) : "memory");
@@ -259,84 +267,122 @@ __global__ void __launch_bounds__(g2::THREADS) ddlerp_lerp_kernel(const __grid_c
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = ctrl->tmem_base;
+    const int nmine = ((int)blockIdx.x < units) ? (units - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;  // units blockIdx.x, + gridDim.x, ...
 
-    if (warp == 4) {
+    if (warp == EPI_WARPS) {
         if (elect_one()) {
-            mbar_expect(&ctrl->ops, (uint32_t)ops_bytes(D));
+            auto issue_loads = [&](int n) {
+                const int u = (int)blockIdx.x + n * (int)gridDim.x, s = n & 1;
+                const int cb = u % ncb, tile = u / ncb, t0 = (tile % tiles_per_seq) * BM, bi = tile / tiles_per_seq;
+                unsigned char* st = sm + s * stage_bytes(D);
+                mbar_expect(&ctrl->ops[s], (uint32_t)ops_bytes(D));
 #pragma unroll
-            for (int kb = 0; kb < KB; ++kb) {
-                tma_load_3d(smem_u32(smM + kb * (BM * 128)), &mapM, &ctrl->ops, kb * 64, t0, bi);
-                tma_load_2d(smem_u32(smR + kb * (BN * 128)), &mapR, &ctrl->ops, kb * 64, c0);
+                for (int kb = 0; kb < KB; ++kb) {
+                    tma_load_3d(smem_u32(st + kb * (BM * 128)), &mapM, &ctrl->ops[s], kb * 64, t0, bi);
+                    tma_load_2d(smem_u32(st + KB * (BM * 128) + kb * (BN * 128)), &mapR, &ctrl->ops[s], kb * 64, cb * BN);
+                }
+                mbar_expect(&ctrl->xs[s], (uint32_t)(XROWS * 128));
+                tma_load_3d(smem_u32(st + ops_bytes(D)), &mapX, &ctrl->xs[s], cb * BN, t0 - 1, bi);  // the row before the sequence's first token is out of range: zeros
+            };
+            if (nmine > 0) issue_loads(0);
+            for (int n = 0; n < nmine; ++n) {
+                const int s = n & 1;
+                if (n + 1 < nmine) {  // the other stage was last used by unit n - 1
+                    if (n >= 1) mbar_wait_bounded<true>(&ctrl->stage_free[s ^ 1], ((n - 1) >> 1) & 1, &ctrl->abort, status);
+                    issue_loads(n + 1);
+                }
+                mbar_wait_bounded<false>(&ctrl->ops[s], (n >> 1) & 1, &ctrl->abort, status);
+                if (n >= 2) mbar_wait_bounded<true>(&ctrl->acc_free[s], ((n - 2) >> 1) & 1, &ctrl->abort, status);  // set s was last read for unit n - 2
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                unsigned char* st = sm + s * stage_bytes(D);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    // columns i D .. i D + D - 1 of the tiles: block (i D) / 64, byte offset ((i D) % 64) * 2 inside the 128-byte rows
+                    const int blk = (i * D) / 64, off = ((i * D) % 64) * 2;
+                    const uint64_t da = desc_sw128(smem_u32(st + blk * (BM * 128))) + (uint64_t)(off >> 4);
+                    const uint64_t db = desc_sw128(smem_u32(st + KB * (BM * 128) + blk * (BN * 128))) + (uint64_t)(off >> 4);
+#pragma unroll
+                    for (int ks = 0; ks < D / 16; ++ks) mma_f16(tmem + 256 * s + 64 * i, da + (uint64_t)(2 * ks), db + (uint64_t)(2 * ks), idesc(BN), ks > 0 ? 1u : 0u);
+                }
+                tc_commit(&ctrl->accum[s]);
             }
-            mbar_expect(&ctrl->xs, (uint32_t)(2 * X_BYTES));
-            tma_load_3d(smem_u32(smX), &mapX, &ctrl->xs, c0, t0, bi);
-            tma_load_3d(smem_u32(smP), &mapX, &ctrl->xs, c0, t0 - 1, bi);  // the row before the sequence's first token is out of range: zeros
-            mbar_wait_bounded<false>(&ctrl->ops, 0, &ctrl->abort, status);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                // columns i D .. i D + D - 1 of the tiles: block (i D) / 64, byte offset ((i D) % 64) * 2 inside the 128-byte rows
-                const int blk = (i * D) / 64, off = ((i * D) % 64) * 2;
-                const uint64_t da = desc_sw128(smem_u32(smM + blk * (BM * 128))) + (uint64_t)(off >> 4);
-                const uint64_t db = desc_sw128(smem_u32(smR + blk * (BN * 128))) + (uint64_t)(off >> 4);
-#pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) mma_f16(tmem + 64 * i, da + (uint64_t)(2 * ks), db + (uint64_t)(2 * ks), idesc(BN), ks > 0 ? 1u : 0u);
-            }
-            tc_commit(&ctrl->accum);
         }
         __syncwarp();
     } else {
-        // epilogue: thread = token row r of the tile (tensor-memory lane r), 16 channels at a time for all four streams
-        const int r = 32 * warp + lane;
-        mbar_wait_bounded<true>(&ctrl->xs, 0, &ctrl->abort, status);
-        mbar_wait_bounded<true>(&ctrl->accum, 0, &ctrl->abort, status);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const bool ok = !ctrl->abort;
+        const int q = warp & 3, h = warp >> 2;       // lane quarter of tensor memory, stream pair
+        const int r = 32 * q + lane;                 // token row of the tile
+        for (int n = 0; n < nmine; ++n) {
+            const int u = (int)blockIdx.x + n * (int)gridDim.x, s = n & 1;
+            const int cb = u % ncb, tile = u / ncb, t0 = (tile % tiles_per_seq) * BM, bi = tile / tiles_per_seq;
+            const unsigned char* smX = sm + s * stage_bytes(D) + ops_bytes(D);
+            // this unit's beta values (buffer s): the first warp of a stream pair loads the pair's 2 x 64 values; the named barrier
+            // below publishes them to the pair's four warps.  Buffer s is written again two units later, after every warp of
+            // the pair has passed the next unit's barrier, i.e. has finished this unit.
+            if (q == 0) {
+                for (int i = lane; i < 2 * BN; i += 32)
+                    ctrl->beta[s][2 * h + i / BN][i % BN] = __bfloat162float(beta[(long long)(2 * h + i / BN) * C + cb * BN + (i % BN)]);
+            }
+            mbar_wait_bounded<true>(&ctrl->xs[s], (n >> 1) & 1, &ctrl->abort, status);
+            mbar_wait_bounded<true>(&ctrl->accum[s], (n >> 1) & 1, &ctrl->abort, status);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // the previous unit's stores out of this warp's staging rows must have been read
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            if (h == 0) asm volatile("bar.sync 1, 128;" ::: "memory");  // the four warps of a stream pair: beta visible
+            else asm volatile("bar.sync 2, 128;" ::: "memory");
+            const bool ok = !ctrl->abort;
 #pragma unroll 1
-        for (int cc = 0; cc < BN / 16; ++cc) {
-            float xv[16], xx[16];
+            for (int cc = 0; cc < BN / 16; ++cc) {
+                float xv[16], xx[16];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int at = r * 128 + (((2 * cc + h) ^ (r & 7)) << 4);
-                float pv[8];
-                unpack8(*reinterpret_cast<const uint4*>(smX + at), xv + 8 * h);
-                unpack8(*reinterpret_cast<const uint4*>(smP + at), pv);
+                for (int hh = 0; hh < 2; ++hh) {
+                    float pv[8];
+                    unpack8(*reinterpret_cast<const uint4*>(smX + (r + 1) * 128 + (((2 * cc + hh) ^ ((r + 1) & 7)) << 4)), xv + 8 * hh);
+                    unpack8(*reinterpret_cast<const uint4*>(smX + r * 128 + (((2 * cc + hh) ^ (r & 7)) << 4)), pv);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) xx[8 * h + j] = pv[j] - xv[8 * h + j];
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                uint32_t v[16];
-                tmem_ld16(tmem + ((uint32_t)(32 * warp) << 16) + 64 * i + 16 * cc, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                float y[16];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float4 b = *reinterpret_cast<const float4*>(&ctrl->beta[i][16 * cc + 4 * q]);
-                    y[4 * q + 0] = xv[4 * q + 0] + xx[4 * q + 0] * (__uint_as_float(v[4 * q + 0]) + b.x);
-                    y[4 * q + 1] = xv[4 * q + 1] + xx[4 * q + 1] * (__uint_as_float(v[4 * q + 1]) + b.y);
-                    y[4 * q + 2] = xv[4 * q + 2] + xx[4 * q + 2] * (__uint_as_float(v[4 * q + 2]) + b.z);
-                    y[4 * q + 3] = xv[4 * q + 3] + xx[4 * q + 3] * (__uint_as_float(v[4 * q + 3]) + b.w);
+                    for (int j = 0; j < 8; ++j) xx[8 * hh + j] = pv[j] - xv[8 * hh + j];
                 }
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    uint4 pk;
-                    pk.x = pack2(y[8 * h + 0], y[8 * h + 1]); pk.y = pack2(y[8 * h + 2], y[8 * h + 3]);
-                    pk.z = pack2(y[8 * h + 4], y[8 * h + 5]); pk.w = pack2(y[8 * h + 6], y[8 * h + 7]);
-                    *reinterpret_cast<uint4*>(sm + i * OUT_BYTES + r * 128 + (((2 * cc + h) ^ (r & 7)) << 4)) = pk;
+                for (int ii = 0; ii < 2; ++ii) {
+                    const int i = 2 * h + ii;
+                    uint32_t v[16];
+                    tmem_ld16(tmem + ((uint32_t)(32 * q) << 16) + 256 * s + 64 * i + 16 * cc, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    float y[16];
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        const float4 b = *reinterpret_cast<const float4*>(&ctrl->beta[s][i][16 * cc + 4 * k4]);
+                        y[4 * k4 + 0] = xv[4 * k4 + 0] + xx[4 * k4 + 0] * (__uint_as_float(v[4 * k4 + 0]) + b.x);
+                        y[4 * k4 + 1] = xv[4 * k4 + 1] + xx[4 * k4 + 1] * (__uint_as_float(v[4 * k4 + 1]) + b.y);
+                        y[4 * k4 + 2] = xv[4 * k4 + 2] + xx[4 * k4 + 2] * (__uint_as_float(v[4 * k4 + 2]) + b.z);
+                        y[4 * k4 + 3] = xv[4 * k4 + 3] + xx[4 * k4 + 3] * (__uint_as_float(v[4 * k4 + 3]) + b.w);
+                    }
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        uint4 pk;
+                        pk.x = pack2(y[8 * hh + 0], y[8 * hh + 1]); pk.y = pack2(y[8 * hh + 2], y[8 * hh + 3]);
+                        pk.z = pack2(y[8 * hh + 4], y[8 * hh + 5]); pk.w = pack2(y[8 * hh + 6], y[8 * hh + 7]);
+                        *reinterpret_cast<uint4*>(smOut + i * OUT_BYTES + r * 128 + (((2 * cc + hh) ^ (r & 7)) << 4)) = pk;
+                    }
                 }
             }
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (ok && lane == 0 && t0 + 32 * warp < T) {
+            // the stage's x tile and the accumulator set are free; the staged rows leave by bulk tensor stores
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ctrl->stage_free[s])) : "memory");
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ctrl->acc_free[s])) : "memory");
+                if (ok && t0 + 32 * q < T) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-                asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];"
-                             ::"l"(&mapY), "r"(c0), "r"(t0 + 32 * warp), "r"(bi), "r"(i), "r"(smem_u32(sm + i * OUT_BYTES + 32 * warp * 128)) : "memory");
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    for (int ii = 0; ii < 2; ++ii)
+                        asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];"
+                                     ::"l"(&mapY), "r"(cb * BN), "r"(t0 + 32 * q), "r"(bi), "r"(2 * h + ii), "r"(smem_u32(smOut + (2 * h + ii) * OUT_BYTES + 32 * q * 128)) : "memory");
+                }
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            __syncwarp();
         }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory must outlive the stores' reads
         __syncwarp();
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -372,10 +418,18 @@ static bool encode(CUtensorMap* m, const void* base, int rank, const long long* 
 template <int D> static int launch_lerp(const CUtensorMap& mM, const CUtensorMap& mR, const CUtensorMap& mX, const CUtensorMap& mY,
                                        const DdlerpFwdParams& p, long long B, int* status, cudaStream_t stream) {
     auto kern = ddlerp_lerp_kernel<D>;
-    const int smem = g2::out_region(D) + 2 * g2::X_BYTES + (int)sizeof(g2::Ctrl) + 1024;
+    constexpr int smem = g2::smem_bytes(D);
+    static_assert(smem <= 232448, "two stages, the output staging and the control block must fit one CTA");
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kLaunchFailed;
-    dim3 grid((unsigned)(p.C / g2::BN), (unsigned)((p.T + BM - 1) / BM), (unsigned)B);
-    kern<<<grid, g2::THREADS, smem, stream>>>(mM, mR, mX, mY, (const __nv_bfloat16*)p.beta, (int)p.C, (int)p.T, status);
+    static const int sms = [] {
+        int dev = 0, n = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        return n;
+    }();
+    const long long tiles_per_seq = (p.T + BM - 1) / BM, units = tiles_per_seq * B * (p.C / g2::BN);
+    if (units > 0x7fffffffLL) return kTooLarge;
+    const unsigned grid = (unsigned)(units < sms ? units : sms);
+    kern<<<grid, g2::THREADS, smem, stream>>>(mM, mR, mX, mY, (const __nv_bfloat16*)p.beta, (int)p.C, (int)p.T, (int)tiles_per_seq, (int)units, status);
     return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
 
@@ -388,7 +442,8 @@ int launch_ddlerp_fwd_tc(const DdlerpFwdParams& p, void* ws, int* status, cudaSt
     if (p.rows == 0) return kOk;
     const long long B = p.rows / p.T, C = p.C, T = p.T;
     const int D = p.D, n4 = 4 * D;
-    if (D != 16 && D != 32 && D != 64) return kBadShape;
+    if (D == 64) return launch_ddlerp_fwd(p, stream);  // the lerp kernel's two stages do not fit shared memory at rank 64
+    if (D != 16 && D != 32) return kBadShape;
     if (B > 65535 || (T + BM - 1) / BM > 65535) return kTooLarge;
     __nv_bfloat16* W12 = (__nv_bfloat16*)ws;
     __nv_bfloat16* Rp = W12 + (long long)n4 * 2 * C;
@@ -398,10 +453,10 @@ int launch_ddlerp_fwd_tc(const DdlerpFwdParams& p, void* ws, int* status, cudaSt
                                                                           W12, Rp, (int)C, D);
         if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
     }
-    alignas(64) CUtensorMap mX, mW, mMs, mMl, mR, mY;
+    alignas(64) CUtensorMap mX, mXl, mW, mMs, mMl, mR, mY;
     {
         const long long dx[3] = {C, T, B}, sx[2] = {C, T * C};
-        const int bx[3] = {BK, BM, 1};
+        const int bx[3] = {BK, BM, 1}, bxl[3] = {g2::BN, g2::XROWS, 1};
         const long long dw[2] = {2 * C, n4}, sw[1] = {2 * C};
         const int bw[2] = {BK, g1::BN};
         const long long dm[3] = {n4, T, B}, sm_[2] = {n4, T * n4};
@@ -410,7 +465,7 @@ int launch_ddlerp_fwd_tc(const DdlerpFwdParams& p, void* ws, int* status, cudaSt
         const int br[2] = {64, g2::BN};
         const long long dy[4] = {C, T, B, 4}, sy[3] = {C, T * C, B * T * C};
         const int by[4] = {g2::BN, 32, 1, 1};
-        if (!(encode(&mX, p.x, 3, dx, sx, bx) && encode(&mW, W12, 2, dw, sw, bw) && encode(&mMs, p.m, 3, dm, sm_, bms) &&
+        if (!(encode(&mX, p.x, 3, dx, sx, bx) && encode(&mXl, p.x, 3, dx, sx, bxl) && encode(&mW, W12, 2, dw, sw, bw) && encode(&mMs, p.m, 3, dm, sm_, bms) &&
               encode(&mMl, p.m, 3, dm, sm_, bml) && encode(&mR, Rp, 2, dr, sr, br) && encode(&mY, p.y, 4, dy, sy, by)))
             return kLaunchFailed;
     }
@@ -421,11 +476,7 @@ int launch_ddlerp_fwd_tc(const DdlerpFwdParams& p, void* ws, int* status, cudaSt
         ddlerp_gemm1_kernel<<<grid, g1::THREADS, smem, stream>>>(mX, mW, mMs, (int)C, n4, (int)T, status);
         if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
     }
-    switch (D) {
-        case 16: return launch_lerp<16>(mMl, mR, mX, mY, p, B, status, stream);
-        case 32: return launch_lerp<32>(mMl, mR, mX, mY, p, B, status, stream);
-        default: return launch_lerp<64>(mMl, mR, mX, mY, p, B, status, stream);
-    }
+    return D == 16 ? launch_lerp<16>(mMl, mR, mXl, mY, p, B, status, stream) : launch_lerp<32>(mMl, mR, mXl, mY, p, B, status, stream);
 }
 
 }  // namespace wkv7
