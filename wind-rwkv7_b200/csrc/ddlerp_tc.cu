@@ -221,16 +221,20 @@ constexpr int EPI_WARPS = 8, THREADS = 32 * (EPI_WARPS + 1);
 constexpr int XROWS = BM + 1;     // the x tile starts one token early: row r holds x_{t0 + r - 1}
 constexpr int X_BYTES = ((XROWS * 128 + 1023) / 1024) * 1024, OUT_BYTES = BM * BN * 2;
 struct Ctrl {
-    uint64_t ops[2], xs[2], accum[2];   // per stage: m and R' tiles landed; x tile landed; per accumulator set: products complete
+    uint64_t ops[2], xs[2], accum[2];   // per stage: R' tile landed; x tile landed; per accumulator set: products complete
+    uint64_t mfull[2];                  // per m buffer: tile landed
     uint64_t stage_free[2], acc_free[2];  // the epilogue warps are done with the stage's x tile / the accumulator set
     uint32_t tmem_base;
     volatile int abort;
     alignas(16) float beta[2][4][BN];   // read as float4
 };
 static_assert(offsetof(Ctrl, beta) % 16 == 0, "beta is read with 16-byte loads");
-__host__ __device__ constexpr int ops_bytes(int D) { return (4 * D / 64) * (BM * 128 + BN * 128); }
-__host__ __device__ constexpr int stage_bytes(int D) { return ops_bytes(D) + X_BYTES; }
-__host__ __device__ constexpr int smem_bytes(int D) { return 2 * stage_bytes(D) + 4 * OUT_BYTES + (int)sizeof(Ctrl) + 1024; }
+// shared memory: two m tiles ((4D/64) blocks of 128 rows x 128 B; a token tile's m is loaded once for all of its channel
+// blocks that this CTA handles), two stages of [R' tile: (4D/64) blocks of 64 rows x 128 B][x tile], the four output tiles, Ctrl
+__host__ __device__ constexpr int m_bytes(int D) { return (4 * D / 64) * (BM * 128); }
+__host__ __device__ constexpr int r_bytes(int D) { return (4 * D / 64) * (BN * 128); }
+__host__ __device__ constexpr int stage_bytes(int D) { return r_bytes(D) + X_BYTES; }
+__host__ __device__ constexpr int smem_bytes(int D) { return 2 * m_bytes(D) + 2 * stage_bytes(D) + 4 * OUT_BYTES + (int)sizeof(Ctrl) + 1024; }
 }  // namespace g2
 
 // mapM: m as (column, time, batch), box 64 x 128 x 1;  mapR: R' as (column, channel), box 64 x 64;
@@ -244,7 +248,8 @@ __global__ void __launch_bounds__(g2::THREADS, 1) ddlerp_lerp_kernel(const __gri
     constexpr int NCOLS = 512;                 // two accumulator sets of 4 x 64 columns: z_i at 256 set + 64 i
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* sm = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
-    unsigned char* smOut = sm + 2 * stage_bytes(D);
+    unsigned char* smSt = sm + 2 * m_bytes(D);
+    unsigned char* smOut = smSt + 2 * stage_bytes(D);
     Ctrl* ctrl = reinterpret_cast<Ctrl*>(smOut + 4 * OUT_BYTES);
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
@@ -254,6 +259,7 @@ __global__ void __launch_bounds__(g2::THREADS, 1) ddlerp_lerp_kernel(const __gri
         for (int s = 0; s < 2; ++s) {
             mbar_init(&ctrl->ops[s], 1); mbar_init(&ctrl->xs[s], 1); mbar_init(&ctrl->accum[s], 1);
             mbar_init(&ctrl->stage_free[s], EPI_WARPS); mbar_init(&ctrl->acc_free[s], EPI_WARPS);
+            mbar_init(&ctrl->mfull[s], 1);
         }
         ctrl->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -267,40 +273,53 @@ __global__ void __launch_bounds__(g2::THREADS, 1) ddlerp_lerp_kernel(const __gri
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = ctrl->tmem_base;
-    const int nmine = ((int)blockIdx.x < units) ? (units - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;  // units blockIdx.x, + gridDim.x, ...
+    // this CTA's units: a contiguous range of the (token tile, channel block) list, channel blocks running fastest
+    const int u_lo = (int)((long long)units * blockIdx.x / gridDim.x), nmine = (int)((long long)units * (blockIdx.x + 1) / gridDim.x) - u_lo;
 
     if (warp == EPI_WARPS) {
         if (elect_one()) {
+            int mslot = 1, mtile = -1;   // m buffer and token tile of the unit whose loads were issued last
             auto issue_loads = [&](int n) {
-                const int u = (int)blockIdx.x + n * (int)gridDim.x, s = n & 1;
+                const int u = u_lo + n, s = n & 1;
                 const int cb = u % ncb, tile = u / ncb, t0 = (tile % tiles_per_seq) * BM, bi = tile / tiles_per_seq;
-                unsigned char* st = sm + s * stage_bytes(D);
-                mbar_expect(&ctrl->ops[s], (uint32_t)ops_bytes(D));
+                unsigned char* st = smSt + s * stage_bytes(D);
+                if (tile != mtile) {  // the buffer's previous tile was read by products that completed before the stage_free wait
+                    mtile = tile; mslot ^= 1;
+                    mbar_expect(&ctrl->mfull[mslot], (uint32_t)m_bytes(D));
 #pragma unroll
-                for (int kb = 0; kb < KB; ++kb) {
-                    tma_load_3d(smem_u32(st + kb * (BM * 128)), &mapM, &ctrl->ops[s], kb * 64, t0, bi);
-                    tma_load_2d(smem_u32(st + KB * (BM * 128) + kb * (BN * 128)), &mapR, &ctrl->ops[s], kb * 64, cb * BN);
+                    for (int kb = 0; kb < KB; ++kb) tma_load_3d(smem_u32(sm + mslot * m_bytes(D) + kb * (BM * 128)), &mapM, &ctrl->mfull[mslot], kb * 64, t0, bi);
                 }
+                mbar_expect(&ctrl->ops[s], (uint32_t)r_bytes(D));
+#pragma unroll
+                for (int kb = 0; kb < KB; ++kb) tma_load_2d(smem_u32(st + kb * (BN * 128)), &mapR, &ctrl->ops[s], kb * 64, cb * BN);
                 mbar_expect(&ctrl->xs[s], (uint32_t)(XROWS * 128));
-                tma_load_3d(smem_u32(st + ops_bytes(D)), &mapX, &ctrl->xs[s], cb * BN, t0 - 1, bi);  // the row before the sequence's first token is out of range: zeros
+                tma_load_3d(smem_u32(st + r_bytes(D)), &mapX, &ctrl->xs[s], cb * BN, t0 - 1, bi);  // the row before the sequence's first token is out of range: zeros
             };
+            int cur_slot = 1, waited[2] = {0, 0};  // m buffer of the unit whose products are issued; completed waits per buffer
             if (nmine > 0) issue_loads(0);
             for (int n = 0; n < nmine; ++n) {
                 const int s = n & 1;
+                const bool tile_first = n == 0 || (u_lo + n - 1) / ncb != (u_lo + n) / ncb;  // buffers alternate from tile to tile, as in issue_loads
+                if (tile_first) cur_slot ^= 1;
                 if (n + 1 < nmine) {  // the other stage was last used by unit n - 1
                     if (n >= 1) mbar_wait_bounded<true>(&ctrl->stage_free[s ^ 1], ((n - 1) >> 1) & 1, &ctrl->abort, status);
                     issue_loads(n + 1);
                 }
+                if (tile_first) {  // its m tile must have landed: load number waited + 1 of this buffer
+                    mbar_wait_bounded<false>(&ctrl->mfull[cur_slot], waited[cur_slot] & 1, &ctrl->abort, status);
+                    ++waited[cur_slot];
+                }
                 mbar_wait_bounded<false>(&ctrl->ops[s], (n >> 1) & 1, &ctrl->abort, status);
                 if (n >= 2) mbar_wait_bounded<true>(&ctrl->acc_free[s], ((n - 2) >> 1) & 1, &ctrl->abort, status);  // set s was last read for unit n - 2
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                unsigned char* st = sm + s * stage_bytes(D);
+                unsigned char* st = smSt + s * stage_bytes(D);
+                unsigned char* mt = sm + cur_slot * m_bytes(D);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     // columns i D .. i D + D - 1 of the tiles: block (i D) / 64, byte offset ((i D) % 64) * 2 inside the 128-byte rows
                     const int blk = (i * D) / 64, off = ((i * D) % 64) * 2;
-                    const uint64_t da = desc_sw128(smem_u32(st + blk * (BM * 128))) + (uint64_t)(off >> 4);
-                    const uint64_t db = desc_sw128(smem_u32(st + KB * (BM * 128) + blk * (BN * 128))) + (uint64_t)(off >> 4);
+                    const uint64_t da = desc_sw128(smem_u32(mt + blk * (BM * 128))) + (uint64_t)(off >> 4);
+                    const uint64_t db = desc_sw128(smem_u32(st + blk * (BN * 128))) + (uint64_t)(off >> 4);
 #pragma unroll
                     for (int ks = 0; ks < D / 16; ++ks) mma_f16(tmem + 256 * s + 64 * i, da + (uint64_t)(2 * ks), db + (uint64_t)(2 * ks), idesc(BN), ks > 0 ? 1u : 0u);
                 }
@@ -312,9 +331,9 @@ __global__ void __launch_bounds__(g2::THREADS, 1) ddlerp_lerp_kernel(const __gri
         const int q = warp & 3, h = warp >> 2;       // lane quarter of tensor memory, stream pair
         const int r = 32 * q + lane;                 // token row of the tile
         for (int n = 0; n < nmine; ++n) {
-            const int u = (int)blockIdx.x + n * (int)gridDim.x, s = n & 1;
+            const int u = u_lo + n, s = n & 1;
             const int cb = u % ncb, tile = u / ncb, t0 = (tile % tiles_per_seq) * BM, bi = tile / tiles_per_seq;
-            const unsigned char* smX = sm + s * stage_bytes(D) + ops_bytes(D);
+            const unsigned char* smX = smSt + s * stage_bytes(D) + r_bytes(D);
             // this unit's beta values (buffer s): the first warp of a stream pair loads the pair's 2 x 64 values; the named barrier
             // below publishes them to the pair's four warps.  Buffer s is written again two units later, after every warp of
             // the pair has passed the next unit's barrier, i.e. has finished this unit.
@@ -330,7 +349,15 @@ __global__ void __launch_bounds__(g2::THREADS, 1) ddlerp_lerp_kernel(const __gri
             if (h == 0) asm volatile("bar.sync 1, 128;" ::: "memory");  // the four warps of a stream pair: beta visible
             else asm volatile("bar.sync 2, 128;" ::: "memory");
             const bool ok = !ctrl->abort;
-#pragma unroll 1
+            // both streams' accumulator columns of all four 16-channel groups are requested before the first is used, so
+            // that the tensor-memory read latency is paid once per unit
+            uint32_t v[2][BN / 16][16];
+#pragma unroll
+            for (int ii = 0; ii < 2; ++ii)
+#pragma unroll
+                for (int cc = 0; cc < BN / 16; ++cc) tmem_ld16(tmem + ((uint32_t)(32 * q) << 16) + 256 * s + 64 * (2 * h + ii) + 16 * cc, v[ii][cc]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
             for (int cc = 0; cc < BN / 16; ++cc) {
                 float xv[16], xx[16];
 #pragma unroll
@@ -344,17 +371,14 @@ __global__ void __launch_bounds__(g2::THREADS, 1) ddlerp_lerp_kernel(const __gri
 #pragma unroll
                 for (int ii = 0; ii < 2; ++ii) {
                     const int i = 2 * h + ii;
-                    uint32_t v[16];
-                    tmem_ld16(tmem + ((uint32_t)(32 * q) << 16) + 256 * s + 64 * i + 16 * cc, v);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     float y[16];
 #pragma unroll
                     for (int k4 = 0; k4 < 4; ++k4) {
                         const float4 b = *reinterpret_cast<const float4*>(&ctrl->beta[s][i][16 * cc + 4 * k4]);
-                        y[4 * k4 + 0] = xv[4 * k4 + 0] + xx[4 * k4 + 0] * (__uint_as_float(v[4 * k4 + 0]) + b.x);
-                        y[4 * k4 + 1] = xv[4 * k4 + 1] + xx[4 * k4 + 1] * (__uint_as_float(v[4 * k4 + 1]) + b.y);
-                        y[4 * k4 + 2] = xv[4 * k4 + 2] + xx[4 * k4 + 2] * (__uint_as_float(v[4 * k4 + 2]) + b.z);
-                        y[4 * k4 + 3] = xv[4 * k4 + 3] + xx[4 * k4 + 3] * (__uint_as_float(v[4 * k4 + 3]) + b.w);
+                        y[4 * k4 + 0] = xv[4 * k4 + 0] + xx[4 * k4 + 0] * (__uint_as_float(v[ii][cc][4 * k4 + 0]) + b.x);
+                        y[4 * k4 + 1] = xv[4 * k4 + 1] + xx[4 * k4 + 1] * (__uint_as_float(v[ii][cc][4 * k4 + 1]) + b.y);
+                        y[4 * k4 + 2] = xv[4 * k4 + 2] + xx[4 * k4 + 2] * (__uint_as_float(v[ii][cc][4 * k4 + 2]) + b.z);
+                        y[4 * k4 + 3] = xv[4 * k4 + 3] + xx[4 * k4 + 3] * (__uint_as_float(v[ii][cc][4 * k4 + 3]) + b.w);
                     }
 #pragma unroll
                     for (int hh = 0; hh < 2; ++hh) {
