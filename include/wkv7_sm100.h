@@ -198,6 +198,19 @@ int wkv7_ddlerp_bwd(const void* x, const void* alpha, const void* L, const void*
                     int64_t B, int64_t T, int64_t C, int64_t D, void* stream);
 
 /*
+ * ddlerp backward with dL = dpre^T u formed on the tcgen05 tensor cores (as dW12 = dpre^T [x_t | x_{t-1}] over bulk
+ * tensor loads, then dL = dW1 (1 - alpha) + dW2 alpha); everything else as wkv7_ddlerp_bwd.  `workspace`:
+ * wkv7_ddlerp_bwd_tc_workspace_bytes(C, D) bytes of device scratch, 16-byte aligned, overwritten.  dL differs from
+ * wkv7_ddlerp_bwd's by bf16 rounding (there u is rounded to bf16, here x is used as it is).  May report
+ * WKV7_ERR_DEVICE_TIMEOUT through the status word (bounded waits).
+ */
+size_t wkv7_ddlerp_bwd_tc_workspace_bytes(int64_t C, int64_t D);
+int wkv7_ddlerp_bwd_tc(const void* x, const void* alpha, const void* L, const void* R, const void* beta, const void* m,
+                       const void* dy0, const void* dy1, const void* dy2, const void* dy3, void* dpre_workspace, void* dx,
+                       float* dalpha, float* dL, float* dR, float* dbeta, void* workspace,
+                       int64_t B, int64_t T, int64_t C, int64_t D, void* stream);
+
+/*
  * Projection of the time mixer, forward: C = act(A W^T) with A [M,K], W [N,K] (an nn.Linear weight), C [M,N], all bf16,
  * contiguous; act = tanh on the columns tanh_from <= n < tanh_to (a LoRA's first stage feeds its second through tanh),
  * identity elsewhere (tanh_from == tanh_to: a plain projection).  Replaces the torch matmuls `x @ W.bfloat16().mT` and the

@@ -103,3 +103,38 @@ def test_rejects_bad_shapes():
     ins = [i.cuda() for i in data(1, 32, 96, 16, 0)]
     with pytest.raises(AssertionError):
         ddlerp(*ins)
+
+
+def test_forward_kernels_agree_through_c_abi():
+    """The two forward entry points of the C ABI on the same inputs: wkv7_ddlerp_fwd (mma.sync) and wkv7_ddlerp_fwd_tc
+    (tcgen05 + TMA, shift folded into the weights).  They round different intermediates to bf16 (u there, the
+    shifted weights here), so m and y agree to bf16 rounding: relative L2 <= 6e-3, and each within 1e-2 of the
+    float64 oracle.  Includes a ragged length (T = 200: tiles of 128 tokens clip) and a batch of sequences
+    (the row before each sequence's first token must read as zero, not as the previous sequence's last row)."""
+    import wkv7_ref
+    from wind_rwkv.rwkv7 import _lib
+    lib = _lib.lib()
+    for (B, T, C, D, seed) in [(3, 200, 256, 32, 11), (2, 128, 128, 16, 12)]:
+        ins = data(B, T, C, D, seed)
+        ys_ref = wkv7_ref.ref_ddlerp(*[i.double() for i in ins], compute_dtype=th.float64)
+        x, al, L, R, be = [i.cuda().contiguous() for i in ins]
+        outs = []
+        for tc in (False, True):
+            m = th.empty(B, T, 4 * D, dtype=th.bfloat16, device='cuda')
+            y = th.empty(4, B, T, C, dtype=th.bfloat16, device='cuda')
+            if tc:
+                ws = th.empty(lib.wkv7_ddlerp_fwd_tc_workspace_bytes(C, D), dtype=th.uint8, device='cuda')
+                rc = lib.wkv7_ddlerp_fwd_tc(x.data_ptr(), al.data_ptr(), L.data_ptr(), R.data_ptr(), be.data_ptr(), m.data_ptr(),
+                                            y.data_ptr(), ws.data_ptr(), B, T, C, D, _lib.stream_of(x))
+            else:
+                rc = lib.wkv7_ddlerp_fwd(x.data_ptr(), al.data_ptr(), L.data_ptr(), R.data_ptr(), be.data_ptr(), m.data_ptr(),
+                                         y.data_ptr(), B, T, C, D, _lib.stream_of(x))
+            assert rc == 0
+            th.cuda.synchronize()
+            assert _lib.device_status() == 0
+            outs.append((m.float().cpu(), y.float().cpu()))
+        (m0, y0), (m1, y1) = outs
+        assert rel_l2(m1, m0.numpy()) <= 6e-3 and rel_l2(y1, y0.numpy()) <= 6e-3
+        for k in range(4):
+            for y in (y0, y1):
+                assert rel_l2(y[k], ys_ref[k].numpy()) <= 1e-2

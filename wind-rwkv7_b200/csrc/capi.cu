@@ -348,12 +348,13 @@ int wkv7_ddlerp_fwd_tc(const void* x, const void* alpha, const void* L, const vo
     return wkv7::launch_ddlerp_fwd_tc(p, workspace, status, (cudaStream_t)stream);
 }
 
-int wkv7_ddlerp_bwd(const void* x, const void* alpha, const void* L, const void* R, const void* beta, const void* m,
-                    const void* dy0, const void* dy1, const void* dy2, const void* dy3, void* dpre_workspace, void* dx,
-                    float* dalpha, float* dL, float* dR, float* dbeta, int64_t B, int64_t T, int64_t C, int64_t D,
-                    void* stream) {
+static int ddlerp_bwd_any(const void* x, const void* alpha, const void* L, const void* R, const void* beta, const void* m,
+                          const void* dy0, const void* dy1, const void* dy2, const void* dy3, void* dpre_workspace, void* dx,
+                          float* dalpha, float* dL, float* dR, float* dbeta, void* workspace, bool tc, int64_t B, int64_t T, int64_t C,
+                          int64_t D, void* stream) {
     int rc = ddlerp_check(B, T, C, D);
     if (rc) return rc;
+    if (tc && (!workspace || !aligned16(workspace))) return workspace ? WKV7_ERR_ALIGN : WKV7_ERR_NULL;
     const void* ptrs[] = {x, alpha, L, R, beta, m, dy0, dy1, dy2, dy3, dpre_workspace, dx, dalpha, dL, dR, dbeta};
     for (const void* q : ptrs) {
         if (!q) return WKV7_ERR_NULL;
@@ -371,7 +372,29 @@ int wkv7_ddlerp_bwd(const void* x, const void* alpha, const void* L, const void*
             return WKV7_ERR_LAUNCH;
         return WKV7_OK;
     }
-    return wkv7::launch_ddlerp_bwd(p, (cudaStream_t)stream);
+    if (!tc) return wkv7::launch_ddlerp_bwd(p, (cudaStream_t)stream);
+    int* status = status_ptr();
+    if (!status) return WKV7_ERR_LAUNCH;
+    return wkv7::launch_ddlerp_bwd_tc(p, workspace, status, (cudaStream_t)stream);
+}
+
+int wkv7_ddlerp_bwd(const void* x, const void* alpha, const void* L, const void* R, const void* beta, const void* m,
+                    const void* dy0, const void* dy1, const void* dy2, const void* dy3, void* dpre_workspace, void* dx,
+                    float* dalpha, float* dL, float* dR, float* dbeta, int64_t B, int64_t T, int64_t C, int64_t D,
+                    void* stream) {
+    return ddlerp_bwd_any(x, alpha, L, R, beta, m, dy0, dy1, dy2, dy3, dpre_workspace, dx, dalpha, dL, dR, dbeta, nullptr, false, B, T, C, D, stream);
+}
+
+size_t wkv7_ddlerp_bwd_tc_workspace_bytes(int64_t C, int64_t D) {
+    if (C <= 0 || D <= 0) return 0;
+    return wkv7::ddlerp_bwd_tc_workspace_bytes(C, (int)D);
+}
+
+int wkv7_ddlerp_bwd_tc(const void* x, const void* alpha, const void* L, const void* R, const void* beta, const void* m,
+                       const void* dy0, const void* dy1, const void* dy2, const void* dy3, void* dpre_workspace, void* dx,
+                       float* dalpha, float* dL, float* dR, float* dbeta, void* workspace, int64_t B, int64_t T, int64_t C, int64_t D,
+                       void* stream) {
+    return ddlerp_bwd_any(x, alpha, L, R, beta, m, dy0, dy1, dy2, dy3, dpre_workspace, dx, dalpha, dL, dR, dbeta, workspace, true, B, T, C, D, stream);
 }
 
 static int loras_check(int64_t B, int64_t T, int64_t C, int64_t D) {

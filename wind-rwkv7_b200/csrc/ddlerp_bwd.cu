@@ -428,7 +428,7 @@ __global__ void __launch_bounds__(256) ddlerp_bwd_dL_kernel(DdlerpBwdParams p, l
     }
 }
 
-template <int D> static int launch_ddlerp_bwd_t(const DdlerpBwdParams& p, cudaStream_t stream) {
+template <int D> static int launch_ddlerp_bwd_t(const DdlerpBwdParams& p, cudaStream_t stream, void* ws = nullptr, int* status = nullptr) {
     const long long B = p.rows / p.T;
     const int C = (int)p.C;
     if (cudaMemsetAsync(p.dalpha, 0, sizeof(float) * C, stream) != cudaSuccess) return kLaunchFailed;
@@ -467,7 +467,10 @@ template <int D> static int launch_ddlerp_bwd_t(const DdlerpBwdParams& p, cudaSt
         kern<<<dim3((unsigned)(C / 64), (unsigned)(B * segs)), 256, smem, stream>>>(p, segs, tiles_per_seg);
         if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
     }
-    {
+    if (ws) {  // dL on the tensor cores
+        const int rc = launch_ddlerp_dL_tc(p, ws, status, stream);
+        if (rc != kOk) return rc;
+    } else {
         auto kern = ddlerp_bwd_dL_kernel<D>;
         const int smem = (int)sizeof(DLSmem<D>);
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kLaunchFailed;
@@ -481,6 +484,15 @@ template <int D> static int launch_ddlerp_bwd_t(const DdlerpBwdParams& p, cudaSt
         if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
     }
     return kOk;
+}
+
+int launch_ddlerp_bwd_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream) {
+    switch (p.D) {
+        case 16: return launch_ddlerp_bwd_t<16>(p, stream, ws, status);
+        case 32: return launch_ddlerp_bwd_t<32>(p, stream, ws, status);
+        case 64: return launch_ddlerp_bwd_t<64>(p, stream, ws, status);
+        default: return kBadShape;
+    }
 }
 
 int launch_ddlerp_bwd(const DdlerpBwdParams& p, cudaStream_t stream) {

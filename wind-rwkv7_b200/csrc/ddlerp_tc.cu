@@ -414,6 +414,127 @@ __global__ void __launch_bounds__(g2::THREADS, 1) ddlerp_lerp_kernel(const __gri
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(NCOLS) : "memory");
 }
 
+// ------------------------------------------------------------------------------------------------------------------------
+// dL of the backward on the tensor cores.  With W12 = [L (1 - alpha) | L alpha] (see the forward):
+//     dW12 = dpre^T [x_t | x_{t-1}]   ([4D, 2C], contraction over all tokens),      dL = dW1 (1 - alpha) + dW2 alpha.
+// Both operands are read as they lie in memory, token-major, i.e. MN-major for a product that contracts over tokens:
+// A = dpre^T from [128 tokens][64 columns] boxes of dpre, B = x from [128 tokens][64 channels] boxes of x (the second half
+// of the columns one time step earlier, by the copy's coordinate).  One CTA owns 128 rows x 256 columns of dW12 and a
+// contiguous range of token tiles; its fp32 accumulator stays in tensor memory over the whole range and is added to global
+// memory once (vector reductions): dW1 straight into dL, dW2 into a scratch array; a small kernel then forms dL in place.
+namespace g3 {
+constexpr int BN = 256, STAGES = 2;
+constexpr int A_BYTES = 2 * BM * 128, B_BYTES = (BN / 64) * BM * 128, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;  // warps 0-3: epilogue, warp 4: TMA, warp 5: MMA
+struct Ctrl {
+    uint64_t full[STAGES], empty[STAGES], accum;
+    uint32_t tmem_base;
+    volatile int abort;
+};
+// MN-major operand: [k = token][64 columns] boxes with the 128-byte swizzle; 8 token rows = 1024 bytes (SBO), next 64
+// columns = next box of 128 tokens = 16384 bytes (LBO)
+__device__ __forceinline__ uint64_t desc_mn(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3fff) | ((uint64_t)(16384 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// fp32 accumulate, bf16 operands, both MN-major, M = 128, N = 256
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}  // namespace g3
+
+// mapD: dpre as (column, time, batch), box 64 x 128 x 1;  mapX: x as (channel, time, batch), box 64 x 128 x 1.
+// grid: (column tiles of 256: first the x_t half, then the x_{t-1} half; token splits; row tiles of 128 of the 4D rows)
+__global__ void __launch_bounds__(g3::THREADS) ddlerp_dw12_kernel(const __grid_constant__ CUtensorMap mapD, const __grid_constant__ CUtensorMap mapX,
+                                                                 float* __restrict__ dW1, float* __restrict__ dW2, int C, int n4, int tiles_per_seq,
+                                                                 int total_tiles, int* status) {
+    using namespace g3;
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* sm = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+    Ctrl* ctrl = reinterpret_cast<Ctrl*>(sm + STAGES * STAGE_BYTES);
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+    const int tiles_per_half = (C + BN - 1) / BN;
+    const int half = blockIdx.x / tiles_per_half, c0 = (blockIdx.x % tiles_per_half) * BN, m0 = blockIdx.z * BM;
+    const int lo = (int)((long long)total_tiles * blockIdx.y / gridDim.y), hi = (int)((long long)total_tiles * (blockIdx.y + 1) / gridDim.y);
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&ctrl->full[s], 1); mbar_init(&ctrl->empty[s], 1); }
+        mbar_init(&ctrl->accum, 1);
+        ctrl->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctrl->tmem_base)), "r"(BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = ctrl->tmem_base;
+
+    if (warp == 4) {
+        if (elect_one()) {
+            for (int i = lo; i < hi; ++i) {
+                const int n = i - lo, s = n % STAGES, round = n / STAGES;
+                const int t0 = (i % tiles_per_seq) * BM, bi = i / tiles_per_seq;
+                if (round > 0) mbar_wait_bounded<true>(&ctrl->empty[s], (round - 1) & 1, &ctrl->abort, status);
+                const uint32_t dst = smem_u32(sm + s * STAGE_BYTES);
+                mbar_expect(&ctrl->full[s], (uint32_t)STAGE_BYTES);
+#pragma unroll
+                for (int b = 0; b < 2; ++b) tma_load_3d(dst + b * (BM * 128), &mapD, &ctrl->full[s], m0 + 64 * b, t0, bi);  // columns beyond 4D: zeros
+#pragma unroll
+                for (int b = 0; b < BN / 64; ++b) tma_load_3d(dst + A_BYTES + b * (BM * 128), &mapX, &ctrl->full[s], c0 + 64 * b, t0 - half, bi);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 5) {
+        if (elect_one()) {
+            for (int i = lo; i < hi; ++i) {
+                const int n = i - lo, s = n % STAGES, round = n / STAGES;
+                mbar_wait_bounded<false>(&ctrl->full[s], round & 1, &ctrl->abort, status);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t da = desc_mn(smem_u32(sm + s * STAGE_BYTES)), db = desc_mn(smem_u32(sm + s * STAGE_BYTES + A_BYTES));
+#pragma unroll
+                for (int ks = 0; ks < BM / 16; ++ks)  // 16 tokens = two groups of 8 rows = 2048 bytes per step
+                    mma_f16(tmem, da + (uint64_t)(ks * (2048 >> 4)), db + (uint64_t)(ks * (2048 >> 4)), IDESC, (n > 0 || ks > 0) ? 1u : 0u);
+                tc_commit(&ctrl->empty[s]);
+            }
+            tc_commit(&ctrl->accum);
+        }
+        __syncwarp();
+    } else if (hi > lo) {
+        // epilogue: lane = row m0 + 32 warp + lane of dW12, 256 columns; added to global memory with 16-byte reductions
+        mbar_wait_bounded<true>(&ctrl->accum, 0, &ctrl->abort, status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int row = m0 + 32 * warp + lane;
+        float* out = (half ? dW2 : dW1) + (long long)row * C + c0;
+        const bool ok = !ctrl->abort && row < n4;
+#pragma unroll 1
+        for (int cb = 0; cb < BN; cb += 16) {
+            uint32_t v[16];
+            tmem_ld16(tmem + ((uint32_t)(32 * warp) << 16) + cb, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (ok) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    if (c0 + cb + 4 * q < C)
+                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + cb + 4 * q), "f"(__uint_as_float(v[4 * q])),
+                                     "f"(__uint_as_float(v[4 * q + 1])), "f"(__uint_as_float(v[4 * q + 2])), "f"(__uint_as_float(v[4 * q + 3])) : "memory");
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
+}
+
+// dL = dW1 (1 - alpha) + dW2 alpha, in place (dL holds dW1 on entry)
+__global__ void ddlerp_dl_finish_kernel(float* __restrict__ dL, const float* __restrict__ dW2, const __nv_bfloat16* __restrict__ alpha, int C, long long n) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float a = __bfloat162float(alpha[i % C]);
+    dL[i] = dL[i] * (1.f - a) + dW2[i] * a;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -458,6 +579,40 @@ template <int D> static int launch_lerp(const CUtensorMap& mM, const CUtensorMap
 }
 
 }  // namespace dtc
+
+size_t ddlerp_bwd_tc_workspace_bytes(long long C, int D) { return (size_t)(4 * D) * (size_t)C * 4; }
+
+// dL (fp32 [4D, C], zero on entry) from dpre and x; ws: ddlerp_bwd_tc_workspace_bytes(C, D) bytes
+int launch_ddlerp_dL_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream) {
+    using namespace dtc;
+    const long long B = p.rows / p.T, C = p.C, T = p.T;
+    const int n4 = 4 * p.D;
+    float* dW2 = (float*)ws;
+    if (cudaMemsetAsync(dW2, 0, sizeof(float) * n4 * C, stream) != cudaSuccess) return kLaunchFailed;
+    alignas(64) CUtensorMap mD, mX;
+    const long long dd[3] = {n4, T, B}, sd[2] = {n4, T * n4}, dx[3] = {C, T, B}, sx[2] = {C, T * C};
+    const int bx[3] = {64, BM, 1};
+    if (!(encode(&mD, p.dpre, 3, dd, sd, bx) && encode(&mX, p.x, 3, dx, sx, bx))) return kLaunchFailed;
+    const int smem = g3::STAGES * g3::STAGE_BYTES + (int)sizeof(g3::Ctrl) + 1024;
+    if (cudaFuncSetAttribute(ddlerp_dw12_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kLaunchFailed;
+    static const int sms = [] {
+        int dev = 0, n = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        return n;
+    }();
+    const long long tiles_per_seq = (T + BM - 1) / BM, total = tiles_per_seq * B;
+    if (total > 0x7fffffffLL) return kTooLarge;
+    const int col_tiles = 2 * (int)((C + g3::BN - 1) / g3::BN), row_tiles = (n4 + BM - 1) / BM;
+    long long splits = sms / (col_tiles * row_tiles);  // one CTA per SM (a stage pair fills its shared memory)
+    if (splits < 1) splits = 1;
+    if (splits > total) splits = total;
+    dim3 grid((unsigned)col_tiles, (unsigned)splits, (unsigned)row_tiles);
+    ddlerp_dw12_kernel<<<grid, g3::THREADS, smem, stream>>>(mD, mX, p.dL, dW2, (int)C, n4, (int)tiles_per_seq, (int)total, status);
+    if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
+    const long long n = (long long)n4 * C;
+    ddlerp_dl_finish_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p.dL, dW2, (const __nv_bfloat16*)p.alpha, (int)C, n);
+    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
 
 size_t ddlerp_fwd_tc_workspace_bytes(long long C, int D) { return (size_t)(4 * D) * (size_t)(3 * C) * 2; }
 

@@ -49,6 +49,8 @@ _SIGNATURES = {
     'wkv7_ddlerp_fwd_tc': (_int, [_vp] * 8 + [_i64] * 4 + [_vp]),
     'wkv7_ddlerp_fwd_tc_workspace_bytes': (ctypes.c_size_t, [_i64] * 2),
     'wkv7_ddlerp_bwd': (_int, [_vp] * 16 + [_i64] * 4 + [_vp]),
+    'wkv7_ddlerp_bwd_tc': (_int, [_vp] * 17 + [_i64] * 4 + [_vp]),
+    'wkv7_ddlerp_bwd_tc_workspace_bytes': (ctypes.c_size_t, [_i64] * 2),
     'wkv7_expand_loras_fwd': (_int, [_vp] * 18 + [_i64] * 4 + [_vp]),
     'wkv7_expand_loras_bwd_workspace_bytes': (_i64, [_i64] * 4),
     'wkv7_expand_loras_bwd': (_int, [_vp] * 33 + [_i64] * 4 + [_vp]),

@@ -36,12 +36,13 @@ def bw_ddlerp(x, ab, Lb, Rb, bb, m, dy0, dy1, dy2, dy3):
     dL = th.empty(4 * D, C, dtype=th.float32, device=dev)
     dR = th.empty(4, C, D, dtype=th.float32, device=dev)
     dbeta = th.empty(4, 1, 1, C, dtype=th.float32, device=dev)
+    ws = th.empty(_lib.lib().wkv7_ddlerp_bwd_tc_workspace_bytes(C, D), dtype=th.uint8, device=dev)
     with _lib.on_device(x, ab, Lb, Rb, bb, m, dy0, dy1, dy2, dy3):
-        rc = _lib.lib().wkv7_ddlerp_bwd(x.data_ptr(), ab.data_ptr(), Lb.data_ptr(), Rb.data_ptr(), bb.data_ptr(),
-                                        m.data_ptr(), dy0.data_ptr(), dy1.data_ptr(), dy2.data_ptr(), dy3.data_ptr(),
-                                        dpre.data_ptr(), dx.data_ptr(), dalpha.data_ptr(), dL.data_ptr(), dR.data_ptr(),
-                                        dbeta.data_ptr(), B, T, C, D, _lib.stream_of(x))
-    _lib.check(rc, 'wkv7_ddlerp_bwd')
+        rc = _lib.lib().wkv7_ddlerp_bwd_tc(x.data_ptr(), ab.data_ptr(), Lb.data_ptr(), Rb.data_ptr(), bb.data_ptr(),
+                                           m.data_ptr(), dy0.data_ptr(), dy1.data_ptr(), dy2.data_ptr(), dy3.data_ptr(),
+                                           dpre.data_ptr(), dx.data_ptr(), dalpha.data_ptr(), dL.data_ptr(), dR.data_ptr(),
+                                           dbeta.data_ptr(), ws.data_ptr(), B, T, C, D, _lib.stream_of(x))
+    _lib.check(rc, 'wkv7_ddlerp_bwd_tc')
     return dx, dalpha, dL, dR, dbeta
 
 
