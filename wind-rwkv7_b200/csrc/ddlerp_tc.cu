@@ -214,10 +214,11 @@ __global__ void __launch_bounds__(g1::THREADS) ddlerp_gemm1_kernel(const __grid_
 // Persistent: one CTA per SM walks work units (128 tokens of one sequence) x (64 channels), consecutive CTAs taking the
 // channel blocks of the same token tile (its m tile then comes out of L2).  Warp 8 issues the bulk loads of the NEXT unit
 // into the other of two shared-memory stages and the current unit's four products into the other of two accumulator
-// sets; warps 0-7 are the epilogue (warp w: token rows 32 (w % 4) ..., streams 2 (w / 4) and 2 (w / 4) + 1).
+// sets; warps 0-7 are the epilogue (warp w: token rows 32 (w % 4) ..., streams SPW (w / 4) ... SPW (w / 4) + SPW - 1).
 namespace g2 {
 constexpr int BN = 64;            // channels per unit
-constexpr int EPI_WARPS = 8, THREADS = 32 * (EPI_WARPS + 1);
+constexpr int SPW = 2;           // streams per epilogue warp (1: sixteen epilogue warps; measured equal)
+constexpr int EPI_WARPS = 4 * (4 / SPW), THREADS = 32 * (EPI_WARPS + 1);
 constexpr int XROWS = BM + 1;     // the x tile starts one token early: row r holds x_{t0 + r - 1}
 constexpr int X_BYTES = ((XROWS * 128 + 1023) / 1024) * 1024, OUT_BYTES = BM * BN * 2;
 struct Ctrl {
@@ -328,34 +329,38 @@ __global__ void __launch_bounds__(g2::THREADS, 1) ddlerp_lerp_kernel(const __gri
         }
         __syncwarp();
     } else {
-        const int q = warp & 3, h = warp >> 2;       // lane quarter of tensor memory, stream pair
+        const int q = warp & 3, h = warp >> 2;       // lane quarter of tensor memory, stream group
         const int r = 32 * q + lane;                 // token row of the tile
         for (int n = 0; n < nmine; ++n) {
             const int u = u_lo + n, s = n & 1;
             const int cb = u % ncb, tile = u / ncb, t0 = (tile % tiles_per_seq) * BM, bi = tile / tiles_per_seq;
             const unsigned char* smX = smSt + s * stage_bytes(D) + r_bytes(D);
-            // this unit's beta values (buffer s): the first warp of a stream pair loads the pair's 2 x 64 values; the named barrier
+            // this unit's beta values (buffer s): the first warp of a stream group loads the group's SPW x 64 values; the named barrier
             // below publishes them to the pair's four warps.  Buffer s is written again two units later, after every warp of
             // the pair has passed the next unit's barrier, i.e. has finished this unit.
             if (q == 0) {
-                for (int i = lane; i < 2 * BN; i += 32)
-                    ctrl->beta[s][2 * h + i / BN][i % BN] = __bfloat162float(beta[(long long)(2 * h + i / BN) * C + cb * BN + (i % BN)]);
+                for (int i = lane; i < SPW * BN; i += 32)
+                    ctrl->beta[s][SPW * h + i / BN][i % BN] = __bfloat162float(beta[(long long)(SPW * h + i / BN) * C + cb * BN + (i % BN)]);
             }
             mbar_wait_bounded<true>(&ctrl->xs[s], (n >> 1) & 1, &ctrl->abort, status);
             mbar_wait_bounded<true>(&ctrl->accum[s], (n >> 1) & 1, &ctrl->abort, status);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // the previous unit's stores out of this warp's staging rows must have been read
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-            if (h == 0) asm volatile("bar.sync 1, 128;" ::: "memory");  // the four warps of a stream pair: beta visible
-            else asm volatile("bar.sync 2, 128;" ::: "memory");
+            switch (h) {  // the four warps of a stream group: beta visible
+                case 0: asm volatile("bar.sync 1, 128;" ::: "memory"); break;
+                case 1: asm volatile("bar.sync 2, 128;" ::: "memory"); break;
+                case 2: asm volatile("bar.sync 3, 128;" ::: "memory"); break;
+                default: asm volatile("bar.sync 4, 128;" ::: "memory"); break;
+            }
             const bool ok = !ctrl->abort;
             // both streams' accumulator columns of all four 16-channel groups are requested before the first is used, so
             // that the tensor-memory read latency is paid once per unit
-            uint32_t v[2][BN / 16][16];
+            uint32_t v[SPW][BN / 16][16];
 #pragma unroll
-            for (int ii = 0; ii < 2; ++ii)
+            for (int ii = 0; ii < SPW; ++ii)
 #pragma unroll
-                for (int cc = 0; cc < BN / 16; ++cc) tmem_ld16(tmem + ((uint32_t)(32 * q) << 16) + 256 * s + 64 * (2 * h + ii) + 16 * cc, v[ii][cc]);
+                for (int cc = 0; cc < BN / 16; ++cc) tmem_ld16(tmem + ((uint32_t)(32 * q) << 16) + 256 * s + 64 * (SPW * h + ii) + 16 * cc, v[ii][cc]);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
             for (int cc = 0; cc < BN / 16; ++cc) {
@@ -369,8 +374,8 @@ __global__ void __launch_bounds__(g2::THREADS, 1) ddlerp_lerp_kernel(const __gri
                     for (int j = 0; j < 8; ++j) xx[8 * hh + j] = pv[j] - xv[8 * hh + j];
                 }
 #pragma unroll
-                for (int ii = 0; ii < 2; ++ii) {
-                    const int i = 2 * h + ii;
+                for (int ii = 0; ii < SPW; ++ii) {
+                    const int i = SPW * h + ii;
                     float y[16];
 #pragma unroll
                     for (int k4 = 0; k4 < 4; ++k4) {
@@ -398,9 +403,9 @@ __global__ void __launch_bounds__(g2::THREADS, 1) ddlerp_lerp_kernel(const __gri
                 asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ctrl->acc_free[s])) : "memory");
                 if (ok && t0 + 32 * q < T) {
 #pragma unroll
-                    for (int ii = 0; ii < 2; ++ii)
+                    for (int ii = 0; ii < SPW; ++ii)
                         asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];"
-                                     ::"l"(&mapY), "r"(cb * BN), "r"(t0 + 32 * q), "r"(bi), "r"(2 * h + ii), "r"(smem_u32(smOut + (2 * h + ii) * OUT_BYTES + 32 * q * 128)) : "memory");
+                                     ::"l"(&mapY), "r"(cb * BN), "r"(t0 + 32 * q), "r"(bi), "r"(SPW * h + ii), "r"(smem_u32(smOut + (SPW * h + ii) * OUT_BYTES + 32 * q * 128)) : "memory");
                 }
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
