@@ -52,6 +52,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Abort path: a bounded wait gave up, later waits fall through.  The thread that issued tensor-core products commits them
+// to a barrier of its own and waits for it, bounded and regardless of the abort flag, before tensor memory is released.
+__device__ __forceinline__ void drain_products(uint64_t* bar, volatile int* never_set, int* status) {
+    tc_commit(bar);
+    mbar_wait_bounded<false>(bar, 0, never_set, status);
+}
 // K-major operand block with 128-byte rows and the 128-byte swizzle: 8-row groups 1024 bytes apart
 __device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
     return (uint64_t)((saddr >> 4) & 0x3fff) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
@@ -107,9 +113,9 @@ constexpr int BN = 128, STAGES = 3;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;  // warps 0-3: epilogue (tensor-memory lane quarters 0-3), warp 4: TMA, warp 5: MMA
 struct Ctrl {
-    uint64_t full[STAGES], empty[STAGES], accum;
+    uint64_t full[STAGES], empty[STAGES], accum, drain;
     uint32_t tmem_base;
-    volatile int abort;
+    volatile int abort, zero;
 };
 }  // namespace g1
 
@@ -127,8 +133,8 @@ __global__ void __launch_bounds__(g1::THREADS) ddlerp_gemm1_kernel(const __grid_
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&ctrl->full[s], 1); mbar_init(&ctrl->empty[s], 1); }
-        mbar_init(&ctrl->accum, 1);
-        ctrl->abort = 0;
+        mbar_init(&ctrl->accum, 1); mbar_init(&ctrl->drain, 1);
+        ctrl->abort = 0; ctrl->zero = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -166,6 +172,7 @@ __global__ void __launch_bounds__(g1::THREADS) ddlerp_gemm1_kernel(const __grid_
                 tc_commit(&ctrl->empty[s]);  // the stage may be refilled once these products have read it
             }
             tc_commit(&ctrl->accum);
+            if (ctrl->abort) drain_products(&ctrl->drain, &ctrl->zero, status);
         }
         __syncwarp();
     } else {
@@ -225,8 +232,9 @@ struct Ctrl {
     uint64_t ops[2], xs[2], accum[2];   // per stage: R' tile landed; x tile landed; per accumulator set: products complete
     uint64_t mfull[2];                  // per m buffer: tile landed
     uint64_t stage_free[2], acc_free[2];  // the epilogue warps are done with the stage's x tile / the accumulator set
+    uint64_t drain;                     // abort path only
     uint32_t tmem_base;
-    volatile int abort;
+    volatile int abort, zero;
     alignas(16) float beta[2][4][BN];   // read as float4
 };
 static_assert(offsetof(Ctrl, beta) % 16 == 0, "beta is read with 16-byte loads");
@@ -262,7 +270,8 @@ __global__ void __launch_bounds__(g2::THREADS, 1) ddlerp_lerp_kernel(const __gri
             mbar_init(&ctrl->stage_free[s], EPI_WARPS); mbar_init(&ctrl->acc_free[s], EPI_WARPS);
             mbar_init(&ctrl->mfull[s], 1);
         }
-        ctrl->abort = 0;
+        mbar_init(&ctrl->drain, 1);
+        ctrl->abort = 0; ctrl->zero = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -326,6 +335,7 @@ __global__ void __launch_bounds__(g2::THREADS, 1) ddlerp_lerp_kernel(const __gri
                 }
                 tc_commit(&ctrl->accum[s]);
             }
+            if (ctrl->abort) drain_products(&ctrl->drain, &ctrl->zero, status);
         }
         __syncwarp();
     } else {
@@ -432,9 +442,9 @@ constexpr int BN = 256, STAGES = 2;
 constexpr int A_BYTES = 2 * BM * 128, B_BYTES = (BN / 64) * BM * 128, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;  // warps 0-3: epilogue, warp 4: TMA, warp 5: MMA
 struct Ctrl {
-    uint64_t full[STAGES], empty[STAGES], accum;
+    uint64_t full[STAGES], empty[STAGES], accum, drain;
     uint32_t tmem_base;
-    volatile int abort;
+    volatile int abort, zero;
 };
 // MN-major operand: [k = token][64 columns] boxes with the 128-byte swizzle; 8 token rows = 1024 bytes (SBO), next 64
 // columns = next box of 128 tokens = 16384 bytes (LBO)
@@ -462,8 +472,8 @@ __global__ void __launch_bounds__(g3::THREADS) ddlerp_dw12_kernel(const __grid_c
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&ctrl->full[s], 1); mbar_init(&ctrl->empty[s], 1); }
-        mbar_init(&ctrl->accum, 1);
-        ctrl->abort = 0;
+        mbar_init(&ctrl->accum, 1); mbar_init(&ctrl->drain, 1);
+        ctrl->abort = 0; ctrl->zero = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -504,6 +514,7 @@ __global__ void __launch_bounds__(g3::THREADS) ddlerp_dw12_kernel(const __grid_c
                 tc_commit(&ctrl->empty[s]);
             }
             tc_commit(&ctrl->accum);
+            if (ctrl->abort) drain_products(&ctrl->drain, &ctrl->zero, status);
         }
         __syncwarp();
     } else if (hi > lo) {

@@ -26,9 +26,9 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTE
 constexpr int THREADS = 192;  // warps 0-3: epilogue (tensor-memory lane quarters 0-3), warp 4: TMA, warp 5: MMA
 
 struct Ctrl {
-    uint64_t full[STAGES], empty[STAGES], accum;
+    uint64_t full[STAGES], empty[STAGES], accum, drain;
     uint32_t tmem_base;
-    volatile int abort;
+    volatile int abort, zero;
 };
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -65,8 +65,8 @@ __global__ void __launch_bounds__(THREADS) proj_gemm_kernel(const __grid_constan
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&ctrl->full[s], 1); mbar_init(&ctrl->empty[s], 1); }
-        mbar_init(&ctrl->accum, 1);
-        ctrl->abort = 0;
+        mbar_init(&ctrl->accum, 1); mbar_init(&ctrl->drain, 1);
+        ctrl->abort = 0; ctrl->zero = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -109,6 +109,12 @@ __global__ void __launch_bounds__(THREADS) proj_gemm_kernel(const __grid_constan
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&ctrl->empty[s])) : "memory");
             }
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&ctrl->accum)) : "memory");
+            if (ctrl->abort) {
+                // a bounded wait gave up and the later waits fell through: commit everything issued to a barrier of its own and
+                // wait for it, bounded and regardless of the abort flag, before tensor memory is released
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&ctrl->drain)) : "memory");
+                mbar_wait_bounded<false>(&ctrl->drain, 0, &ctrl->zero, status);
+            }
         }
         __syncwarp();
     } else {
