@@ -220,6 +220,23 @@ def run_prefill(args):
     if dist:
         ms = max_over_ranks(ms, dist, dev)
     ms /= args.steps
+    # the same call with the chains of the last, partly filled round of SMs cut in time (a no-op split where the shard has no such tail)
+    tstep = lambda: attn(*ins, N, s0=d['s0'], return_state=True, time_split='tail')
+    with th.no_grad():
+        for _ in range(2):
+            tstep()
+        th.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        e0.record()
+        for _ in range(args.steps):
+            tstep()
+        e1.record()
+        th.cuda.synchronize()
+    tms = e0.elapsed_time(e1)
+    if dist:
+        tms = max_over_ranks(tms, dist, dev)
+    tms /= args.steps
     finite = bool(th.isfinite(sT).all()) and bool(th.isfinite(y[:, -1]).all())
     status = _lib.device_status()
     if rank == 0:
@@ -235,6 +252,7 @@ def run_prefill(args):
             'roofline': {'bound': 'hbm', 'kernel': 'wkv7_fwd_tc_kernel (tcgen05)', 'achieved': alg / world / (ms * 1e-3) / 1e9, 'peak': peak,
                          'unit': 'GB/s', 'frac': alg / world / (ms * 1e-3) / 1e9 / peak, 'peak_source': which,
                          'algorithmic_bytes': alg // world, 'traffic': None, 'note': 'per GPU'},
+            'tail_split': {'ms_per_step': tms, 'value': Bt * Tn / (tms * 1e-3) / 1e6, 'note': "attn(..., time_split='tail')"},
             'gpu_launches': args.steps, 'clocks': clocks.summary(), 'finite': finite, 'device_status': status}))
     if dist:
         dist.destroy_process_group()
@@ -479,8 +497,9 @@ def run_ours(args):
                     ol = other_line(wl, None, 5, 3)
                     sec[wl] = {'workload': ol['config']['workload'], 'value': ol['value'], 'unit': ol['unit'], 'ms_per_step': ol['ms_per_step'],
                                'roofline_frac': None if ol['roofline'] is None else ol['roofline']['frac'], 'steps': 5}
-                    if 'cuda_graph' in ol:
-                        sec[wl]['cuda_graph'] = ol['cuda_graph']
+                    for extra in ('cuda_graph', 'tail_split', 'unsplit_ms_per_step'):
+                        if extra in ol:
+                            sec[wl][extra] = ol[extra]
                 except Exception as e:
                     sec[wl] = {'error': repr(e)[:200]}
                 th.cuda.empty_cache()
@@ -625,6 +644,21 @@ def other_line(wl, batch, steps, warmup):
                                                    'frac': alg / (ms * 1e-3) / 1e9 / peak, 'peak_source': which,
                                                    'algorithmic_bytes': alg, 'note': 'whole step (all kernels of the op, forward and backward)'},
             'clocks': clocks.summary()}
+    if wl == 'prefill':  # the same call with the chains of the last, partly filled round of SMs cut in time
+        with th.no_grad():
+            tl = lambda: attn(*ins, N, s0=d['s0'], return_state=True, time_split='tail')
+            for _ in range(2):
+                tl()
+            th.cuda.synchronize()
+            u0, u1 = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
+            u0.record()
+            for _ in range(3):
+                tl()
+            u1.record()
+            th.cuda.synchronize()
+        tms = u0.elapsed_time(u1) / 3
+        line['tail_split'] = {'ms_per_step': tms, 'value': tokens / (tms * 1e-3) / 1e6, 'roofline_frac': alg / (tms * 1e-3) / 1e9 / peak,
+                              'note': "attn(..., time_split='tail')"}
     if wl == 'prefill_b1':  # the same sequence as one chain per head, for comparison
         with th.no_grad():
             one = lambda: attn(*ins, N, s0=d['s0'], return_state=True)

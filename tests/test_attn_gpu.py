@@ -393,3 +393,39 @@ def test_time_split_forward(nseg):
     yo, sTo = c_oracle.wkv7_fwd(*cpu)
     assert maxabs_rms(y.view(B, 512, H, N), yo) <= 1e-4 and maxabs_rms(sT, sTo) <= 1e-4
     assert _lib.device_status() == 0
+
+
+def test_tail_split_forward():
+    """attn(..., time_split='tail'): the chains of the last, partly filled round of SMs are cut in time, the others run
+    as usual, all into views of one output.  Against the unsplit call on every chain (they differ only on the split
+    chains, by the rounding of M) and against the oracle on the last batch entry (which holds the split heads and,
+    next to them, plainly run ones).  Without such a tail the call is the plain forward."""
+    c_oracle, _lib, attn, synthetic, _ = _mods()
+    from wind_rwkv.rwkv7.rwkv7_attn import tail_split_plan
+    sms = th.cuda.get_device_properties(0).multi_processor_count
+    H, T = 40, 8192                        # (the split only pays for long sequences: tail_split_plan declines T = 1024)
+    B = sms // H + 1                       # one round of SMs and a few heads of the last batch entry
+    plan = tail_split_plan(B, T, H, sms)
+    assert plan is not None and plan[0] == B * H - sms
+    d = synthetic.wkv7_inputs(B, T, H, N, seed=41, dtype=th.bfloat16, device='cuda', s0_std=0.1)
+    ins = [d[n] for n in NAMES]
+    with th.no_grad():
+        y, sT = attn(*ins, N, s0=d['s0'], return_state=True, time_split='tail')
+        y1, sT1 = attn(*ins, N, s0=d['s0'], return_state=True)
+    th.cuda.synchronize()
+    h0 = H - plan[0]
+    y4, y14 = y.view(B, T, H, N), y1.view(B, T, H, N)
+    assert th.equal(y4[:B - 1], y14[:B - 1]) and th.equal(y4[B - 1, :, :h0], y14[B - 1, :, :h0])   # plainly run chains: same kernel, same inputs
+    assert th.equal(sT[:B - 1], sT1[:B - 1]) and th.equal(sT[B - 1, :h0], sT1[B - 1, :h0])
+    hs = slice(h0 - 2, H)                  # two plainly run heads and the split ones
+    cpu = [x.view(B, T, H, N)[B - 1:, :, hs].double().cpu().numpy() for x in ins]
+    yo, sTo = c_oracle.wkv7_fwd(*cpu, s0=d['s0'][B - 1:, hs].double().cpu().numpy())
+    check('y', y4[B - 1:, :, hs], yo, th.bfloat16)
+    assert maxabs_rms(sT[B - 1:, hs], sTo) <= 2e-2
+    assert maxabs_rms(sT[B - 1:, h0:], sT1[B - 1:, h0:].double().cpu().numpy()) <= 2e-2
+    # no tail: plain forward, bit for bit
+    d = synthetic.wkv7_inputs(2, 256, 3, N, seed=42, dtype=th.bfloat16, device='cuda')
+    ins = [d[n] for n in NAMES]
+    with th.no_grad():
+        assert th.equal(attn(*ins, N, time_split='tail'), attn(*ins, N))
+    assert _lib.device_status() == 0

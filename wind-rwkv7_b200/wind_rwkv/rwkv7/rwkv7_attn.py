@@ -171,18 +171,129 @@ def _attn_time_split(r, w, k, v, a, b, C, s0, nseg):
     return y.view(B, T, HC), sT.view(B, nseg, H, C, C)[:, -1].contiguous()
 
 
+def _fw_into(w, q, k, v, a, b, s0, y):
+    """Forward without checkpoints into a caller-provided y view that shares the inputs' strides. Returns sT."""
+    B, T, H, C = w.shape
+    assert _same_layout([w, q, k, v, a, b, y]), 'inputs and output must share one layout'
+    sT = th.empty(B, H, C, C, dtype=th.float32, device=w.device)
+    sb, st, sh = _lib.strides4(w)
+    with _lib.on_device(w, q, k, v, a, b, s0):
+        rc = _lib.lib().wkv7_fwd(q.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), b.data_ptr(),
+                                 _lib.ptr(s0), y.data_ptr(), sT.data_ptr(), None, B, T, H, C, sb, st, sh,
+                                 _lib.io_dtype(w), _lib.stream_of(w))
+    _lib.check(rc, 'wkv7_fwd')
+    return sT
+
+
+def tail_split_plan(B, T, H, sms):
+    """(number of chains cut in time, segments) for attn(..., time_split='tail'), or None when it does not pay.
+
+    One CTA walks one chain, so B*H chains take ceil(B*H / sms) rounds of T steps; the last round runs
+    B*H mod sms chains and leaves the other SMs idle.  Those chains (they must lie within the last batch entry)
+    can instead run as n segments each through the affine form (three passes of T/n steps)."""
+    chains = B * H
+    tail = chains % sms
+    if chains <= sms or tail == 0 or tail > H:
+        return None
+    # Cost of the three passes in time steps of one chain: 3 passes x rounds of SMs x (segment length + a chain's start-up,
+    # about 300 steps) + the n - 1 serial start-state products (about 250 steps' worth each: two small launches).
+    # Worth it below the one round of T steps that it replaces (measured on B200: T = 16384, 12 chains: n = 8 is
+    # the fastest of 4 / 8 / 16 / 32, as this model says).
+    best = None
+    for n in range(4, 33):
+        if T % n or (T // n) % 16:
+            continue
+        cost = 3 * -(-tail * n // sms) * (T // n + 300) + (n - 1) * 250
+        if best is None or cost < best[0]:
+            best = (cost, n)
+    return (tail, best[1]) if best and best[0] < 0.85 * T else None
+
+
+_TAIL_STREAMS = {}
+
+
+def _tail_streams(dev):
+    """Two side streams per device, the second of high priority, created once: libraries keep per-stream state (a BLAS
+    handle and its workspace), and a fresh stream on every call would pay for that state again and again."""
+    key = th.device(dev).index if th.device(dev).index is not None else th.cuda.current_device()
+    if key not in _TAIL_STREAMS:
+        _TAIL_STREAMS[key] = [th.cuda.Stream(dev), th.cuda.Stream(dev, priority=-1)]
+    return _TAIL_STREAMS[key]
+
+
+def _attn_tail_split(r, w, k, v, a, b, C, s0):
+    """Forward only.  All chains but those of the last, partly filled round of SMs run as usual; the rest are cut in
+    time (see tail_split_plan and _attn_time_split; here M comes from a pass that starts at the identity state with
+    the real inputs, S_end = M + R, so no zero copy of v is needed).  The three groups of launches go to three
+    streams, write into views of one output tensor (head slices of the last batch entry, no copies) and share the
+    SMs.  Falls back to the plain call when the shape gives no such tail."""
+    B, T, HC = w.shape
+    H = HC // C
+    dev = w.device
+    plan = tail_split_plan(B, T, H, th.cuda.get_device_properties(dev).multi_processor_count)
+    ins = [i.contiguous().view(B, T, H, C) for i in (w, r, k, v, a, b)]
+    y = th.empty(B, T, H, C, dtype=w.dtype, device=dev)
+    s0 = None if s0 is None else s0.float().contiguous()
+    if plan is None:
+        sT = _fw_into(*ins, s0, y)
+        return y.view(B, T, HC), sT
+    tail, n = plan
+    h0, Ts = H - tail, T // n
+    sT = th.empty(B, H, C, C, dtype=th.float32, device=dev)
+    main = th.cuda.current_stream(dev)
+    # the short chains go first and on a high-priority stream, so that their dependent passes are not queued behind
+    # the long chains' second round
+    sides = _tail_streams(dev)
+    for sd in sides:
+        sd.wait_stream(main)
+    with th.cuda.stream(sides[1]):
+        # segments of the last entry's remaining heads as batch entries: [n, Ts, tail, C] views, no copy
+        def seg(x):
+            return x.as_strided((n, Ts, tail, C), (Ts * HC, HC, C, 1), x[B - 1, 0, h0, 0].storage_offset())
+        sin, sy = [seg(i) for i in ins], seg(y)
+        eye = th.eye(C, dtype=th.float32, device=dev).expand(n, tail, C, C).contiguous()
+        R = _fw_into(*sin, None, sy)
+        M = _fw_into(*sin, eye, sy) - R
+        S = th.zeros(tail, C, C, dtype=th.float32, device=dev) if s0 is None else s0[B - 1, h0:]
+        starts = [S]
+        prev = th.backends.cuda.matmul.allow_tf32
+        th.backends.cuda.matmul.allow_tf32 = False
+        try:
+            for j in range(n - 1):
+                S = S @ M[j] + R[j]
+                starts.append(S)
+        finally:
+            th.backends.cuda.matmul.allow_tf32 = prev
+        sT[B - 1, h0:] = _fw_into(*sin, th.stack(starts, 0).contiguous(), sy)[-1]
+    if B > 1:  # whole batch entries
+        sT[:B - 1] = _fw_into(*[i[:B - 1] for i in ins], None if s0 is None else s0[:B - 1].contiguous(), y[:B - 1])
+    if h0 > 0:  # the last entry's heads that still fit the full rounds
+        with th.cuda.stream(sides[0]):
+            sT[B - 1:, :h0] = _fw_into(*[i[B - 1:, :, :h0] for i in ins], None if s0 is None else s0[B - 1:, :h0].contiguous(), y[B - 1:, :, :h0])
+    for sd in sides:
+        main.wait_stream(sd)
+    for t in ins + [y, sT] + ([] if s0 is None else [s0]):
+        for sd in sides:
+            t.record_stream(sd)
+    return y.view(B, T, HC), sT
+
+
 def attn(r, w, k, v, a, b, HEAD_SIZE, *, s0=None, return_state=False, time_split=None):
     """y = WKV7(r,w,k,v,a,b) for [B,T,H*HEAD_SIZE] tensors (upstream: rwkv7_attn.py:53-59).
 
     time_split=n (no upstream counterpart; inference only, no autograd): the sequence runs as n segments in
-    parallel, see _attn_time_split.  Pays when B*H is far below the number of SMs."""
+    parallel, see _attn_time_split.  Pays when B*H is far below the number of SMs.
+    time_split='tail': only the chains of the last, partly filled round of SMs are cut in time, see _attn_tail_split."""
     B, T, HC = w.shape
     C = HEAD_SIZE
     H = HC // C
-    if time_split is not None and time_split > 1:
+    if time_split == 'tail' or (time_split is not None and time_split > 1):
         assert C == _lib.HEAD_SIZE, 'only head size 64 is built'
         assert not (th.is_grad_enabled() and any(i.requires_grad for i in (r, w, k, v, a, b))), 'time_split is forward only'
-        y, sT = _attn_time_split(r, w, k, v, a, b, C, s0, int(time_split))
+        if time_split == 'tail':
+            y, sT = _attn_tail_split(r, w, k, v, a, b, C, s0)
+        else:
+            y, sT = _attn_time_split(r, w, k, v, a, b, C, s0, int(time_split))
         return (y, sT) if return_state else y
     r, w, k, v, a, b = [i.view(B, T, H, C) for i in [r, w, k, v, a, b]]
     y, sT, _ = WindRWKV7.apply(w, r, k, v, a, b, s0)
