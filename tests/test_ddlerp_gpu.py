@@ -138,3 +138,39 @@ def test_forward_kernels_agree_through_c_abi():
         for k in range(4):
             for y in (y0, y1):
                 assert rel_l2(y[k], ys_ref[k].numpy()) <= 1e-2
+
+
+def test_backward_entry_points_agree_through_c_abi():
+    """wkv7_ddlerp_bwd (dL by the mma.sync kernel) and wkv7_ddlerp_bwd_tc (dL on tcgen05 as dpre^T [x_t | x_{t-1}], then
+    combined with alpha) on the same inputs: everything but dL comes from the same kernels and is bit-identical up to
+    the order of the fp32 atomics (relative L2 <= 1e-5); dL agrees to the bf16 rounding of u (<= 6e-3).  T = 200 is not a
+    multiple of the 128-token tiles, and B = 3 checks that x_{t-1} of a sequence's first token reads as zero."""
+    from wind_rwkv.rwkv7 import _lib
+    lib = _lib.lib()
+    B, T, C, D = 3, 200, 256, 32
+    x, al, L, R, be = [i.cuda().contiguous() for i in data(B, T, C, D, 21)]
+    gen = th.Generator().manual_seed(22)
+    dys = [th.randn(B, T, C, generator=gen).bfloat16().cuda() for _ in range(4)]
+    m = th.empty(B, T, 4 * D, dtype=th.bfloat16, device='cuda')
+    y = th.empty(4, B, T, C, dtype=th.bfloat16, device='cuda')
+    assert lib.wkv7_ddlerp_fwd(x.data_ptr(), al.data_ptr(), L.data_ptr(), R.data_ptr(), be.data_ptr(), m.data_ptr(), y.data_ptr(),
+                               B, T, C, D, _lib.stream_of(x)) == 0
+    res = []
+    for tc in (False, True):
+        dpre = th.empty(B, T, 4 * D, dtype=th.bfloat16, device='cuda')
+        dx = th.empty_like(x)
+        f32 = dict(dtype=th.float32, device='cuda')
+        dal, dL, dR, dbe = th.empty(C, **f32), th.empty(4 * D, C, **f32), th.empty(4, C, D, **f32), th.empty(4, C, **f32)
+        args = [x, al, L, R, be, m] + dys + [dpre, dx, dal, dL, dR, dbe]
+        if tc:
+            ws = th.empty(lib.wkv7_ddlerp_bwd_tc_workspace_bytes(C, D), dtype=th.uint8, device='cuda')
+            rc = lib.wkv7_ddlerp_bwd_tc(*[t.data_ptr() for t in args], ws.data_ptr(), B, T, C, D, _lib.stream_of(x))
+        else:
+            rc = lib.wkv7_ddlerp_bwd(*[t.data_ptr() for t in args], B, T, C, D, _lib.stream_of(x))
+        assert rc == 0
+        th.cuda.synchronize()
+        assert _lib.device_status() == 0
+        res.append([t.float().cpu() for t in (dx, dal, dR, dbe, dL)])
+    for a, b in zip(res[0][:4], res[1][:4]):
+        assert rel_l2(b, a.numpy()) <= 1e-5
+    assert rel_l2(res[1][4], res[0][4].numpy()) <= 6e-3
