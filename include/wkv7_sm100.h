@@ -200,7 +200,8 @@ int wkv7_ddlerp_bwd(const void* x, const void* alpha, const void* L, const void*
 /*
  * ddlerp backward with dL = dpre^T u formed on the tcgen05 tensor cores (as dW12 = dpre^T [x_t | x_{t-1}] over bulk
  * tensor loads, then dL = dW1 (1 - alpha) + dW2 alpha); everything else as wkv7_ddlerp_bwd.  `workspace`:
- * wkv7_ddlerp_bwd_tc_workspace_bytes(C, D) bytes of device scratch, 16-byte aligned, overwritten.  dL differs from
+ * wkv7_ddlerp_bwd_tc_workspace_bytes(C, D) bytes of device scratch, 16-byte aligned, overwritten.  At ranks 16 and 32 dpre
+ * is formed on the tensor cores as well (dz = dy * xx in place in bulk-loaded tiles, K = C products with R^T).  dL differs from
  * wkv7_ddlerp_bwd's by bf16 rounding (there u is rounded to bf16, here x is used as it is).  May report
  * WKV7_ERR_DEVICE_TIMEOUT through the status word (bounded waits).
  */

@@ -31,5 +31,6 @@ int launch_ddlerp_bwd(const DdlerpBwdParams& p, cudaStream_t stream);
 size_t ddlerp_bwd_tc_workspace_bytes(long long C, int D);
 int launch_ddlerp_bwd_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream);
 int launch_ddlerp_dL_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream);
+int launch_ddlerp_dpre_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream);  // kBadShape: rank not covered
 
 }  // namespace wkv7

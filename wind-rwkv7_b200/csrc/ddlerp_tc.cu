@@ -551,6 +551,172 @@ __global__ void ddlerp_dl_finish_kernel(float* __restrict__ dL, const float* __r
     dL[i] = dL[i] * (1.f - a) + dW2[i] * a;
 }
 
+// ------------------------------------------------------------------------------------------------------------------------
+// dpre of the backward on the tensor cores:  dm_k = (dy_k * (x_{t-1} - x_t)) R_k  (contraction over all C channels),
+// dpre = dm * (1 - m^2).  One CTA per 128 tokens of one sequence, 64 channels per step through two stages: bulk tensor
+// loads bring the four dy tiles, a 129-row x tile and the block of R^T; four warps turn the dy tiles into dz = dy * xx IN
+// PLACE (eight warps: one token row per thread and two streams per warp; the tiles keep the swizzled K-major layout the copy
+// gave them, so they are the A operands as they stand); one thread issues, per stream k, the K = 64 products into
+// tensor-memory columns k D ...; at the end the same warps read dm, apply the tanh derivative from m and store dpre.
+namespace g4 {
+constexpr int STAGES = 2, THREADS = 320;  // warps 0-7: transform + epilogue (row quarter w % 4, stream pair w / 4), warp 8: TMA, warp 9: MMA
+constexpr int X_BYTES = ((BM + 1) * 128 + 1023) / 1024 * 1024, DY_BYTES = BM * 128;
+struct Ctrl {
+    uint64_t full[STAGES], ready[STAGES], empty[STAGES], accum, drain;
+    uint32_t tmem_base;
+    volatile int abort, zero;
+};
+__host__ __device__ constexpr int rt_bytes(int D) { return 4 * D * 128; }           // [4D rows][64 channels] bf16
+__host__ __device__ constexpr int stage_bytes(int D) { return 4 * DY_BYTES + X_BYTES + (rt_bytes(D) + 1023) / 1024 * 1024; }
+}  // namespace g4
+
+// R^T as [4D, C]: row k D + d = R[k][:, d]
+__global__ void ddlerp_prep_rt_kernel(const __nv_bfloat16* __restrict__ R, __nv_bfloat16* __restrict__ Rt, int C, int D) {
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i >= (long long)4 * D * C) return;
+    const int n = (int)(i / C), c = (int)(i % C), k = n / D, d = n % D;
+    Rt[i] = R[((long long)k * C + c) * D + d];
+}
+
+// mapY: the four dy as (channel, time, batch) each (four maps), box 64 x 128 x 1;  mapX: x, box 64 x 129 x 1;
+// mapRt: R^T as (channel, row), box 64 x 4D;  mapP: dpre as (column, time, batch), box 64 x 32 x 1
+struct DyMaps { CUtensorMap m[4]; };
+template <int D>
+__global__ void __launch_bounds__(g4::THREADS, 1) ddlerp_dpre_tc_kernel(const __grid_constant__ DyMaps mapY, const __grid_constant__ CUtensorMap mapX,
+                                                                       const __grid_constant__ CUtensorMap mapRt, const __grid_constant__ CUtensorMap mapP,
+                                                                       const __nv_bfloat16* __restrict__ m, int C, int T, int* status) {
+    using namespace g4;
+    constexpr int N4 = 4 * D;
+    static_assert(N4 <= 128, "one accumulator of 4D columns and one 128-row block of R^T per stage");
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* sm = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+    Ctrl* ctrl = reinterpret_cast<Ctrl*>(sm + STAGES * stage_bytes(D));
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+    const int t0 = blockIdx.x * BM, bi = blockIdx.y;
+    const int ncb = C / 64;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&ctrl->full[s], 1); mbar_init(&ctrl->ready[s], 8); mbar_init(&ctrl->empty[s], 1); }
+        mbar_init(&ctrl->accum, 1); mbar_init(&ctrl->drain, 1);
+        ctrl->abort = 0; ctrl->zero = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctrl->tmem_base)), "r"(128) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = ctrl->tmem_base;
+
+    if (warp == 8) {
+        if (elect_one()) {
+            for (int cb = 0; cb < ncb; ++cb) {
+                const int s = cb % STAGES, round = cb / STAGES;
+                if (round > 0) mbar_wait_bounded<true>(&ctrl->empty[s], (round - 1) & 1, &ctrl->abort, status);
+                const uint32_t dst = smem_u32(sm + s * stage_bytes(D));
+                mbar_expect(&ctrl->full[s], (uint32_t)(4 * DY_BYTES + (BM + 1) * 128 + rt_bytes(D)));
+#pragma unroll
+                for (int k = 0; k < 4; ++k) tma_load_3d(dst + k * DY_BYTES, &mapY.m[k], &ctrl->full[s], cb * 64, t0, bi);
+                tma_load_3d(dst + 4 * DY_BYTES, &mapX, &ctrl->full[s], cb * 64, t0 - 1, bi);   // row r: x_{t0 + r - 1}; before the sequence: zeros
+                tma_load_2d(dst + 4 * DY_BYTES + X_BYTES, &mapRt, &ctrl->full[s], cb * 64, 0);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 9) {
+        if (elect_one()) {
+            for (int cb = 0; cb < ncb; ++cb) {
+                const int s = cb % STAGES, round = cb / STAGES;
+                mbar_wait_bounded<false>(&ctrl->ready[s], round & 1, &ctrl->abort, status);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t st = smem_u32(sm + s * stage_bytes(D));
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint64_t da = desc_sw128(st + k * DY_BYTES), db = desc_sw128(st + 4 * DY_BYTES + X_BYTES + k * D * 128);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) mma_f16(tmem + k * D, da + (uint64_t)(2 * ks), db + (uint64_t)(2 * ks), idesc(D), (cb > 0 || ks > 0) ? 1u : 0u);
+                }
+                tc_commit(&ctrl->empty[s]);
+            }
+            tc_commit(&ctrl->accum);
+            if (ctrl->abort) drain_products(&ctrl->drain, &ctrl->zero, status);
+        }
+        __syncwarp();
+    } else {
+        const int q = warp & 3, g = warp >> 2;  // row quarter (= tensor-memory lane quarter), stream pair
+        const int r = 32 * q + lane;     // token row of the tile = tensor-memory lane
+        for (int cb = 0; cb < ncb; ++cb) {
+            const int s = cb % STAGES, round = cb / STAGES;
+            mbar_wait_bounded<true>(&ctrl->full[s], round & 1, &ctrl->abort, status);
+            unsigned char* st = sm + s * stage_bytes(D);
+            const unsigned char* xs = st + 4 * DY_BYTES;
+#pragma unroll 2
+            for (int pc = 0; pc < 8; ++pc) {  // 16-byte pieces of the 64-channel rows
+                float xv[8], pv[8];
+                unpack8(*reinterpret_cast<const uint4*>(xs + (r + 1) * 128 + ((pc ^ ((r + 1) & 7)) << 4)), xv);
+                unpack8(*reinterpret_cast<const uint4*>(xs + r * 128 + ((pc ^ (r & 7)) << 4)), pv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) pv[j] -= xv[j];
+#pragma unroll
+                for (int k = 2 * g; k < 2 * g + 2; ++k) {
+                    uint4* cell = reinterpret_cast<uint4*>(st + k * DY_BYTES + r * 128 + ((pc ^ (r & 7)) << 4));
+                    float dv[8];
+                    unpack8(*cell, dv);
+                    uint4 o;
+                    o.x = pack2(dv[0] * pv[0], dv[1] * pv[1]); o.y = pack2(dv[2] * pv[2], dv[3] * pv[3]);
+                    o.z = pack2(dv[4] * pv[4], dv[5] * pv[5]); o.w = pack2(dv[6] * pv[6], dv[7] * pv[7]);
+                    *cell = o;
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what these threads wrote
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ctrl->ready[s])) : "memory");
+        }
+        // epilogue: dpre = dm (1 - m^2), staged as [128 rows][64 columns] bf16 blocks (swizzled) in stage 0, stored by bulk tensor stores
+        mbar_wait_bounded<true>(&ctrl->accum, 0, &ctrl->abort, status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const bool ok = !ctrl->abort;
+        const bool live = t0 + r < T;
+        const __nv_bfloat16* mrow = m + ((long long)bi * T + (live ? t0 + r : 0)) * N4;
+        // columns of this warp: with 4D = 128 the stream pair's 64; with 4D = 64 the first group takes all, the second none
+        const int col0 = N4 == 128 ? 64 * g : 0, col1 = N4 == 128 ? 64 * g + 64 : (g == 0 ? N4 : 0);
+#pragma unroll 1
+        for (int cbk = col0; cbk < col1; cbk += 16) {
+            uint32_t v[16];
+            tmem_ld16(tmem + ((uint32_t)(32 * q) << 16) + cbk, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float mv[8];
+                unpack8(live ? *reinterpret_cast<const uint4*>(mrow + cbk + 8 * h) : make_uint4(0, 0, 0, 0), mv);
+                float o[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = __uint_as_float(v[8 * h + j]) * (1.f - mv[j] * mv[j]);
+                uint4 pk;
+                pk.x = pack2(o[0], o[1]); pk.y = pack2(o[2], o[3]); pk.z = pack2(o[4], o[5]); pk.w = pack2(o[6], o[7]);
+                const int piece = ((cbk & 63) >> 3) + h;
+                *reinterpret_cast<uint4*>(sm + (cbk >> 6) * (BM * 128) + r * 128 + ((piece ^ (r & 7)) << 4)) = pk;
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (ok && lane == 0 && t0 + 32 * q < T && col1 > col0) {
+            const int h2 = col0 >> 6;
+            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+                         ::"l"(&mapP), "r"(64 * h2), "r"(t0 + 32 * q), "r"(bi), "r"(smem_u32(sm + h2 * (BM * 128) + 32 * q * 128)) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        }
+        __syncwarp();
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(128) : "memory");
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -596,7 +762,42 @@ template <int D> static int launch_lerp(const CUtensorMap& mM, const CUtensorMap
 
 }  // namespace dtc
 
-size_t ddlerp_bwd_tc_workspace_bytes(long long C, int D) { return (size_t)(4 * D) * (size_t)C * 4; }
+// scratch of the backward: dW2 (fp32 [4D, C]) and R^T (bf16 [4D, C])
+size_t ddlerp_bwd_tc_workspace_bytes(long long C, int D) { return (size_t)(4 * D) * (size_t)C * 6; }
+
+// dpre (bf16 [rows, 4D]) from dy, x, R and m; ranks 16 and 32
+template <int D> static int launch_dpre_tc_t(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream) {
+    using namespace dtc;
+    const long long B = p.rows / p.T, C = p.C, T = p.T;
+    const int n4 = 4 * D;
+    __nv_bfloat16* Rt = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(ws) + (size_t)n4 * C * 4);
+    {
+        const long long n = (long long)n4 * C;
+        ddlerp_prep_rt_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)p.R, Rt, (int)C, D);
+        if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
+    }
+    if (B > 65535) return kTooLarge;
+    alignas(64) DyMaps mY;
+    alignas(64) CUtensorMap mX, mRt, mP;
+    const long long dx[3] = {C, T, B}, sx[2] = {C, T * C}, dr[2] = {C, n4}, sr[1] = {C}, dp[3] = {n4, T, B}, sp[2] = {n4, T * n4};
+    const int by[3] = {64, BM, 1}, bx[3] = {64, BM + 1, 1}, br[2] = {64, n4}, bp[3] = {64, 32, 1};
+    for (int k = 0; k < 4; ++k)
+        if (!encode(&mY.m[k], p.dy[k], 3, dx, sx, by)) return kLaunchFailed;
+    if (!(encode(&mX, p.x, 3, dx, sx, bx) && encode(&mRt, Rt, 2, dr, sr, br) && encode(&mP, p.dpre, 3, dp, sp, bp))) return kLaunchFailed;
+    auto kern = ddlerp_dpre_tc_kernel<D>;
+    constexpr int smem = g4::STAGES * g4::stage_bytes(D) + (int)sizeof(g4::Ctrl) + 1024;
+    static_assert(smem <= 232448, "two stages must fit one CTA");
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kLaunchFailed;
+    dim3 grid((unsigned)((T + BM - 1) / BM), (unsigned)B);
+    kern<<<grid, g4::THREADS, smem, stream>>>(mY, mX, mRt, mP, (const __nv_bfloat16*)p.m, (int)C, (int)T, status);
+    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+// returns kBadShape for ranks this form does not cover (the caller then runs the mma.sync kernel)
+int launch_ddlerp_dpre_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream) {
+    if (p.D == 16) return launch_dpre_tc_t<16>(p, ws, status, stream);
+    if (p.D == 32) return launch_dpre_tc_t<32>(p, ws, status, stream);
+    return kBadShape;
+}
 
 // dL (fp32 [4D, C], zero on entry) from dpre and x; ws: ddlerp_bwd_tc_workspace_bytes(C, D) bytes
 int launch_ddlerp_dL_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream) {
