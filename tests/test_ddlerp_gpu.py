@@ -141,10 +141,10 @@ def test_forward_kernels_agree_through_c_abi():
 
 
 def test_backward_entry_points_agree_through_c_abi():
-    """wkv7_ddlerp_bwd (dL by the mma.sync kernel) and wkv7_ddlerp_bwd_tc (dL on tcgen05 as dpre^T [x_t | x_{t-1}], then
-    combined with alpha) on the same inputs: everything but dL comes from the same kernels and is bit-identical up to
-    the order of the fp32 atomics (relative L2 <= 1e-5); dL agrees to the bf16 rounding of u (<= 6e-3).  T = 200 is not a
-    multiple of the 128-token tiles, and B = 3 checks that x_{t-1} of a sequence's first token reads as zero."""
+    """wkv7_ddlerp_bwd (mma.sync kernels) and wkv7_ddlerp_bwd_tc (tcgen05 kernels) on the same inputs.  The two form the same
+    sums from differently rounded terms (there u and fp32 dz, here x, the shifted weights and bf16 dz), so every output
+    agrees to bf16 rounding: relative L2 <= 6e-3.  T = 200 is not a multiple of the 128-token tiles, and B = 3 checks that
+    x_{t-1} of a sequence's first token reads as zero and that the token after a sequence's last contributes nothing."""
     from wind_rwkv.rwkv7 import _lib
     lib = _lib.lib()
     B, T, C, D = 3, 200, 256, 32
@@ -171,6 +171,5 @@ def test_backward_entry_points_agree_through_c_abi():
         th.cuda.synchronize()
         assert _lib.device_status() == 0
         res.append([t.float().cpu() for t in (dx, dal, dR, dbe, dL)])
-    for a, b in zip(res[0][:4], res[1][:4]):
-        assert rel_l2(b, a.numpy()) <= 1e-5
-    assert rel_l2(res[1][4], res[0][4].numpy()) <= 6e-3
+    for name, a, b in zip(['dx', 'dalpha', 'dR', 'dbeta', 'dL'], res[0], res[1]):
+        assert rel_l2(b, a.numpy()) <= 6e-3, name

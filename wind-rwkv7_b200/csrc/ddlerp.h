@@ -30,7 +30,8 @@ int launch_ddlerp_bwd(const DdlerpBwdParams& p, cudaStream_t stream);
 // The backward with dL formed on the tensor cores (ddlerp_tc.cu); `ws`: ddlerp_bwd_tc_workspace_bytes(C, D) bytes of scratch
 size_t ddlerp_bwd_tc_workspace_bytes(long long C, int D);
 int launch_ddlerp_bwd_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream);
-int launch_ddlerp_dL_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream);
+int launch_ddlerp_dL_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream, bool with_dalpha);
+int launch_ddlerp_main_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream);  // kBadShape: rank not covered
 int launch_ddlerp_dpre_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream);  // kBadShape: rank not covered
 
 }  // namespace wkv7

@@ -444,7 +444,9 @@ template <int D> static int launch_ddlerp_bwd_t(const DdlerpBwdParams& p, cudaSt
         kern<<<(unsigned)((p.rows + 31) / 32), 256, smem, stream>>>(p);
         if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
     }
-    {
+    int main_rc = ws ? launch_ddlerp_main_tc(p, ws, status, stream) : kBadShape;  // tcgen05 form where it covers the rank
+    if (main_rc != kOk && main_rc != kBadShape) return main_rc;
+    if (main_rc == kBadShape) {
         auto kern = ddlerp_bwd_main_kernel<D>;
         const int smem = (int)sizeof(MainSmem<D>);
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kLaunchFailed;
@@ -470,7 +472,7 @@ template <int D> static int launch_ddlerp_bwd_t(const DdlerpBwdParams& p, cudaSt
         if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
     }
     if (ws) {  // dL on the tensor cores
-        const int rc = launch_ddlerp_dL_tc(p, ws, status, stream);
+        const int rc = launch_ddlerp_dL_tc(p, ws, status, stream, main_rc == kOk);  // the tcgen05 main kernel leaves dalpha to this step
         if (rc != kOk) return rc;
     } else {
         auto kern = ddlerp_bwd_dL_kernel<D>;

@@ -543,12 +543,23 @@ __global__ void __launch_bounds__(g3::THREADS) ddlerp_dw12_kernel(const __grid_c
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
 }
 
-// dL = dW1 (1 - alpha) + dW2 alpha, in place (dL holds dW1 on entry)
-__global__ void ddlerp_dl_finish_kernel(float* __restrict__ dL, const float* __restrict__ dW2, const __nv_bfloat16* __restrict__ alpha, int C, long long n) {
-    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const float a = __bfloat162float(alpha[i % C]);
-    dL[i] = dL[i] * (1.f - a) + dW2[i] * a;
+// dL = dW1 (1 - alpha) + dW2 alpha, in place (dL holds dW1 on entry); a thread takes 8 rows of one channel.  With dalpha !=
+// nullptr (zero on entry) also dalpha[c] += sum_n L[n, c] (dW2 - dW1)[n, c]  ( = sum_t (dpre L)[t, c] (x_{t-1} - x_t)[c] ).
+__global__ void ddlerp_dl_finish_kernel(float* __restrict__ dL, const float* __restrict__ dW2, const __nv_bfloat16* __restrict__ alpha,
+                                        const __nv_bfloat16* __restrict__ L, float* __restrict__ dalpha, int C, int n4) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, n0 = blockIdx.y * 8;
+    if (c >= C) return;
+    const float a = __bfloat162float(alpha[c]);
+    float acc = 0.f;
+#pragma unroll
+    for (int n = n0; n < n0 + 8; ++n) {
+        if (n >= n4) break;
+        const long long i = (long long)n * C + c;
+        const float w1 = dL[i], w2 = dW2[i];
+        dL[i] = w1 * (1.f - a) + w2 * a;
+        acc += __bfloat162float(L[i]) * (w2 - w1);
+    }
+    if (dalpha) atomicAdd(dalpha + c, acc);
 }
 
 // ------------------------------------------------------------------------------------------------------------------------
@@ -717,6 +728,383 @@ __global__ void __launch_bounds__(g4::THREADS, 1) ddlerp_dpre_tc_kernel(const __
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(128) : "memory");
 }
 
+// ------------------------------------------------------------------------------------------------------------------------
+// The rest of the backward on the tensor cores, per (128 tokens of one sequence) x (64 channels):
+//     du  = dpre L[:, cb]                 z_k = m_k R_k[cb]^T                      (products 1: contraction over 4D / D)
+//     X   = du alpha + sum_k dy_k (z_k + beta_k)        Dd = du + sum_k dy_k        dz_k = dy_k (x_{t-1} - x_t)
+//     dx_t = Dd_t - X_t + X_{t+1}
+//     dR_k[cb] += dz_k^T m_k              dbeta_k[cb] += dz_k^T 1                  (products 2: contraction over tokens)
+// Persistent: one CTA per SM walks a contiguous range of the unit list (channel blocks slowest), so the token-contracted
+// accumulators stay in tensor memory until the channel block changes.  Per unit: bulk tensor loads of the dpre, m, dy_k and
+// x tiles (and, when the channel block changes, of its blocks of L^T and R'); products 1 into tensor-memory columns 0..319;
+// eight epilogue warps (row quarter x channel half) read them one token row per thread, form X, Dd, write dz_k IN PLACE into
+// the dy tiles (which then are, as they lie, the MN-major A operands of products 2) and dx into a staging tile for a bulk
+// tensor store; X_{t+1} comes from the next lane, across warps through shared memory, and for the tile's last row from a
+// halo row computed on the CUDA cores (one row of du and z_k: 16K multiply-adds), so units are independent of each other.
+namespace g5 {
+constexpr int THREADS = 320;  // warps 0-7: epilogue (row quarter w % 4, channel half w / 4), warp 8: TMA, warp 9: MMA
+constexpr int TILE = BM * 128;                               // a [128 rows][64 columns] bf16 block
+constexpr int X_BYTES = ((BM + 1) * 128 + 1023) / 1024 * 1024;
+struct Ctrl {
+    uint64_t full, wfull, acc1, dz_ready, unit_free, flushed, drain;
+    uint32_t tmem_base;
+    volatile int abort, zero;
+    alignas(16) float alpha[64], beta[4][64], halo[64], edge[4][64];
+};
+// shared memory: dpre tile, m tile (KB blocks each), four dy tiles, x tile, L^T block, R' block (KB blocks of 64 rows each),
+// a tile of ones, the dx staging tile, Ctrl
+__host__ __device__ constexpr int kb_of(int D) { return 4 * D / 64; }
+__host__ __device__ constexpr int off_m(int D) { return kb_of(D) * TILE; }
+__host__ __device__ constexpr int off_dy(int D) { return 2 * kb_of(D) * TILE; }
+__host__ __device__ constexpr int off_x(int D) { return off_dy(D) + 4 * TILE; }
+__host__ __device__ constexpr int off_lt(int D) { return off_x(D) + X_BYTES; }
+__host__ __device__ constexpr int off_rp(int D) { return off_lt(D) + kb_of(D) * 64 * 128; }
+__host__ __device__ constexpr int off_ones(int D) { return off_rp(D) + kb_of(D) * 64 * 128; }
+__host__ __device__ constexpr int off_dx(int D) { return off_ones(D) + TILE; }
+__host__ __device__ constexpr int off_ctrl(int D) { return off_dx(D) + TILE; }
+// tensor-memory columns: du 0..63, z_k 64 + 64 k, dR_k 320 + D k, dbeta_k 320 + 4D + 8 k
+constexpr int C_DU = 0, C_Z = 64, C_DR = 320;
+// MN-major operand out of [token][64 columns] tiles with the 128-byte swizzle (see g3::desc_mn); M = 64
+__device__ __forceinline__ uint64_t desc_mn(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3fff) | ((uint64_t)(16384 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__host__ __device__ constexpr uint32_t idesc_mn64(int n) {  // fp32 accumulate, bf16 operands, both MN-major, M = 64
+    return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(n >> 3) << 17) | (4u << 24);
+}
+}  // namespace g5
+
+// L^T as [C, 4D] and R' as [C, 4D] (column k D + d = R[k][c][d])
+__global__ void ddlerp_prep_lt_rp_kernel(const __nv_bfloat16* __restrict__ L, const __nv_bfloat16* __restrict__ R, __nv_bfloat16* __restrict__ Lt,
+                                         __nv_bfloat16* __restrict__ Rp, int C, int D) {
+    const int n4 = 4 * D;
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i >= (long long)C * n4) return;
+    const int c = (int)(i / n4), n = (int)(i % n4);
+    Lt[i] = L[(long long)n * C + c];
+    Rp[i] = R[((long long)(n / D) * C + c) * D + (n % D)];
+}
+
+struct MainMaps { CUtensorMap dy[4], x, dpre, m, lt, rp, dx; };
+// maps: dy_k, x as (channel, time, batch), boxes 64 x 128 x 1 and 64 x 129 x 1; dpre, m as (column, time, batch), box 64 x 128 x 1;
+// lt, rp as (column, channel), box 64 x 64; dx as (channel, time, batch), box 64 x 32 x 1
+template <int D>
+__global__ void __launch_bounds__(g5::THREADS, 1) ddlerp_main_tc_kernel(const __grid_constant__ MainMaps maps, const __nv_bfloat16* __restrict__ dyp0,
+                                                                       const __nv_bfloat16* __restrict__ dyp1, const __nv_bfloat16* __restrict__ dyp2,
+                                                                       const __nv_bfloat16* __restrict__ dyp3, const __nv_bfloat16* __restrict__ dpre,
+                                                                       const __nv_bfloat16* __restrict__ mten, const __nv_bfloat16* __restrict__ L,
+                                                                       const __nv_bfloat16* __restrict__ R, const __nv_bfloat16* __restrict__ alpha,
+                                                                       const __nv_bfloat16* __restrict__ beta, float* __restrict__ dR,
+                                                                       float* __restrict__ dbeta, int C, int T, int tiles_per_seq, int tiles, int units,
+                                                                       int* status) {
+    using namespace g5;
+    constexpr int KB = 4 * D / 64, N4 = 4 * D;
+    constexpr int C_DB = C_DR + N4;
+    static_assert(C_DB + 32 <= 512, "tensor-memory columns");
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* sm = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+    Ctrl* ctrl = reinterpret_cast<Ctrl*>(sm + off_ctrl(D));
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+    const int u_lo = (int)((long long)units * blockIdx.x / gridDim.x), nmine = (int)((long long)units * (blockIdx.x + 1) / gridDim.x) - u_lo;
+    // unit u: channel block u / tiles, token tile u % tiles (tile -> sequence tile / tiles_per_seq, first token (tile % tiles_per_seq) * 128)
+
+    if (tid == 0) {
+        mbar_init(&ctrl->full, 1); mbar_init(&ctrl->wfull, 1); mbar_init(&ctrl->acc1, 1); mbar_init(&ctrl->dz_ready, 8);
+        mbar_init(&ctrl->unit_free, 1); mbar_init(&ctrl->flushed, 8); mbar_init(&ctrl->drain, 1);
+        ctrl->abort = 0; ctrl->zero = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = tid; i < TILE / 4; i += THREADS) reinterpret_cast<uint32_t*>(sm + off_ones(D))[i] = 0x3f803f80u;  // bf16 1.0 pairs
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctrl->tmem_base)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = ctrl->tmem_base;
+    const uint32_t sb = smem_u32(sm);
+
+    if (warp == 8) {
+        if (elect_one()) {
+            int cb_prev = -1, nw = 0;
+            for (int n = 0; n < nmine; ++n) {
+                const int u = u_lo + n, cb = u / tiles, tile = u % tiles, t0 = (tile % tiles_per_seq) * BM, bi = tile / tiles_per_seq;
+                if (n > 0) mbar_wait_bounded<true>(&ctrl->unit_free, (n - 1) & 1, &ctrl->abort, status);  // products 2 of the previous unit have read the tiles
+                if (cb != cb_prev) {
+                    // the previous channel block's accumulators must have been flushed before products 2 of this unit overwrite
+                    // them; the weights may be replaced as soon as the previous unit's products are complete (unit_free)
+                    cb_prev = cb; ++nw;
+                    mbar_expect(&ctrl->wfull, (uint32_t)(2 * KB * 64 * 128));
+#pragma unroll
+                    for (int kb = 0; kb < KB; ++kb) {
+                        tma_load_2d(sb + off_lt(D) + kb * 64 * 128, &maps.lt, &ctrl->wfull, kb * 64, cb * 64);
+                        tma_load_2d(sb + off_rp(D) + kb * 64 * 128, &maps.rp, &ctrl->wfull, kb * 64, cb * 64);
+                    }
+                }
+                mbar_expect(&ctrl->full, (uint32_t)(2 * KB * TILE + 4 * TILE + (BM + 1) * 128));
+#pragma unroll
+                for (int kb = 0; kb < KB; ++kb) {
+                    tma_load_3d(sb + kb * TILE, &maps.dpre, &ctrl->full, kb * 64, t0, bi);
+                    tma_load_3d(sb + off_m(D) + kb * TILE, &maps.m, &ctrl->full, kb * 64, t0, bi);
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) tma_load_3d(sb + off_dy(D) + k * TILE, &maps.dy[k], &ctrl->full, cb * 64, t0, bi);
+                tma_load_3d(sb + off_x(D), &maps.x, &ctrl->full, cb * 64, t0 - 1, bi);
+            }
+            (void)nw;
+        }
+        __syncwarp();
+    } else if (warp == 9) {
+        if (elect_one()) {
+            int cb_prev = -1, nw = 0, nflush = 0;
+            for (int n = 0; n < nmine; ++n) {
+                const int u = u_lo + n, cb = u / tiles;
+                const bool newcb = cb != cb_prev;
+                if (newcb) {
+                    cb_prev = cb;
+                    mbar_wait_bounded<false>(&ctrl->wfull, nw & 1, &ctrl->abort, status);
+                    ++nw;
+                }
+                mbar_wait_bounded<false>(&ctrl->full, n & 1, &ctrl->abort, status);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // products 1: du = dpre L^T-block^T (K = 4D), z_k = m_k R'_k^T (K = D)
+#pragma unroll
+                for (int kb = 0; kb < KB; ++kb) {
+                    const uint64_t da = desc_sw128(sb + kb * TILE), db = desc_sw128(sb + off_lt(D) + kb * 64 * 128);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) mma_f16(tmem + C_DU, da + (uint64_t)(2 * ks), db + (uint64_t)(2 * ks), idesc(64), (kb > 0 || ks > 0) ? 1u : 0u);
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int blk = (k * D) / 64, off = ((k * D) % 64) * 2;
+                    const uint64_t da = desc_sw128(sb + off_m(D) + blk * TILE) + (uint64_t)(off >> 4);
+                    const uint64_t db = desc_sw128(sb + off_rp(D) + blk * 64 * 128) + (uint64_t)(off >> 4);
+#pragma unroll
+                    for (int ks = 0; ks < D / 16; ++ks) mma_f16(tmem + C_Z + 64 * k, da + (uint64_t)(2 * ks), db + (uint64_t)(2 * ks), idesc(64), ks > 0 ? 1u : 0u);
+                }
+                tc_commit(&ctrl->acc1);
+                // products 2, once the epilogue has turned dy into dz: dR_k += dz_k^T m_k, dbeta_k += dz_k^T 1 (contraction over the 128 tokens)
+                mbar_wait_bounded<false>(&ctrl->dz_ready, n & 1, &ctrl->abort, status);
+                if (newcb && n > 0) {  // the accumulators still hold the previous channel block until the epilogue warps have flushed them
+                    mbar_wait_bounded<false>(&ctrl->flushed, nflush & 1, &ctrl->abort, status);
+                    ++nflush;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int blk = (k * D) / 64, off = ((k * D) % 64) * 2;
+                    const uint64_t da = desc_mn(sb + off_dy(D) + k * TILE);
+                    const uint64_t dbm = desc_mn(sb + off_m(D) + blk * TILE) + (uint64_t)(off >> 4), dbo = desc_mn(sb + off_ones(D));
+#pragma unroll
+                    for (int ks = 0; ks < BM / 16; ++ks) {
+                        const uint32_t acc = (!newcb || ks > 0) ? 1u : 0u;
+                        mma_f16(tmem + C_DR + D * k, da + (uint64_t)(ks * 128), dbm + (uint64_t)(ks * 128), idesc_mn64(D), acc);
+                        mma_f16(tmem + C_DB + 8 * k, da + (uint64_t)(ks * 128), dbo + (uint64_t)(ks * 128), idesc_mn64(8), acc);
+                    }
+                }
+                tc_commit(&ctrl->unit_free);
+            }
+            if (ctrl->abort) drain_products(&ctrl->drain, &ctrl->zero, status);
+        }
+        __syncwarp();
+    } else {
+        const int q = warp & 3, g = warp >> 2;   // row quarter (= tensor-memory lane quarter), channel half
+        const int r = 32 * q + lane, ch0 = 32 * g;
+        const int et = tid;                       // 0..255 among the epilogue warps
+        const __nv_bfloat16* dyp[4] = {dyp0, dyp1, dyp2, dyp3};
+        const uint32_t tlane = tmem + ((uint32_t)(32 * q) << 16);
+        // token-contracted accumulators of channel block cbf -> global memory (vector reductions); the M = 64 products keep
+        // channel c in tensor-memory lane 32 (c / 16) + c % 16
+        auto flush = [&](int cbf) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (g == 0) {
+                const int c = cbf * 64 + 16 * q + (lane & 15);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+#pragma unroll
+                    for (int d0 = 0; d0 < D; d0 += 16) {
+                        uint32_t v[16];
+                        tmem_ld16(tlane + C_DR + D * k + d0, v);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (lane < 16) {
+                            float* o = dR + ((long long)k * C + c) * D + d0;
+#pragma unroll
+                            for (int jj = 0; jj < 4; ++jj)
+                                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + 4 * jj), "f"(__uint_as_float(v[4 * jj])), "f"(__uint_as_float(v[4 * jj + 1])),
+                                             "f"(__uint_as_float(v[4 * jj + 2])), "f"(__uint_as_float(v[4 * jj + 3])) : "memory");
+                        }
+                    }
+                uint32_t v0[16], v1[16];   // dbeta_k in column C_DB + 8 k
+                tmem_ld16(tlane + C_DB, v0);
+                tmem_ld16(tlane + C_DB + 16, v1);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (lane < 16) {
+                    atomicAdd(dbeta + c, __uint_as_float(v0[0]));
+                    atomicAdd(dbeta + (long long)C + c, __uint_as_float(v0[8]));
+                    atomicAdd(dbeta + 2LL * C + c, __uint_as_float(v1[0]));
+                    atomicAdd(dbeta + 3LL * C + c, __uint_as_float(v1[8]));
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ctrl->flushed)) : "memory");
+        };
+        if (et < 64) ctrl->halo[et] = 0.f;
+        int cb_prev = -1;
+        for (int n = 0; n < nmine; ++n) {
+            const int u = u_lo + n, cb = u / tiles, tile = u % tiles, t0 = (tile % tiles_per_seq) * BM, bi = tile / tiles_per_seq;
+            if (cb != cb_prev) {
+                if (n > 0) {  // the previous channel block's sums are complete once the previous unit's products 2 are
+                    mbar_wait_bounded<true>(&ctrl->unit_free, (n - 1) & 1, &ctrl->abort, status);
+                    flush(cb_prev);
+                }
+                cb_prev = cb;
+                asm volatile("bar.sync 1, 256;" ::: "memory");  // every epilogue warp has finished the previous unit
+                if (et < 64) ctrl->alpha[et] = __bfloat162float(alpha[cb * 64 + et]);
+                ctrl->beta[et >> 6][et & 63] = __bfloat162float(beta[(long long)(et >> 6) * C + cb * 64 + (et & 63)]);
+                asm volatile("bar.sync 1, 256;" ::: "memory");  // alpha and beta of this channel block are in place
+            }
+            // ---- halo: X of the token after this tile (zero past the sequence's end), accumulated with shared-memory atomics.
+            // Thread = (8 channels, one of 32 slices of the contraction): 4 rows of L and, for stream slice / 8, 4 ranks of R.
+            if (t0 + BM < T) {
+                const long long hrow = (long long)bi * T + t0 + BM;
+                const int cg8 = (et & 7) * 8, sl = et >> 3;   // lanes of a warp: 8 channel groups x 4 slices
+                float acc[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+                for (int i4 = 0; i4 < N4 / 32; ++i4) {   // du part: rows sl * (4D / 32) ... of L
+                    const int nn = sl * (N4 / 32) + i4;
+                    float lv[8];
+                    unpack8(*reinterpret_cast<const uint4*>(L + (long long)nn * C + cb * 64 + cg8), lv);
+                    const float dp = __bfloat162float(dpre[hrow * N4 + nn]);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] += dp * lv[j] * ctrl->alpha[cg8 + j];
+                }
+                {   // z part of stream k: ranks (sl % 8) * (D / 8) ...
+                    const int k = sl >> 3, d0 = (sl & 7) * (D / 8);
+                    float zz[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) zz[j] = 0.f;
+#pragma unroll
+                    for (int dd = 0; dd < D / 8; ++dd) {
+                        const float mv = __bfloat162float(mten[hrow * N4 + k * D + d0 + dd]);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) zz[j] += mv * __bfloat162float(R[((long long)k * C + cb * 64 + cg8 + j) * D + d0 + dd]);
+                    }
+                    float dv[8];
+                    unpack8(*reinterpret_cast<const uint4*>(dyp[k] + hrow * C + cb * 64 + cg8), dv);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] += dv[j] * (zz[j] + ((sl & 7) == 0 ? ctrl->beta[k][cg8 + j] : 0.f));
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) atomicAdd(&ctrl->halo[cg8 + j], acc[j]);
+            }
+            // ---- X, Dd and dz for this thread's row and 32 channels ---------------------------------------------------
+            mbar_wait_bounded<true>(&ctrl->full, n & 1, &ctrl->abort, status);
+            mbar_wait_bounded<true>(&ctrl->acc1, n & 1, &ctrl->abort, status);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const bool ok = !ctrl->abort;
+            float X[32], Dd[32];
+            const unsigned char* xs = sm + off_x(D);
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                uint32_t du[16], zk[4][16];
+                tmem_ld16(tlane + C_DU + ch0 + 16 * cc, du);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) tmem_ld16(tlane + C_Z + 64 * k + ch0 + 16 * cc, zk[k]);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int pc = (ch0 >> 3) + 2 * cc + h, cbase = ch0 + 16 * cc + 8 * h;   // 16-byte piece of the 64-channel rows
+                    float xv[8], pv[8];
+                    unpack8(*reinterpret_cast<const uint4*>(xs + (r + 1) * 128 + ((pc ^ ((r + 1) & 7)) << 4)), xv);
+                    unpack8(*reinterpret_cast<const uint4*>(xs + r * 128 + ((pc ^ (r & 7)) << 4)), pv);
+                    float xa[8], da[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        pv[j] -= xv[j];
+                        const float d = __uint_as_float(du[8 * h + j]);
+                        xa[j] = d * ctrl->alpha[cbase + j];
+                        da[j] = d;
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        uint4* cell = reinterpret_cast<uint4*>(sm + off_dy(D) + k * TILE + r * 128 + ((pc ^ (r & 7)) << 4));
+                        float dv[8];
+                        unpack8(*cell, dv);
+                        uint4 o;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            xa[j] += dv[j] * (__uint_as_float(zk[k][8 * h + j]) + ctrl->beta[k][cbase + j]);
+                            da[j] += dv[j];
+                        }
+                        o.x = pack2(dv[0] * pv[0], dv[1] * pv[1]); o.y = pack2(dv[2] * pv[2], dv[3] * pv[3]);
+                        o.z = pack2(dv[4] * pv[4], dv[5] * pv[5]); o.w = pack2(dv[6] * pv[6], dv[7] * pv[7]);
+                        *cell = o;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) { X[16 * cc + 8 * h + j] = xa[j]; Dd[16 * cc + 8 * h + j] = da[j]; }
+                }
+            }
+            // dz is in place: products 2 may start.  X of the first row of every quarter goes to shared memory for the row above.
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            if (lane == 0) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) ctrl->edge[q][ch0 + j] = X[j];
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous unit's dx store has read the staging tile
+            }
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ctrl->dz_ready)) : "memory");
+            asm volatile("bar.sync 2, 256;" ::: "memory");   // edges and the halo sums are complete
+            // ---- dx_t = Dd_t - X_t + X_{t+1} ------------------------------------------------------------------------------
+            unsigned char* dxs = sm + off_dx(D);
+#pragma unroll
+            for (int pcl = 0; pcl < 4; ++pcl) {
+                float o[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int cj = 8 * pcl + j;
+                    float xn = __shfl_down_sync(0xffffffffu, X[cj], 1);
+                    if (lane == 31) xn = q < 3 ? ctrl->edge[q + 1][ch0 + cj] : ctrl->halo[ch0 + cj];
+                    o[j] = Dd[cj] - X[cj] + xn;
+                }
+                uint4 pk;
+                pk.x = pack2(o[0], o[1]); pk.y = pack2(o[2], o[3]); pk.z = pack2(o[4], o[5]); pk.w = pack2(o[6], o[7]);
+                const int pc = (ch0 >> 3) + pcl;
+                *reinterpret_cast<uint4*>(dxs + r * 128 + ((pc ^ (r & 7)) << 4)) = pk;
+            }
+            if (q == 3 && lane == 31) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) ctrl->halo[ch0 + j] = 0.f;   // read above; the next unit's sums start after the barrier below
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("bar.sync 3, 256;" ::: "memory");   // staging tile complete; edge and halo values have been read
+            if (g == 0 && lane == 0) {
+                if (ok && t0 + 32 * q < T)
+                    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+                                 ::"l"(&maps.dx), "r"(cb * 64), "r"(t0 + 32 * q), "r"(bi), "r"(smem_u32(dxs + 32 * q * 128)) : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            __syncwarp();
+        }
+        if (nmine > 0) {
+            mbar_wait_bounded<true>(&ctrl->unit_free, (nmine - 1) & 1, &ctrl->abort, status);
+            flush(cb_prev);
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        __syncwarp();
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+}
+
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -762,8 +1150,53 @@ template <int D> static int launch_lerp(const CUtensorMap& mM, const CUtensorMap
 
 }  // namespace dtc
 
-// scratch of the backward: dW2 (fp32 [4D, C]) and R^T (bf16 [4D, C])
-size_t ddlerp_bwd_tc_workspace_bytes(long long C, int D) { return (size_t)(4 * D) * (size_t)C * 6; }
+// scratch of the backward: dW2 (fp32 [4D, C]), R^T (bf16 [4D, C]), L^T and R' (bf16 [C, 4D] each)
+size_t ddlerp_bwd_tc_workspace_bytes(long long C, int D) { return (size_t)(4 * D) * (size_t)C * 10; }
+
+// dx, dR, dbeta (dR, dbeta zero on entry) on the tensor cores; ranks 16 and 32.  dalpha is NOT formed here (see the dL step).
+template <int D> static int launch_main_tc_t(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream) {
+    using namespace dtc;
+    const long long B = p.rows / p.T, C = p.C, T = p.T;
+    const int n4 = 4 * D;
+    __nv_bfloat16* Lt = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(ws) + (size_t)n4 * C * 6);
+    __nv_bfloat16* Rp = Lt + (size_t)n4 * C;
+    {
+        const long long n = (long long)n4 * C;
+        ddlerp_prep_lt_rp_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)p.L, (const __nv_bfloat16*)p.R, Lt, Rp, (int)C, D);
+        if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
+    }
+    alignas(64) MainMaps mm;
+    const long long dx[3] = {C, T, B}, sx[2] = {C, T * C}, dn[3] = {n4, T, B}, sn[2] = {n4, T * n4}, dw[2] = {n4, C}, sw[1] = {n4};
+    const int b128[3] = {64, BM, 1}, b129[3] = {64, BM + 1, 1}, bw[2] = {64, 64}, b32[3] = {64, 32, 1};
+    for (int k = 0; k < 4; ++k)
+        if (!encode(&mm.dy[k], p.dy[k], 3, dx, sx, b128)) return kLaunchFailed;
+    if (!(encode(&mm.x, p.x, 3, dx, sx, b129) && encode(&mm.dpre, p.dpre, 3, dn, sn, b128) && encode(&mm.m, p.m, 3, dn, sn, b128) &&
+          encode(&mm.lt, Lt, 2, dw, sw, bw) && encode(&mm.rp, Rp, 2, dw, sw, bw) && encode(&mm.dx, p.dx, 3, dx, sx, b32)))
+        return kLaunchFailed;
+    auto kern = ddlerp_main_tc_kernel<D>;
+    constexpr int smem = g5::off_ctrl(D) + (int)sizeof(g5::Ctrl) + 1024;
+    static_assert(smem <= 232448, "the unit's tiles must fit one CTA");
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kLaunchFailed;
+    static const int sms = [] {
+        int dev = 0, n = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        return n;
+    }();
+    const long long tiles_per_seq = (T + BM - 1) / BM, tiles = tiles_per_seq * B, units = tiles * (C / 64);
+    if (units > 0x7fffffffLL) return kTooLarge;
+    const unsigned grid = (unsigned)(units < sms ? units : sms);
+    kern<<<grid, g5::THREADS, smem, stream>>>(mm, (const __nv_bfloat16*)p.dy[0], (const __nv_bfloat16*)p.dy[1], (const __nv_bfloat16*)p.dy[2],
+                                             (const __nv_bfloat16*)p.dy[3], (const __nv_bfloat16*)p.dpre, (const __nv_bfloat16*)p.m,
+                                             (const __nv_bfloat16*)p.L, (const __nv_bfloat16*)p.R, (const __nv_bfloat16*)p.alpha,
+                                             (const __nv_bfloat16*)p.beta, p.dR, p.dbeta, (int)C, (int)T, (int)tiles_per_seq, (int)tiles, (int)units, status);
+    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+// returns kBadShape for ranks this form does not cover (the caller then runs the mma.sync kernel)
+int launch_ddlerp_main_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream) {
+    if (p.D == 16) return launch_main_tc_t<16>(p, ws, status, stream);
+    if (p.D == 32) return launch_main_tc_t<32>(p, ws, status, stream);
+    return kBadShape;
+}
 
 // dpre (bf16 [rows, 4D]) from dy, x, R and m; ranks 16 and 32
 template <int D> static int launch_dpre_tc_t(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream) {
@@ -799,8 +1232,8 @@ int launch_ddlerp_dpre_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaS
     return kBadShape;
 }
 
-// dL (fp32 [4D, C], zero on entry) from dpre and x; ws: ddlerp_bwd_tc_workspace_bytes(C, D) bytes
-int launch_ddlerp_dL_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream) {
+// dL (fp32 [4D, C], zero on entry) from dpre and x, and with with_dalpha also dalpha (overwritten); ws: the backward's scratch
+int launch_ddlerp_dL_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream, bool with_dalpha) {
     using namespace dtc;
     const long long B = p.rows / p.T, C = p.C, T = p.T;
     const int n4 = 4 * p.D;
@@ -826,8 +1259,8 @@ int launch_ddlerp_dL_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStr
     dim3 grid((unsigned)col_tiles, (unsigned)splits, (unsigned)row_tiles);
     ddlerp_dw12_kernel<<<grid, g3::THREADS, smem, stream>>>(mD, mX, p.dL, dW2, (int)C, n4, (int)tiles_per_seq, (int)total, status);
     if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
-    const long long n = (long long)n4 * C;
-    ddlerp_dl_finish_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p.dL, dW2, (const __nv_bfloat16*)p.alpha, (int)C, n);
+    ddlerp_dl_finish_kernel<<<dim3((unsigned)((C + 127) / 128), (unsigned)((n4 + 7) / 8)), 128, 0, stream>>>(
+        p.dL, dW2, (const __nv_bfloat16*)p.alpha, (const __nv_bfloat16*)p.L, with_dalpha ? p.dalpha : nullptr, (int)C, n4);
     return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
 
