@@ -198,12 +198,13 @@ int wkv7_ddlerp_bwd(const void* x, const void* alpha, const void* L, const void*
                     int64_t B, int64_t T, int64_t C, int64_t D, void* stream);
 
 /*
- * ddlerp backward with dL = dpre^T u formed on the tcgen05 tensor cores (as dW12 = dpre^T [x_t | x_{t-1}] over bulk
- * tensor loads, then dL = dW1 (1 - alpha) + dW2 alpha); everything else as wkv7_ddlerp_bwd.  `workspace`:
- * wkv7_ddlerp_bwd_tc_workspace_bytes(C, D) bytes of device scratch, 16-byte aligned, overwritten.  At ranks 16 and 32 dpre
- * is formed on the tensor cores as well (dz = dy * xx in place in bulk-loaded tiles, K = C products with R^T).  dL differs from
- * wkv7_ddlerp_bwd's by bf16 rounding (there u is rounded to bf16, here x is used as it is).  May report
- * WKV7_ERR_DEVICE_TIMEOUT through the status word (bounded waits).
+ * ddlerp backward on the tcgen05 tensor cores with bulk tensor (TMA) loads and stores: same arguments, results and limits
+ * as wkv7_ddlerp_bwd, plus `workspace`: wkv7_ddlerp_bwd_tc_workspace_bytes(C, D) bytes of device scratch, 16-byte aligned,
+ * overwritten.  dL is formed as dW12 = dpre^T [x_t | x_{t-1}] and combined with alpha (dalpha is a by-product); at ranks 16
+ * and 32 dpre (dz = dy * xx formed in place in the loaded tiles, K = C products with R^T) and the main step (dx, dR, dbeta:
+ * token-contracted sums resident in tensor memory) run on the tensor cores as well, at rank 64 the mma.sync kernels of
+ * wkv7_ddlerp_bwd.  The two entry points sum differently rounded terms (there u and fp32 dz, here x, the shifted weights and
+ * bf16 dz): their outputs agree to bf16 rounding.  May report WKV7_ERR_DEVICE_TIMEOUT through the status word (bounded waits).
  */
 size_t wkv7_ddlerp_bwd_tc_workspace_bytes(int64_t C, int64_t D);
 int wkv7_ddlerp_bwd_tc(const void* x, const void* alpha, const void* L, const void* R, const void* beta, const void* m,
