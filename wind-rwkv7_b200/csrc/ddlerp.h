@@ -32,6 +32,7 @@ size_t ddlerp_bwd_tc_workspace_bytes(long long C, int D);
 int launch_ddlerp_bwd_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream);
 int launch_ddlerp_dL_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream, bool with_dalpha);
 int launch_ddlerp_main_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream);  // kBadShape: rank not covered
+int launch_ddlerp_prep_bwd(const DdlerpBwdParams& p, void* ws, cudaStream_t stream);  // rearranged weights for the two below
 int launch_ddlerp_dpre_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream);  // kBadShape: rank not covered
 
 }  // namespace wkv7

@@ -435,6 +435,7 @@ template <int D> static int launch_ddlerp_bwd_t(const DdlerpBwdParams& p, cudaSt
     if (cudaMemsetAsync(p.dbeta, 0, sizeof(float) * 4 * C, stream) != cudaSuccess) return kLaunchFailed;
     if (cudaMemsetAsync(p.dR, 0, sizeof(float) * 4 * C * D, stream) != cudaSuccess) return kLaunchFailed;
     if (cudaMemsetAsync(p.dL, 0, sizeof(float) * 4 * D * C, stream) != cudaSuccess) return kLaunchFailed;
+    if (ws && (D == 16 || D == 32) && launch_ddlerp_prep_bwd(p, ws, stream) != kOk) return kLaunchFailed;
     int dpre_rc = ws ? launch_ddlerp_dpre_tc(p, ws, status, stream) : kBadShape;  // tcgen05 form where it covers the rank
     if (dpre_rc != kOk && dpre_rc != kBadShape) return dpre_rc;
     if (dpre_rc == kBadShape) {

@@ -581,12 +581,22 @@ __host__ __device__ constexpr int rt_bytes(int D) { return 4 * D * 128; }       
 __host__ __device__ constexpr int stage_bytes(int D) { return 4 * DY_BYTES + X_BYTES + (rt_bytes(D) + 1023) / 1024 * 1024; }
 }  // namespace g4
 
-// R^T as [4D, C]: row k D + d = R[k][:, d]
-__global__ void ddlerp_prep_rt_kernel(const __nv_bfloat16* __restrict__ R, __nv_bfloat16* __restrict__ Rt, int C, int D) {
+// The backward's rearranged weights, one launch: R^T as [4D, C] (row k D + d = R[k][:, d]), L^T as [C, 4D], and R' as [C, 4D]
+// (column k D + d = R[k][c][d])
+__global__ void ddlerp_prep_bwd_kernel(const __nv_bfloat16* __restrict__ L, const __nv_bfloat16* __restrict__ R, __nv_bfloat16* __restrict__ Rt,
+                                       __nv_bfloat16* __restrict__ Lt, __nv_bfloat16* __restrict__ Rp, int C, int D) {
+    const int n4 = 4 * D;
     const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-    if (i >= (long long)4 * D * C) return;
-    const int n = (int)(i / C), c = (int)(i % C), k = n / D, d = n % D;
-    Rt[i] = R[((long long)k * C + c) * D + d];
+    if (i >= (long long)C * n4) return;
+    {
+        const int n = (int)(i / C), c = (int)(i % C);
+        Rt[i] = R[((long long)(n / D) * C + c) * D + (n % D)];
+    }
+    {
+        const int c = (int)(i / n4), n = (int)(i % n4);
+        Lt[i] = L[(long long)n * C + c];
+        Rp[i] = R[((long long)(n / D) * C + c) * D + (n % D)];
+    }
 }
 
 // mapY: the four dy as (channel, time, batch) each (four maps), box 64 x 128 x 1;  mapX: x, box 64 x 129 x 1;
@@ -772,17 +782,6 @@ __host__ __device__ constexpr uint32_t idesc_mn64(int n) {  // fp32 accumulate, 
     return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(n >> 3) << 17) | (4u << 24);
 }
 }  // namespace g5
-
-// L^T as [C, 4D] and R' as [C, 4D] (column k D + d = R[k][c][d])
-__global__ void ddlerp_prep_lt_rp_kernel(const __nv_bfloat16* __restrict__ L, const __nv_bfloat16* __restrict__ R, __nv_bfloat16* __restrict__ Lt,
-                                         __nv_bfloat16* __restrict__ Rp, int C, int D) {
-    const int n4 = 4 * D;
-    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-    if (i >= (long long)C * n4) return;
-    const int c = (int)(i / n4), n = (int)(i % n4);
-    Lt[i] = L[(long long)n * C + c];
-    Rp[i] = R[((long long)(n / D) * C + c) * D + (n % D)];
-}
 
 struct MainMaps { CUtensorMap dy[4], x, dpre, m, lt, rp, dx; };
 // maps: dy_k, x as (channel, time, batch), boxes 64 x 128 x 1 and 64 x 129 x 1; dpre, m as (column, time, batch), box 64 x 128 x 1;
@@ -1158,13 +1157,8 @@ template <int D> static int launch_main_tc_t(const DdlerpBwdParams& p, void* ws,
     using namespace dtc;
     const long long B = p.rows / p.T, C = p.C, T = p.T;
     const int n4 = 4 * D;
-    __nv_bfloat16* Lt = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(ws) + (size_t)n4 * C * 6);
+    __nv_bfloat16* Lt = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(ws) + (size_t)n4 * C * 6);  // written by launch_ddlerp_prep_bwd
     __nv_bfloat16* Rp = Lt + (size_t)n4 * C;
-    {
-        const long long n = (long long)n4 * C;
-        ddlerp_prep_lt_rp_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)p.L, (const __nv_bfloat16*)p.R, Lt, Rp, (int)C, D);
-        if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
-    }
     alignas(64) MainMaps mm;
     const long long dx[3] = {C, T, B}, sx[2] = {C, T * C}, dn[3] = {n4, T, B}, sn[2] = {n4, T * n4}, dw[2] = {n4, C}, sw[1] = {n4};
     const int b128[3] = {64, BM, 1}, b129[3] = {64, BM + 1, 1}, bw[2] = {64, 64}, b32[3] = {64, 32, 1};
@@ -1198,17 +1192,22 @@ int launch_ddlerp_main_tc(const DdlerpBwdParams& p, void* ws, int* status, cudaS
     return kBadShape;
 }
 
+// the rearranged weights of the tcgen05 backward kernels into the scratch: R^T, L^T, R' behind dW2
+int launch_ddlerp_prep_bwd(const DdlerpBwdParams& p, void* ws, cudaStream_t stream) {
+    const long long C = p.C;
+    const int n4 = 4 * p.D;
+    __nv_bfloat16* Rt = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(ws) + (size_t)n4 * C * 4);
+    const long long n = (long long)n4 * C;
+    dtc::ddlerp_prep_bwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)p.L, (const __nv_bfloat16*)p.R, Rt, Rt + n, Rt + 2 * n, (int)C, p.D);
+    return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
 // dpre (bf16 [rows, 4D]) from dy, x, R and m; ranks 16 and 32
 template <int D> static int launch_dpre_tc_t(const DdlerpBwdParams& p, void* ws, int* status, cudaStream_t stream) {
     using namespace dtc;
     const long long B = p.rows / p.T, C = p.C, T = p.T;
     const int n4 = 4 * D;
-    __nv_bfloat16* Rt = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(ws) + (size_t)n4 * C * 4);
-    {
-        const long long n = (long long)n4 * C;
-        ddlerp_prep_rt_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)p.R, Rt, (int)C, D);
-        if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
-    }
+    __nv_bfloat16* Rt = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(ws) + (size_t)n4 * C * 4);  // written by launch_ddlerp_prep_bwd
     if (B > 65535) return kTooLarge;
     alignas(64) DyMaps mY;
     alignas(64) CUtensorMap mX, mRt, mP;
