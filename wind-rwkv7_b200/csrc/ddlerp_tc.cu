@@ -747,12 +747,14 @@ __global__ void __launch_bounds__(g4::THREADS, 1) ddlerp_dpre_tc_kernel(const __
 // Persistent: one CTA per SM walks a contiguous range of the unit list (channel blocks slowest), so the token-contracted
 // accumulators stay in tensor memory until the channel block changes.  Per unit: bulk tensor loads of the dpre, m, dy_k and
 // x tiles (and, when the channel block changes, of its blocks of L^T and R'); products 1 into tensor-memory columns 0..319;
-// eight epilogue warps (row quarter x channel half) read them one token row per thread, form X, Dd, write dz_k IN PLACE into
+// sixteen epilogue warps (row quarter x channel quarter) read them one token row per thread, form X, Dd, write dz_k IN PLACE into
 // the dy tiles (which then are, as they lie, the MN-major A operands of products 2) and dx into a staging tile for a bulk
 // tensor store; X_{t+1} comes from the next lane, across warps through shared memory, and for the tile's last row from a
-// halo row computed on the CUDA cores (one row of du and z_k: 16K multiply-adds), so units are independent of each other.
+// halo row computed on the CUDA cores out of the weight tiles in shared memory (one row of du and z_k: 16K multiply-adds),
+// so units are independent of each other.
 namespace g5 {
-constexpr int THREADS = 320;  // warps 0-7: epilogue (row quarter w % 4, channel half w / 4), warp 8: TMA, warp 9: MMA
+constexpr int EPI_WARPS = 16, THREADS = 32 * (EPI_WARPS + 2);  // warps 0-15: epilogue (row quarter w % 4, channel quarter w / 4), warp 16: TMA, warp 17: MMA
+constexpr int CPT = 64 / (EPI_WARPS / 4);   // channels per epilogue thread
 constexpr int TILE = BM * 128;                               // a [128 rows][64 columns] bf16 block
 constexpr int X_BYTES = ((BM + 1) * 128 + 1023) / 1024 * 1024;
 struct Ctrl {
@@ -808,8 +810,8 @@ __global__ void __launch_bounds__(g5::THREADS, 1) ddlerp_main_tc_kernel(const __
     // unit u: channel block u / tiles, token tile u % tiles (tile -> sequence tile / tiles_per_seq, first token (tile % tiles_per_seq) * 128)
 
     if (tid == 0) {
-        mbar_init(&ctrl->full, 1); mbar_init(&ctrl->wfull, 1); mbar_init(&ctrl->acc1, 1); mbar_init(&ctrl->dz_ready, 8);
-        mbar_init(&ctrl->unit_free, 1); mbar_init(&ctrl->flushed, 8); mbar_init(&ctrl->drain, 1);
+        mbar_init(&ctrl->full, 1); mbar_init(&ctrl->wfull, 1); mbar_init(&ctrl->acc1, 1); mbar_init(&ctrl->dz_ready, EPI_WARPS);
+        mbar_init(&ctrl->unit_free, 1); mbar_init(&ctrl->flushed, EPI_WARPS); mbar_init(&ctrl->drain, 1);
         ctrl->abort = 0; ctrl->zero = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -826,7 +828,7 @@ __global__ void __launch_bounds__(g5::THREADS, 1) ddlerp_main_tc_kernel(const __
     const uint32_t tmem = ctrl->tmem_base;
     const uint32_t sb = smem_u32(sm);
 
-    if (warp == 8) {
+    if (warp == EPI_WARPS) {
         if (elect_one()) {
             int cb_prev = -1, nw = 0;
             for (int n = 0; n < nmine; ++n) {
@@ -856,7 +858,7 @@ __global__ void __launch_bounds__(g5::THREADS, 1) ddlerp_main_tc_kernel(const __
             (void)nw;
         }
         __syncwarp();
-    } else if (warp == 9) {
+    } else if (warp == EPI_WARPS + 1) {
         if (elect_one()) {
             int cb_prev = -1, nw = 0, nflush = 0;
             for (int n = 0; n < nmine; ++n) {
@@ -910,9 +912,9 @@ __global__ void __launch_bounds__(g5::THREADS, 1) ddlerp_main_tc_kernel(const __
         }
         __syncwarp();
     } else {
-        const int q = warp & 3, g = warp >> 2;   // row quarter (= tensor-memory lane quarter), channel half
-        const int r = 32 * q + lane, ch0 = 32 * g;
-        const int et = tid;                       // 0..255 among the epilogue warps
+        const int q = warp & 3, g = warp >> 2;   // row quarter (= tensor-memory lane quarter), channel group
+        const int r = 32 * q + lane, ch0 = CPT * g;
+        const int et = tid;                       // 0..32 EPI_WARPS - 1 among the epilogue warps
         const __nv_bfloat16* dyp[4] = {dyp0, dyp1, dyp2, dyp3};
         const uint32_t tlane = tmem + ((uint32_t)(32 * q) << 16);
         // token-contracted accumulators of channel block cbf -> global memory (vector reductions); the M = 64 products keep
@@ -952,7 +954,7 @@ __global__ void __launch_bounds__(g5::THREADS, 1) ddlerp_main_tc_kernel(const __
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ctrl->flushed)) : "memory");
         };
         if (et < 64) ctrl->halo[et] = 0.f;
-        int cb_prev = -1;
+        int cb_prev = -1, nwf = 0;
         for (int n = 0; n < nmine; ++n) {
             const int u = u_lo + n, cb = u / tiles, tile = u % tiles, t0 = (tile % tiles_per_seq) * BM, bi = tile / tiles_per_seq;
             if (cb != cb_prev) {
@@ -961,92 +963,91 @@ __global__ void __launch_bounds__(g5::THREADS, 1) ddlerp_main_tc_kernel(const __
                     flush(cb_prev);
                 }
                 cb_prev = cb;
-                asm volatile("bar.sync 1, 256;" ::: "memory");  // every epilogue warp has finished the previous unit
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");  // every epilogue warp has finished the previous unit
                 if (et < 64) ctrl->alpha[et] = __bfloat162float(alpha[cb * 64 + et]);
-                ctrl->beta[et >> 6][et & 63] = __bfloat162float(beta[(long long)(et >> 6) * C + cb * 64 + (et & 63)]);
-                asm volatile("bar.sync 1, 256;" ::: "memory");  // alpha and beta of this channel block are in place
+                if (et < 256) ctrl->beta[et >> 6][et & 63] = __bfloat162float(beta[(long long)(et >> 6) * C + cb * 64 + (et & 63)]);
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");  // alpha and beta of this channel block are in place
+                mbar_wait_bounded<true>(&ctrl->wfull, nwf & 1, &ctrl->abort, status);   // and its weight tiles (read for the halo row)
+                ++nwf;
             }
             // ---- halo: X of the token after this tile (zero past the sequence's end), accumulated with shared-memory atomics.
-            // Thread = (8 channels, one of 32 slices of the contraction): 4 rows of L and, for stream slice / 8, 4 ranks of R.
-            if (t0 + BM < T) {
+            // Thread = (channel c, quarter of the contraction = stream k): D rows of L^T for du, the D ranks of R' for z_k, both
+            // read out of the swizzled weight tiles in shared memory (16-byte pieces; lanes are consecutive channels).
+            if (t0 + BM < T && et < 256) {
                 const long long hrow = (long long)bi * T + t0 + BM;
-                const int cg8 = (et & 7) * 8, sl = et >> 3;   // lanes of a warp: 8 channel groups x 4 slices
-                float acc[8];
+                const int c = et & 63, k = et >> 6, n0 = k * D;
+                const unsigned char* lt = sm + off_lt(D) + (n0 >> 6) * 64 * 128 + c * 128;
+                const unsigned char* rp = sm + off_rp(D) + (n0 >> 6) * 64 * 128 + c * 128;
+                float du = 0.f, z = 0.f;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+                for (int pc8 = 0; pc8 < D / 8; ++pc8) {
+                    const int slot = ((((n0 & 63) >> 3) + pc8) ^ (c & 7)) << 4;
+                    float lv[8], rv[8], dp[8], mv[8];
+                    unpack8(*reinterpret_cast<const uint4*>(lt + slot), lv);
+                    unpack8(*reinterpret_cast<const uint4*>(rp + slot), rv);
+                    unpack8(*reinterpret_cast<const uint4*>(dpre + hrow * N4 + n0 + 8 * pc8), dp);
+                    unpack8(*reinterpret_cast<const uint4*>(mten + hrow * N4 + n0 + 8 * pc8), mv);
 #pragma unroll
-                for (int i4 = 0; i4 < N4 / 32; ++i4) {   // du part: rows sl * (4D / 32) ... of L
-                    const int nn = sl * (N4 / 32) + i4;
-                    float lv[8];
-                    unpack8(*reinterpret_cast<const uint4*>(L + (long long)nn * C + cb * 64 + cg8), lv);
-                    const float dp = __bfloat162float(dpre[hrow * N4 + nn]);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[j] += dp * lv[j] * ctrl->alpha[cg8 + j];
+                    for (int j = 0; j < 8; ++j) { du += dp[j] * lv[j]; z += mv[j] * rv[j]; }
                 }
-                {   // z part of stream k: ranks (sl % 8) * (D / 8) ...
-                    const int k = sl >> 3, d0 = (sl & 7) * (D / 8);
-                    float zz[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) zz[j] = 0.f;
-#pragma unroll
-                    for (int dd = 0; dd < D / 8; ++dd) {
-                        const float mv = __bfloat162float(mten[hrow * N4 + k * D + d0 + dd]);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) zz[j] += mv * __bfloat162float(R[((long long)k * C + cb * 64 + cg8 + j) * D + d0 + dd]);
-                    }
-                    float dv[8];
-                    unpack8(*reinterpret_cast<const uint4*>(dyp[k] + hrow * C + cb * 64 + cg8), dv);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[j] += dv[j] * (zz[j] + ((sl & 7) == 0 ? ctrl->beta[k][cg8 + j] : 0.f));
-                }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) atomicAdd(&ctrl->halo[cg8 + j], acc[j]);
+                const float dyh = __bfloat162float(dyp[k][hrow * C + cb * 64 + c]);
+                atomicAdd(&ctrl->halo[c], du * ctrl->alpha[c] + dyh * (z + ctrl->beta[k][c]));
             }
             // ---- X, Dd and dz for this thread's row and 32 channels ---------------------------------------------------
             mbar_wait_bounded<true>(&ctrl->full, n & 1, &ctrl->abort, status);
             mbar_wait_bounded<true>(&ctrl->acc1, n & 1, &ctrl->abort, status);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const bool ok = !ctrl->abort;
-            float X[32], Dd[32];
+            float X[CPT], Dd[CPT];
             const unsigned char* xs = sm + off_x(D);
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
-                uint32_t du[16], zk[4][16];
-                tmem_ld16(tlane + C_DU + ch0 + 16 * cc, du);
+            for (int cc = 0; cc < CPT / 16; ++cc) {
+                float pvs[16];   // x_{t-1} - x_t of these 16 channels
+                {
+                    uint32_t du[16];
+                    tmem_ld16(tlane + C_DU + ch0 + 16 * cc, du);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) tmem_ld16(tlane + C_Z + 64 * k + ch0 + 16 * cc, zk[k]);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    for (int h = 0; h < 2; ++h) {
+                        const int pc = (ch0 >> 3) + 2 * cc + h;   // 16-byte piece of the 64-channel rows
+                        float xv[8], pv[8];
+                        unpack8(*reinterpret_cast<const uint4*>(xs + (r + 1) * 128 + ((pc ^ ((r + 1) & 7)) << 4)), xv);
+                        unpack8(*reinterpret_cast<const uint4*>(xs + r * 128 + ((pc ^ (r & 7)) << 4)), pv);
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int pc = (ch0 >> 3) + 2 * cc + h, cbase = ch0 + 16 * cc + 8 * h;   // 16-byte piece of the 64-channel rows
-                    float xv[8], pv[8];
-                    unpack8(*reinterpret_cast<const uint4*>(xs + (r + 1) * 128 + ((pc ^ ((r + 1) & 7)) << 4)), xv);
-                    unpack8(*reinterpret_cast<const uint4*>(xs + r * 128 + ((pc ^ (r & 7)) << 4)), pv);
-                    float xa[8], da[8];
+                        for (int j = 0; j < 8; ++j) pvs[8 * h + j] = pv[j] - xv[j];
+                    }
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        pv[j] -= xv[j];
-                        const float d = __uint_as_float(du[8 * h + j]);
-                        xa[j] = d * ctrl->alpha[cbase + j];
-                        da[j] = d;
+                    for (int j = 0; j < 16; ++j) {
+                        const float d = __uint_as_float(du[j]);
+                        X[16 * cc + j] = d * ctrl->alpha[ch0 + 16 * cc + j];
+                        Dd[16 * cc + j] = d;
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    uint32_t zk[16];
+                    tmem_ld16(tlane + C_Z + 64 * k + ch0 + 16 * cc, zk);
+                    float dv[16];
+                    uint4* cell[2];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int pc = (ch0 >> 3) + 2 * cc + h;
+                        cell[h] = reinterpret_cast<uint4*>(sm + off_dy(D) + k * TILE + r * 128 + ((pc ^ (r & 7)) << 4));
+                        unpack8(*cell[h], dv + 8 * h);
+                    }
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        X[16 * cc + j] += dv[j] * (__uint_as_float(zk[j]) + ctrl->beta[k][ch0 + 16 * cc + j]);
+                        Dd[16 * cc + j] += dv[j];
                     }
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        uint4* cell = reinterpret_cast<uint4*>(sm + off_dy(D) + k * TILE + r * 128 + ((pc ^ (r & 7)) << 4));
-                        float dv[8];
-                        unpack8(*cell, dv);
+                    for (int h = 0; h < 2; ++h) {
                         uint4 o;
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            xa[j] += dv[j] * (__uint_as_float(zk[k][8 * h + j]) + ctrl->beta[k][cbase + j]);
-                            da[j] += dv[j];
-                        }
-                        o.x = pack2(dv[0] * pv[0], dv[1] * pv[1]); o.y = pack2(dv[2] * pv[2], dv[3] * pv[3]);
-                        o.z = pack2(dv[4] * pv[4], dv[5] * pv[5]); o.w = pack2(dv[6] * pv[6], dv[7] * pv[7]);
-                        *cell = o;
+                        o.x = pack2(dv[8 * h + 0] * pvs[8 * h + 0], dv[8 * h + 1] * pvs[8 * h + 1]); o.y = pack2(dv[8 * h + 2] * pvs[8 * h + 2], dv[8 * h + 3] * pvs[8 * h + 3]);
+                        o.z = pack2(dv[8 * h + 4] * pvs[8 * h + 4], dv[8 * h + 5] * pvs[8 * h + 5]); o.w = pack2(dv[8 * h + 6] * pvs[8 * h + 6], dv[8 * h + 7] * pvs[8 * h + 7]);
+                        *cell[h] = o;
                     }
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) { X[16 * cc + 8 * h + j] = xa[j]; Dd[16 * cc + 8 * h + j] = da[j]; }
                 }
             }
             // dz is in place: products 2 may start.  X of the first row of every quarter goes to shared memory for the row above.
@@ -1054,16 +1055,16 @@ __global__ void __launch_bounds__(g5::THREADS, 1) ddlerp_main_tc_kernel(const __
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             if (lane == 0) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) ctrl->edge[q][ch0 + j] = X[j];
+                for (int j = 0; j < CPT; ++j) ctrl->edge[q][ch0 + j] = X[j];
                 asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous unit's dx store has read the staging tile
             }
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ctrl->dz_ready)) : "memory");
-            asm volatile("bar.sync 2, 256;" ::: "memory");   // edges and the halo sums are complete
+            asm volatile("bar.sync 2, %0;" ::"n"(32 * EPI_WARPS) : "memory");   // edges and the halo sums are complete
             // ---- dx_t = Dd_t - X_t + X_{t+1} ------------------------------------------------------------------------------
             unsigned char* dxs = sm + off_dx(D);
 #pragma unroll
-            for (int pcl = 0; pcl < 4; ++pcl) {
+            for (int pcl = 0; pcl < CPT / 8; ++pcl) {
                 float o[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
@@ -1079,10 +1080,10 @@ __global__ void __launch_bounds__(g5::THREADS, 1) ddlerp_main_tc_kernel(const __
             }
             if (q == 3 && lane == 31) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) ctrl->halo[ch0 + j] = 0.f;   // read above; the next unit's sums start after the barrier below
+                for (int j = 0; j < CPT; ++j) ctrl->halo[ch0 + j] = 0.f;   // read above; the next unit's sums start after the barrier below
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            asm volatile("bar.sync 3, 256;" ::: "memory");   // staging tile complete; edge and halo values have been read
+            asm volatile("bar.sync 3, %0;" ::"n"(32 * EPI_WARPS) : "memory");   // staging tile complete; edge and halo values have been read
             if (g == 0 && lane == 0) {
                 if (ok && t0 + 32 * q < T)
                     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
