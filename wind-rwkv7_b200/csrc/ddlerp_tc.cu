@@ -758,7 +758,7 @@ constexpr int CPT = 64 / (EPI_WARPS / 4);   // channels per epilogue thread
 constexpr int TILE = BM * 128;                               // a [128 rows][64 columns] bf16 block
 constexpr int X_BYTES = ((BM + 1) * 128 + 1023) / 1024 * 1024;
 struct Ctrl {
-    uint64_t full, wfull, acc1, dz_ready, unit_free, flushed, drain;
+    uint64_t full, full_a, full_x, wfull, acc1, dz_ready, unit_free, flushed, drain;   // full: m and dy tiles; full_a: dpre tile; full_x: x tile
     uint32_t tmem_base;
     volatile int abort, zero;
     alignas(16) float alpha[64], beta[4][64], halo[64], edge[4][64];
@@ -810,7 +810,7 @@ __global__ void __launch_bounds__(g5::THREADS, 1) ddlerp_main_tc_kernel(const __
     // unit u: channel block u / tiles, token tile u % tiles (tile -> sequence tile / tiles_per_seq, first token (tile % tiles_per_seq) * 128)
 
     if (tid == 0) {
-        mbar_init(&ctrl->full, 1); mbar_init(&ctrl->wfull, 1); mbar_init(&ctrl->acc1, 1); mbar_init(&ctrl->dz_ready, EPI_WARPS);
+        mbar_init(&ctrl->full, 1); mbar_init(&ctrl->full_a, 1); mbar_init(&ctrl->full_x, 1); mbar_init(&ctrl->wfull, 1); mbar_init(&ctrl->acc1, 1); mbar_init(&ctrl->dz_ready, EPI_WARPS);
         mbar_init(&ctrl->unit_free, 1); mbar_init(&ctrl->flushed, EPI_WARPS); mbar_init(&ctrl->drain, 1);
         ctrl->abort = 0; ctrl->zero = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -831,12 +831,25 @@ __global__ void __launch_bounds__(g5::THREADS, 1) ddlerp_main_tc_kernel(const __
     if (warp == EPI_WARPS) {
         if (elect_one()) {
             int cb_prev = -1, nw = 0;
+            // The dpre tile is only read by products 1 and the x tile only by the epilogue's first phase: the next unit's copies
+            // of the two are requested as soon as those are done, ahead of the m and dy tiles, which products 2 still read.
+            auto load_dpre = [&](int n) {
+                const int tile = (u_lo + n) % tiles, t0 = (tile % tiles_per_seq) * BM, bi = tile / tiles_per_seq;
+                mbar_expect(&ctrl->full_a, (uint32_t)(KB * TILE));
+#pragma unroll
+                for (int kb = 0; kb < KB; ++kb) tma_load_3d(sb + kb * TILE, &maps.dpre, &ctrl->full_a, kb * 64, t0, bi);
+            };
+            auto load_x = [&](int n) {
+                const int u = u_lo + n, cb = u / tiles, tile = u % tiles, t0 = (tile % tiles_per_seq) * BM, bi = tile / tiles_per_seq;
+                mbar_expect(&ctrl->full_x, (uint32_t)((BM + 1) * 128));
+                tma_load_3d(sb + off_x(D), &maps.x, &ctrl->full_x, cb * 64, t0 - 1, bi);
+            };
+            if (nmine > 0) { load_dpre(0); load_x(0); }
             for (int n = 0; n < nmine; ++n) {
                 const int u = u_lo + n, cb = u / tiles, tile = u % tiles, t0 = (tile % tiles_per_seq) * BM, bi = tile / tiles_per_seq;
                 if (n > 0) mbar_wait_bounded<true>(&ctrl->unit_free, (n - 1) & 1, &ctrl->abort, status);  // products 2 of the previous unit have read the tiles
                 if (cb != cb_prev) {
-                    // the previous channel block's accumulators must have been flushed before products 2 of this unit overwrite
-                    // them; the weights may be replaced as soon as the previous unit's products are complete (unit_free)
+                    // the weights may be replaced as soon as the previous unit's products are complete (unit_free)
                     cb_prev = cb; ++nw;
                     mbar_expect(&ctrl->wfull, (uint32_t)(2 * KB * 64 * 128));
 #pragma unroll
@@ -845,15 +858,17 @@ __global__ void __launch_bounds__(g5::THREADS, 1) ddlerp_main_tc_kernel(const __
                         tma_load_2d(sb + off_rp(D) + kb * 64 * 128, &maps.rp, &ctrl->wfull, kb * 64, cb * 64);
                     }
                 }
-                mbar_expect(&ctrl->full, (uint32_t)(2 * KB * TILE + 4 * TILE + (BM + 1) * 128));
+                mbar_expect(&ctrl->full, (uint32_t)(KB * TILE + 4 * TILE));
 #pragma unroll
-                for (int kb = 0; kb < KB; ++kb) {
-                    tma_load_3d(sb + kb * TILE, &maps.dpre, &ctrl->full, kb * 64, t0, bi);
-                    tma_load_3d(sb + off_m(D) + kb * TILE, &maps.m, &ctrl->full, kb * 64, t0, bi);
-                }
+                for (int kb = 0; kb < KB; ++kb) tma_load_3d(sb + off_m(D) + kb * TILE, &maps.m, &ctrl->full, kb * 64, t0, bi);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) tma_load_3d(sb + off_dy(D) + k * TILE, &maps.dy[k], &ctrl->full, cb * 64, t0, bi);
-                tma_load_3d(sb + off_x(D), &maps.x, &ctrl->full, cb * 64, t0 - 1, bi);
+                if (n + 1 < nmine) {
+                    mbar_wait_bounded<true>(&ctrl->acc1, n & 1, &ctrl->abort, status);       // products 1 of this unit have read the dpre tile
+                    load_dpre(n + 1);
+                    mbar_wait_bounded<true>(&ctrl->dz_ready, n & 1, &ctrl->abort, status);   // every epilogue warp is past the x tile
+                    load_x(n + 1);
+                }
             }
             (void)nw;
         }
@@ -869,6 +884,7 @@ __global__ void __launch_bounds__(g5::THREADS, 1) ddlerp_main_tc_kernel(const __
                     mbar_wait_bounded<false>(&ctrl->wfull, nw & 1, &ctrl->abort, status);
                     ++nw;
                 }
+                mbar_wait_bounded<false>(&ctrl->full_a, n & 1, &ctrl->abort, status);
                 mbar_wait_bounded<false>(&ctrl->full, n & 1, &ctrl->abort, status);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 // products 1: du = dpre L^T-block^T (K = 4D), z_k = m_k R'_k^T (K = D)
@@ -994,6 +1010,7 @@ __global__ void __launch_bounds__(g5::THREADS, 1) ddlerp_main_tc_kernel(const __
                 atomicAdd(&ctrl->halo[c], du * ctrl->alpha[c] + dyh * (z + ctrl->beta[k][c]));
             }
             // ---- X, Dd and dz for this thread's row and 32 channels ---------------------------------------------------
+            mbar_wait_bounded<true>(&ctrl->full_x, n & 1, &ctrl->abort, status);
             mbar_wait_bounded<true>(&ctrl->full, n & 1, &ctrl->abort, status);
             mbar_wait_bounded<true>(&ctrl->acc1, n & 1, &ctrl->abort, status);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
