@@ -792,8 +792,7 @@ template <int D>
 __global__ void __launch_bounds__(g5::THREADS, 1) ddlerp_main_tc_kernel(const __grid_constant__ MainMaps maps, const __nv_bfloat16* __restrict__ dyp0,
                                                                        const __nv_bfloat16* __restrict__ dyp1, const __nv_bfloat16* __restrict__ dyp2,
                                                                        const __nv_bfloat16* __restrict__ dyp3, const __nv_bfloat16* __restrict__ dpre,
-                                                                       const __nv_bfloat16* __restrict__ mten, const __nv_bfloat16* __restrict__ L,
-                                                                       const __nv_bfloat16* __restrict__ R, const __nv_bfloat16* __restrict__ alpha,
+                                                                       const __nv_bfloat16* __restrict__ mten, const __nv_bfloat16* __restrict__ alpha,
                                                                        const __nv_bfloat16* __restrict__ beta, float* __restrict__ dR,
                                                                        float* __restrict__ dbeta, int C, int T, int tiles_per_seq, int tiles, int units,
                                                                        int* status) {
@@ -1198,8 +1197,7 @@ template <int D> static int launch_main_tc_t(const DdlerpBwdParams& p, void* ws,
     if (units > 0x7fffffffLL) return kTooLarge;
     const unsigned grid = (unsigned)(units < sms ? units : sms);
     kern<<<grid, g5::THREADS, smem, stream>>>(mm, (const __nv_bfloat16*)p.dy[0], (const __nv_bfloat16*)p.dy[1], (const __nv_bfloat16*)p.dy[2],
-                                             (const __nv_bfloat16*)p.dy[3], (const __nv_bfloat16*)p.dpre, (const __nv_bfloat16*)p.m,
-                                             (const __nv_bfloat16*)p.L, (const __nv_bfloat16*)p.R, (const __nv_bfloat16*)p.alpha,
+                                             (const __nv_bfloat16*)p.dy[3], (const __nv_bfloat16*)p.dpre, (const __nv_bfloat16*)p.m, (const __nv_bfloat16*)p.alpha,
                                              (const __nv_bfloat16*)p.beta, p.dR, p.dbeta, (int)C, (int)T, (int)tiles_per_seq, (int)tiles, (int)units, status);
     return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
 }
