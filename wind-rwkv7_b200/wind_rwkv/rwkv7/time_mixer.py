@@ -16,6 +16,29 @@ from .rwkv7_expand_loras import expand_loras
 from .rwkv7_proj import proj as fused_proj
 
 
+class _CastAll(torch.autograd.Function):
+    """bf16 copies of the projection weights in one multi-tensor copy, and their gradients back to the parameters'
+    dtypes in another (upstream casts weight by weight, time_mixer.py:120-131: a dozen small launches each way)."""
+
+    @staticmethod
+    def forward(ctx, *params):
+        ctx.dtypes = [p.dtype for p in params]
+        outs = [torch.empty_like(p, dtype=torch.bfloat16) for p in params]
+        torch._foreach_copy_(outs, [p.detach() for p in params])
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        idx = [i for i, g in enumerate(grads) if g is not None]
+        outs = [torch.empty_like(grads[i], dtype=ctx.dtypes[i]) for i in idx]
+        if idx:
+            torch._foreach_copy_(outs, [grads[i].contiguous() for i in idx])
+        res = [None] * len(grads)
+        for i, o in zip(idx, outs):
+            res[i] = o
+        return tuple(res)
+
+
 def ref_attn(q, w, k, v, a, b, HEAD_SIZE):
     """The naive per-step recurrence (upstream time_mixer.py:6-16), kept for users who call it to
     check results; it runs on whatever device and dtype its inputs have."""
@@ -96,30 +119,35 @@ class TimeMixer(nn.Module):
         self.Wr, self.Wk, self.Wv, self.Wo = uniform(0.5), uniform(0.05), uniform(0.5), uniform(0)
         self.ln_x = nn.GroupNorm(self.n_head, C, eps=64e-5)
 
+    # the weights of the plain projections (their gradients are bf16 products anyway); the parameters of ddlerp and
+    # expand_loras go to those ops as they are: the ops cast them themselves and return fp32 gradients
+    _BF16_PARAMS = ('Wr', 'Wk', 'Wv', 'Wo', 'gate_w1', 'gate_w2', 'time_kkk_w1', 'mk_w1', 'time_decay_w1', 'time_aaa_w1', 'ma_w1',
+                    'time_decay_w2')
+
     def forward(self, x):
         r16 = self.SMALL_RANK
         bf = torch.bfloat16
+        P = dict(zip(self._BF16_PARAMS, _CastAll.apply(*[getattr(self, n) for n in self._BF16_PARAMS])))  # bf16, one launch
         xrg, xwa, xk, xv = ddlerp(x.to(bf), self.time_maa_x, self.time_maa_w1, self.time_maa_w2, self.time_maa)
 
-        def proj(inp, *weights):
-            w = weights[0] if len(weights) == 1 else torch.cat(weights)
-            return inp @ w.to(bf).mT
+        def proj(inp, name):
+            return inp @ P[name].mT
 
-        def lora1(inp, tanh_cols, *weights):
+        def lora1(inp, tanh_cols, *names):
             # first stage of one or several LoRAs on the tcgen05 projection kernel, tanh fused into the chosen columns
-            return fused_proj(inp, torch.cat(weights).to(bf) if len(weights) > 1 else weights[0].to(bf), tanh_cols)
+            return fused_proj(inp, torch.cat([P[n] for n in names]) if len(names) > 1 else P[names[0]], tanh_cols)
 
-        r = proj(xrg, self.Wr)
-        g = lora1(xrg, (0, self.GATE_RANK), self.gate_w1) @ self.gate_w2.to(bf).mT
-        k = proj(xk, self.Wk)
-        kk1, mk1 = lora1(xk, None, self.time_kkk_w1, self.mk_w1).split([r16, r16], dim=2)
-        v = proj(xv, self.Wv)
-        w1t, a1, ma1 = lora1(xwa, (0, self.DECAY_RANK), self.time_decay_w1, self.time_aaa_w1, self.ma_w1).split(
+        r = proj(xrg, 'Wr')
+        g = lora1(xrg, (0, self.GATE_RANK), 'gate_w1') @ P['gate_w2'].mT
+        k = proj(xk, 'Wk')
+        kk1, mk1 = lora1(xk, None, 'time_kkk_w1', 'mk_w1').split([r16, r16], dim=2)
+        v = proj(xv, 'Wv')
+        w1t, a1, ma1 = lora1(xwa, (0, self.DECAY_RANK), 'time_decay_w1', 'time_aaa_w1', 'ma_w1').split(
             [self.DECAY_RANK, r16, r16], dim=2)
-        w2 = w1t @ self.time_decay_w2.to(bf).mT
+        w2 = w1t @ P['time_decay_w2'].mT
 
         w, k, kk, b = expand_loras(w2, k, kk1, a1, ma1, mk1, self.time_kkk_w2, self.time_aaa_w2, self.ma_w2, self.mk_w2,
                                    self.time_decay, self.time_aaaaa, self.time_misc_a, self.time_misc_k, self.head_size)
         params = torch.stack([self.ln_x.weight, self.ln_x.bias, self.time_faaaa]).float()
         y = attn_ln(r, w, k, v, kk, b, g, params, self.head_size)
-        return y @ self.Wo.to(bf).mT
+        return y @ P['Wo'].mT
