@@ -211,20 +211,7 @@ __global__ void __launch_bounds__(128) loras_bwd_kernel(LorasParams p) {
     for (int t0 = tbeg; t0 < tend; t0 += 64) {
         const long long r0 = b0 + t0 + 16 * warp;
         const bool valid = t0 + 16 * warp < T;
-        // ---- stage this tile's LoRA inputs (tanh applied to z_in) ---------------------------------------
-        for (int i = tid; i < 4 * 64 * (D / 8); i += 128) {
-            const int l = i / (64 * (D / 8)), r = (i / (D / 8)) % 64, ch = i % (D / 8);
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (t0 + r < T) v = *reinterpret_cast<const uint4*>((const bf16*)p.lin[l] + (b0 + t0 + r) * D + ch * 8);
-            if (l == 0) {
-                float f[8];
-                unpack8(v, f);
-#pragma unroll
-                for (int q = 0; q < 8; ++q) f[q] = tanh_f(f[q]);
-                v = pack8(f);
-            }
-            *reinterpret_cast<uint4*>(&sm.in[l][r][ch * 8]) = v;
-        }
+        // ---- the six [token][channel] tiles first (asynchronous copies), then this tile's LoRA inputs under them ------------
         {
             const bf16* src6[6] = {(const bf16*)p.w_in, (const bf16*)p.k_in, (const bf16*)p.dw_out, (const bf16*)p.dk_out,
                                    (const bf16*)p.db_out, (const bf16*)p.dkk_out};
@@ -234,6 +221,35 @@ __global__ void __launch_bounds__(128) loras_bwd_kernel(LorasParams p) {
                 cp_async16_zfill(&sm.gr[ten][r][ch * 8], src6[ten] + (b0 + (live ? t0 + r : 0)) * C + h * HC + ch * 8, live);
             }
             cp_async_commit();
+        }
+        // LoRA inputs (tanh applied to z_in): the loads of a group of four are issued together, so that their latencies overlap
+        {
+            constexpr int ITEMS = 4 * 64 * (D / 8) / 128;  // per thread
+            static_assert(ITEMS % 4 == 0, "groups of four loads per thread");
+#pragma unroll
+            for (int i0 = 0; i0 < ITEMS; i0 += 4) {
+                uint4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = tid + 128 * (i0 + u);
+                    const int l = i / (64 * (D / 8)), r = (i / (D / 8)) % 64, ch = i % (D / 8);
+                    v[u] = make_uint4(0, 0, 0, 0);
+                    if (t0 + r < T) v[u] = *reinterpret_cast<const uint4*>((const bf16*)p.lin[l] + (b0 + t0 + r) * D + ch * 8);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = tid + 128 * (i0 + u);
+                    const int l = i / (64 * (D / 8)), r = (i / (D / 8)) % 64, ch = i % (D / 8);
+                    if (l == 0) {
+                        float f[8];
+                        unpack8(v[u], f);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) f[q] = tanh_f(f[q]);
+                        v[u] = pack8(f);
+                    }
+                    *reinterpret_cast<uint4*>(&sm.in[l][r][ch * 8]) = v[u];
+                }
+            }
         }
         cp_async_wait<0>();
         __syncthreads();
