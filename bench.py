@@ -9,7 +9,7 @@ torchrun, one rank per GPU) every rank processes its own batch shard; chains are
 there is no collective on the data path ("weak" scaling) and NCCL is used only to take the maximum
 time over ranks.  One JSON line is printed by rank 0.
 
-`--workload attn_ln|prefill|ddlerp|expand_loras|mixer` time the other workloads of the path (prefill also under
+`--workload attn_ln|prefill|ddlerp|expand_loras|mixer|proj` time the other workloads of the path (prefill also under
 torchrun: config 4 with its 8 sequences sharded over the ranks, "strong" scaling); the default run reports them under
 `secondary`.  `--impl reference-cuda` times the reference's own CUDA kernels from baseline/_ref (context only).
 
@@ -678,6 +678,50 @@ def other_line(wl, batch, steps, warmup):
     return line
 
 
+def run_proj(args):
+    """The projection GEMM (wkv7_proj_gemm through proj()) at the time mixer's shapes, beside the torch call it replaces
+    (a cuBLAS product, plus an elementwise tanh pass where the LoRA's first stage has one).  Forward only, CUDA events,
+    one JSON line per shape."""
+    from wind_rwkv.rwkv7 import proj
+    th.cuda.set_device(0)
+    dev = th.device('cuda', 0)
+    M = 32 * 1024
+    flush = th.empty(256 * 1024 * 1024, dtype=th.uint8, device=dev)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        th.cuda.synchronize()
+        e0, e1 = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
+        tot = 0.0
+        for _ in range(args.steps):
+            flush.zero_()   # L2 flush between timed calls
+            e0.record()
+            fn()
+            e1.record()
+            th.cuda.synchronize()
+            tot += e0.elapsed_time(e1)
+        return tot / args.steps * 1e3
+
+    with th.no_grad():
+        for (N_, K_, tanh) in [(128, 768, (0, 128)), (96, 768, (0, 64)), (768, 768, None), (768, 128, None)]:
+            th.manual_seed(0)
+            A = th.randn(M, K_, device=dev).bfloat16()
+            W = (th.randn(N_, K_, device=dev) / K_ ** 0.5).bfloat16()
+
+            def torch_ref():
+                y = A @ W.mT
+                if tanh:
+                    y[:, tanh[0]:tanh[1]] = th.tanh(y[:, tanh[0]:tanh[1]])
+                return y
+            ours, ref = timed(lambda: proj(A, W, tanh)), timed(torch_ref)
+            err = (proj(A, W, tanh).float() - torch_ref().float()).abs().max().item()
+            print(json.dumps({'metric': f'projection GEMM M{M} N{N_} K{K_} bf16' + (f' tanh on columns {tanh}' if tanh else ''), 'unit': 'us',
+                              'value': ours, 'torch_cublas_us': ref, 'tflops': 2 * M * N_ * K_ / ours / 1e6, 'max_abs_diff_vs_torch': err,
+                              'steps': args.steps, 'higher_is_better': False, 'dtype': 'bf16', 'data': 'synthetic',
+                              'config': {'workload': 'proj', 'l2': 'flushed by zeroing a 256 MB buffer before each timed call'}}))
+
+
 def run_other(args):
     th.cuda.set_device(0)
     print(json.dumps(other_line(args.workload, None if args.batch == B_PER_GPU else args.batch, args.steps, args.warmup)))
@@ -695,13 +739,15 @@ def main():
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer leg (profiling runs)')
     ap.add_argument('--batch', type=int, default=B_PER_GPU, help='batch per GPU (default: the benchmark shape)')
-    ap.add_argument('--workload', default='wkv7', choices=['wkv7', 'attn_ln', 'prefill', 'prefill_b1', 'ddlerp', 'expand_loras', 'mixer'],
+    ap.add_argument('--workload', default='wkv7', choices=['wkv7', 'attn_ln', 'prefill', 'prefill_b1', 'ddlerp', 'expand_loras', 'mixer', 'proj'],
                     help='wkv7 (default) is the headline line; the others time secondary workloads on one GPU')
     args = ap.parse_args()
     if args.impl == 'reference':
         run_reference(args)
     elif args.impl == 'reference-cuda':
         run_reference_cuda(args)
+    elif args.workload == 'proj':
+        run_proj(args)
     elif args.workload == 'prefill':
         run_prefill(args)
     elif args.workload != 'wkv7':
