@@ -84,16 +84,20 @@ __global__ void __launch_bounds__(128) loras_fwd_kernel(LorasParams p) {
         }
     }
     cp_async_commit();
+    // the LoRA inputs come straight from global memory into MMA fragments: requested before the wait for the asynchronous
+    // copies, so that the two latencies overlap
+    uint32_t az[D / 16][4], aa[D / 16][4], am[D / 16][4], ak[D / 16][4];
+    if (r0 < p.rows) {
+        load_in_frags<D, true>(az, (const bf16*)p.lin[0], r0, g, t4);
+        load_in_frags<D, false>(aa, (const bf16*)p.lin[1], r0, g, t4);
+        load_in_frags<D, false>(am, (const bf16*)p.lin[2], r0, g, t4);
+        load_in_frags<D, false>(ak, (const bf16*)p.lin[3], r0, g, t4);
+    }
     cp_async_wait<0>();
     __syncthreads();
     if (r0 >= p.rows) return;
     const int lr = 16 * warp;  // this warp's first tile row
 
-    uint32_t az[D / 16][4], aa[D / 16][4], am[D / 16][4], ak[D / 16][4];
-    load_in_frags<D, true>(az, (const bf16*)p.lin[0], r0, g, t4);
-    load_in_frags<D, false>(aa, (const bf16*)p.lin[1], r0, g, t4);
-    load_in_frags<D, false>(am, (const bf16*)p.lin[2], r0, g, t4);
-    load_in_frags<D, false>(ak, (const bf16*)p.lin[3], r0, g, t4);
     float z[8][4];
     float ss0 = 0.f, ss1 = 0.f;
 #pragma unroll
