@@ -550,14 +550,18 @@ __global__ void ddlerp_dl_finish_kernel(float* __restrict__ dL, const float* __r
     const int c = blockIdx.x * blockDim.x + threadIdx.x, n0 = blockIdx.y * 8;
     if (c >= C) return;
     const float a = __bfloat162float(alpha[c]);
+    // (4D is a multiple of 8: every thread has its 8 rows; all loads are issued before the first use)
+    float w1[8], w2[8], lv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const long long i = (long long)(n0 + j) * C + c;
+        w1[j] = dL[i]; w2[j] = dW2[i]; lv[j] = __bfloat162float(L[i]);
+    }
     float acc = 0.f;
 #pragma unroll
-    for (int n = n0; n < n0 + 8; ++n) {
-        if (n >= n4) break;
-        const long long i = (long long)n * C + c;
-        const float w1 = dL[i], w2 = dW2[i];
-        dL[i] = w1 * (1.f - a) + w2 * a;
-        acc += __bfloat162float(L[i]) * (w2 - w1);
+    for (int j = 0; j < 8; ++j) {
+        dL[(long long)(n0 + j) * C + c] = w1[j] * (1.f - a) + w2[j] * a;
+        acc += lv[j] * (w2[j] - w1[j]);
     }
     if (dalpha) atomicAdd(dalpha + c, acc);
 }
