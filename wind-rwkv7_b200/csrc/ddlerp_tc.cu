@@ -1,6 +1,6 @@
-// ddlerp forward on the 5th-generation tensor cores (tcgen05 + TMA), bf16.
+// ddlerp forward and backward on the 5th-generation tensor cores (tcgen05 + TMA), bf16.
 //
-// Replaces fw1_triton_ + fw2_triton_ of the reference (wind_rwkv/rwkv7/rwkv7_ddlerp.py:19-84).  With xx = x_{t-1} - x_t:
+// Forward: replaces fw1_triton_ + fw2_triton_ of the reference (wind_rwkv/rwkv7/rwkv7_ddlerp.py:19-84).  With xx = x_{t-1} - x_t:
 //     u   = x + xx * alpha                         m = tanh(u L^T)                y_i = x + xx * (m_i R_i^T + beta_i)
 // The token shift is linear, so it moves into the weights and into the coordinates of the tile copies:
 //     u L^T = x_t (L (1 - alpha))^T + x_{t-1} (L alpha)^T  =  [x_t | x_{t-1}] [L1 | L2]^T,      y_i = x_t + (x_{t-1} - x_t) z_i.
@@ -16,6 +16,10 @@
 //             warps read z_i one token row per thread, form y_i from rows r and r + 1 of the x tile and store [32 x 64]
 //             pieces of the four output tiles by bulk tensor stores.  HBM traffic = x once (re-reads hit L2) + m + outputs.
 //             Rank 64 (two stages would not fit shared memory) runs the mma.sync forward of ddlerp_fwd.cu instead.
+// Backward (replaces bw1..bw4_triton_, rwkv7_ddlerp.py:92-303; ranks 16 and 32, rank 64 runs ddlerp_bwd.cu's kernels), further
+// down in this file, each with its own description: the rearranged weights (one small launch), dpre (ddlerp_dpre_tc_kernel),
+// the main step dx / dR / dbeta (ddlerp_main_tc_kernel), dW12 = dpre^T [x_t | x_{t-1}] (ddlerp_dw12_kernel) and the step
+// that turns it into dL and dalpha (ddlerp_dl_finish_kernel).
 // Every wait on an mbarrier is bounded (mbar_wait_bounded): a wait that runs out sets the CTA's abort flag, reports
 // kDeviceTimeout, and the CTA leaves without storing; tensor memory is released in every case.
 #include <cuda.h>
